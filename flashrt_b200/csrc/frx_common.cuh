@@ -1,0 +1,147 @@
+// Shared definitions for the libfrx kernels (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "frx.h"
+
+namespace frx {
+
+// ---- Q2_0 format and the tiled layout (see frx_q2_tile_experts in frx.h)
+constexpr int kQK = 64;           // weights per Q2_0 block
+constexpr int kBlockBytes = 18;   // fp16 scale + 16 code bytes
+constexpr int kQ8 = 32;           // values per int8 activation block
+constexpr int kUnitRows = 16;     // M rows of one unit
+constexpr int kUnitK = 128;       // weights of K in one unit (two blocks)
+constexpr int kUnitCodeBytes = 512;
+constexpr int kUnitBytes = 576;   // 16 rows x 2 blocks x 18 bytes
+constexpr int kTokPerItem = 8;    // tokens of one work item: the N of mma.m16n8k32
+
+// The float 1.5 * 2^23 and its bit pattern: an int32 accumulator started at kMagicBits + c,
+// read as a float, is exactly kMagic + c for |c| < 2^22, so int -> float costs one subtraction.
+constexpr float kMagic = 12582912.0f;
+constexpr int kMagicBits = 0x4B400000;
+
+constexpr size_t kAlign = 256;
+__host__ __device__ inline size_t align_up(size_t x, size_t a = kAlign) { return (x + a - 1) / a * a; }
+
+inline size_t gu_group_bytes(int n) { return size_t(n / kUnitK) * kUnitBytes; }      // 8 gate + 8 up rows
+inline size_t down_group_bytes(int ff) { return size_t(ff / kUnitK) * kUnitBytes; }  // 16 down rows
+inline size_t gu_section_bytes(int n, int ff) { return size_t(ff / 8) * gu_group_bytes(n); }
+
+// ---- errors (host side)
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+#define FRX_CUDA(expr)                                              \
+    do {                                                            \
+        cudaError_t e_ = (expr);                                    \
+        if (e_ != cudaSuccess) return ::frx::cuda_fail(e_, #expr);  \
+    } while (0)
+
+int sm_count();
+int max_smem_optin();
+
+// Device-side error codes written to a workspace's status word.
+enum : int {
+    kDevOk = 0,
+    kDevBadExpertId = 1,   // an id outside [0, E)
+    kDevWaitTimeout = 2,   // a bounded wait on a shared-memory barrier ran out
+    kDevTooManyItems = 3,
+};
+
+// ---- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for a barrier phase for at most kWaitLimitNs. Returns false when the wait ran out or
+// `*abort` was already set; it then sets `*abort` so every later wait of the block returns at
+// once, and the caller's block finishes its control flow without trusting the data.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+    const uint64_t t0 = global_ns();
+    for (uint32_t polls = 1;; ++polls) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((polls & 63u) == 0) {
+            if (*abort) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *abort = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// 1-D bulk copy global -> shared through the TMA unit, completion counted on an mbarrier.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// D (16x8 s32) += A (16x32 u8, row) * B (32x8 s8, col)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- oracle-exact scalar pieces (no FMA contraction, IEEE division; never built with fast-math)
+
+// roundf: to nearest, halves away from zero
+__device__ __forceinline__ float round_half_away(float v) {
+    const float t = truncf(v);
+    const float f = __fsub_rn(v, t);   // exact
+    return fabsf(f) >= 0.5f ? t + copysignf(1.0f, v) : t;
+}
+
+// Correctly rounded expf for all but a vanishing fraction of inputs: exp in double, one rounding.
+__device__ __forceinline__ float expf_cr(float x) { return float(exp(double(x))); }
+
+// silu(g) * u as the reference's CPU path writes it: g / (1 + exp(-g)) * u
+__device__ __forceinline__ float swiglu_ref(float g, float u) {
+    const float e = expf_cr(-g);
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
+}
+
+__device__ __forceinline__ float sigmoid_ref(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_cr(-x))); }
+
+}  // namespace frx

@@ -1,0 +1,1019 @@
+// Decode-sized MoE layer: quantize x, group (token, expert) slots by expert, gate/up + SwiGLU,
+// down, ordered weighted combine. Experts are streamed once from HBM in the tiled layout by a
+// producer warp issuing 1-D bulk (TMA) copies into a shared-memory ring; consumer warps unpack the
+// 2-bit codes in registers and feed int8 tensor-core MMAs whose N dimension is the (at most 8)
+// tokens routed to the expert. Integer sums are exact; the float scaling and the accumulation over
+// the blocks of a row run in one lane, in block order, with the roundings of the reference's
+// scalar matvec (quant/q2_0/q2_0.cpp:119-140), so results match it bit for bit.
+#include "frx_common.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace frx {
+namespace {
+
+constexpr int kMaxChunkTokens = 64;   // tokens grouped by one k_group launch
+constexpr int kCookie = 0x46525831;
+
+// One unit of expert work: a tiled expert blob and up to 8 (token, expert) slots routed to it.
+// A slot is a row of the hidden and output buffers: t * K + k for the k-th expert of token t,
+// TK + t for the shared expert of token t.
+struct __align__(16) Item {
+    const uint8_t* blob;
+    int32_t n_tok;
+    int32_t expert;              // for diagnostics: the expert id, -1 for the shared expert
+    int32_t slot[kTokPerItem];
+};
+static_assert(sizeof(Item) == 48, "Item is 48 bytes");
+constexpr int kItemWords = sizeof(Item) / 4;
+
+__host__ __device__ inline int slot_token(int slot, int K, int TK) { return slot < TK ? slot / K : slot - TK; }
+
+// Workspace status words: [0] device error, [1] items of the current chunk, [2] detail, [3] cookie.
+struct Layout {
+    size_t status, items, order, xq, xd, xs, h, y, ysh, total;
+    int max_items;
+};
+
+Layout make_layout(int T, int K, int n, int ff) {
+    const int Tc = T < kMaxChunkTokens ? T : kMaxChunkTokens;
+    Layout L{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += align_up(bytes);
+        return o;
+    };
+    L.max_items = Tc * K + (Tc + kTokPerItem - 1) / kTokPerItem;
+    L.status = take(64);
+    L.items = take(size_t(L.max_items) * sizeof(Item));
+    L.order = take(size_t(Tc) * K * 4);
+    L.xq = take(size_t(Tc) * n);
+    L.xd = take(size_t(Tc) * (n / kQ8) * 4);
+    L.xs = take(size_t(Tc) * (n / kQ8) * 4);
+    L.h = take(size_t(Tc) * (K + 1) * ff * 4);
+    L.y = take(size_t(Tc) * K * n * 4);
+    L.ysh = take(size_t(Tc) * n * 4);
+    L.total = off;
+    return L;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Q8 quantization of 32 values held one per lane: returns the code; lane 0 gets scale and sum.
+// quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16.
+__device__ __forceinline__ int q8_block(float v, float& d_out, int& sum_out) {
+    float am = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float d = __fdiv_rn(am, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const int q = int(round_half_away(__fmul_rn(v, id)));
+    int s = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    d_out = __half2float(__float2half_rn(d));
+    sum_out = s;
+    return q;
+}
+
+// x [T][n] -> q [T][n], d [T][n/32], and (optionally) the block sums of the codes.
+__global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ q,
+                                                  float* __restrict__ d, int32_t* __restrict__ sums) {
+    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= n_blocks) return;
+    float dd;
+    int ss;
+    const int c = q8_block(x[blk * kQ8 + lane], dd, ss);
+    q[blk * kQ8 + lane] = int8_t(c);
+    if (lane == 0) {
+        d[blk] = dd;
+        if (sums) sums[blk] = ss;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouping: the distinct experts of up to 64 tokens in ascending id, each with its tokens in
+// token order, cut into items of at most 8 tokens; then the shared expert's items; and per token
+// the order in which its slots are summed (ascending expert id, the order in which the
+// reference's CPU path adds them, quant/q2_0/moe_cpu.cpp:70-79). One block, no atomics on data:
+// the result does not depend on thread timing.
+__global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids, int T, int K, int E,
+                                                const uint8_t* __restrict__ experts, size_t stride,
+                                                const uint8_t* __restrict__ shared, Item* __restrict__ items,
+                                                int* __restrict__ status, int32_t* __restrict__ order, int max_items) {
+    extern __shared__ unsigned long long mask[];   // [E] tokens routed to each expert
+    __shared__ int scan[1024];
+    const int tid = threadIdx.x;
+    if (tid == 0 && status[3] != kCookie) {   // first use of this workspace
+        status[0] = kDevOk;
+        status[2] = 0;
+        status[3] = kCookie;
+    }
+    for (int e = tid; e < E; e += 1024) mask[e] = 0ull;
+    __syncthreads();
+    for (int s = tid; s < T * K; s += 1024) {
+        const int e = ids[s];
+        if (e < 0 || e >= E) {
+            status[0] = kDevBadExpertId;
+            status[2] = s;
+        } else {
+            atomicOr(&mask[e], 1ull << (s / K));
+        }
+    }
+    __syncthreads();
+    const int per = (E + 1023) / 1024, e0 = tid * per, e1 = min(E, e0 + per);
+    int cnt = 0;
+    for (int e = e0; e < e1; ++e) cnt += (__popcll(mask[e]) + kTokPerItem - 1) / kTokPerItem;
+    scan[tid] = cnt;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {   // inclusive scan
+        const int v = tid >= o ? scan[tid - o] : 0;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    int at = scan[tid] - cnt;
+    const int routed_items = scan[1023];
+    const int shared_items = shared ? (T + kTokPerItem - 1) / kTokPerItem : 0;
+    if (routed_items + shared_items > max_items) {
+        if (tid == 0) {
+            status[0] = kDevTooManyItems;
+            status[1] = 0;
+        }
+        return;
+    }
+    for (int e = e0; e < e1; ++e) {
+        unsigned long long bits = mask[e];
+        while (bits) {
+            Item it;
+            it.blob = experts + size_t(e) * stride;
+            it.expert = e;
+            int m = 0;
+            while (bits && m < kTokPerItem) {
+                const int t = __ffsll((long long)bits) - 1;
+                bits &= bits - 1;
+                int k = 0;
+                while (k < K - 1 && ids[t * K + k] != e) ++k;
+                it.slot[m] = t * K + k;
+                ++m;
+            }
+            it.n_tok = m;
+            for (int j = m; j < kTokPerItem; ++j) it.slot[j] = 0;
+            items[at++] = it;
+        }
+    }
+    if (tid < shared_items) {
+        Item it;
+        it.blob = shared;
+        it.expert = -1;
+        const int t0 = tid * kTokPerItem, m = min(kTokPerItem, T - t0);
+        it.n_tok = m;
+        for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? T * K + t0 + j : 0;
+        items[routed_items + tid] = it;
+    }
+    if (tid == 0) status[1] = routed_items + shared_items;
+    if (tid < T) {   // slots of token tid by ascending expert id (insertion sort, K <= 32)
+        int32_t* o = order + tid * K;
+        for (int k = 0; k < K; ++k) {
+            const int e = ids[tid * K + k];
+            int j = k;
+            while (j > 0 && ids[o[j - 1]] > e) {
+                o[j] = o[j - 1];
+                --j;
+            }
+            o[j] = tid * K + k;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The streaming expert kernel, used for both halves of the FFN.
+//   GATE_UP: a tile is one gate/up group (8 gate + 8 up rows over K = n); the activations are the
+//            Q8 codes of x; the epilogue is SwiGLU and a float store of the hidden value.
+//   else   : a tile is kDownGroups down groups (16 rows each over K = ff); the activations are
+//            the hidden values, quantized here; the epilogue stores the expert's output rows.
+constexpr int kDownGroups = 4;
+
+struct StreamParams {
+    const Item* items;
+    int* status;
+    // activations: GATE_UP reads xq/xd/xs; down reads h
+    const int8_t* xq;
+    const float* xd;
+    const int32_t* xs;
+    float* h;          // [slots][ff]   written by GATE_UP, read by down
+    float* y;          // [T*K][n]      routed slots (down)
+    float* ysh;        // [T][n]        shared-expert slots (down)
+    int n, ff, K, TK;
+    int ring;          // ring slots
+};
+
+// Shared-memory plan of k_stream.
+struct SmemPlan {
+    uint32_t ring, bfrag[2], da[2], ci[2], item[2], bars, abort, total;
+};
+__host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t tile_bytes, int ring) {
+    const uint32_t nb = uint32_t(kdim / kQK);
+    SmemPlan s{};
+    uint32_t off = 0;
+    s.ring = off;
+    off += uint32_t(ring) * tile_bytes;
+    for (int i = 0; i < 2; ++i) {
+        s.bfrag[i] = off;
+        off += nb * 512;   // [block][lane] uint4
+    }
+    for (int i = 0; i < 2; ++i) {
+        s.da[i] = off;
+        off += nb * 64;    // [block][t4] float4
+    }
+    for (int i = 0; i < 2; ++i) {
+        s.ci[i] = off;
+        off += nb * 64;    // [block][t4] int4
+    }
+    for (int i = 0; i < 2; ++i) {
+        s.item[i] = off;
+        off += 64;
+    }
+    s.bars = off;
+    off += uint32_t(ring) * 16;
+    s.abort = off;
+    off += 16;
+    s.total = off;
+    return s;
+}
+
+// 16 M rows x kdim of one group against the item's tokens: sums[0..1] = M row g, columns
+// 2*t4 and 2*t4+1; sums[2..3] = M row g + 8, same columns.
+__device__ __forceinline__ void group_mma(const uint8_t* __restrict__ grp, int units, const uint4* __restrict__ bfrag,
+                                          const float4* __restrict__ da, const int4* __restrict__ ci, int lane, float (&sum)[4]) {
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr uint32_t M = 0x03030303u;
+    sum[0] = sum[1] = sum[2] = sum[3] = 0.0f;
+#pragma unroll 2
+    for (int u = 0; u < units; ++u) {
+        const uint4 c = *reinterpret_cast<const uint4*>(grp + u * kUnitBytes + lane * 16);
+        const uint2 sc = *reinterpret_cast<const uint2*>(grp + u * kUnitBytes + kUnitCodeBytes + g * 8);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t w0 = j ? c.y : c.x, w1 = j ? c.w : c.z;
+            const int b = 2 * u + j;
+            const uint4 bf = bfrag[b * 32 + lane];
+            const int4 c0 = ci[b * 4 + t4];
+            const float4 a = da[b * 4 + t4];
+            int acc0[4] = {c0.x, c0.y, c0.x, c0.y};
+            int acc1[4] = {c0.z, c0.w, c0.z, c0.w};
+            mma_u8s8(acc0, w0 & M, w1 & M, (w0 >> 2) & M, (w1 >> 2) & M, bf.x, bf.y);
+            mma_u8s8(acc1, (w0 >> 4) & M, (w1 >> 4) & M, (w0 >> 6) & M, (w1 >> 6) & M, bf.z, bf.w);
+            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
+            const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
+            const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a0 = (i & 1) ? a.y : a.x, a1 = (i & 1) ? a.w : a.z;
+                const float s0 = __fsub_rn(__int_as_float(acc0[i]), kMagic);
+                const float s1 = __fsub_rn(__int_as_float(acc1[i]), kMagic);
+                // a0 * s0 and a1 * s1 are exact (11-bit scale x 13-bit integer), so one fused
+                // multiply-add rounds exactly where the reference's two statements round once.
+                const float sumi = __fmaf_rn(a1, s1, __fmul_rn(a0, s0));
+                sum[i] = __fadd_rn(sum[i], __fmul_rn(i < 2 ? d_lo : d_hi, sumi));
+            }
+        }
+    }
+}
+
+template <bool GATE_UP, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kdim = GATE_UP ? p.n : p.ff;
+    const int nb = kdim / kQK, units = kdim / kUnitK;
+    const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
+    const int groups_per_tile = GATE_UP ? 1 : kDownGroups;
+    const uint32_t tile_bytes = group_bytes * groups_per_tile;
+    const int tiles_per_expert = GATE_UP ? p.ff / 8 : p.n / 16 / kDownGroups;
+    const size_t section = GATE_UP ? 0 : size_t(p.ff / 8) * (size_t(p.n / kUnitK) * kUnitBytes);
+    const SmemPlan sp = smem_plan(kdim, tile_bytes, p.ring);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars);
+    uint64_t* empty = full + p.ring;
+    volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
+
+    const int n_items = p.status[1];
+    const long long total = (long long)n_items * tiles_per_expert;
+    const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    const int ntiles = int(hi - lo);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.ring; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        *abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == NW) {
+        // ---- producer: one lane streams this block's tiles through the ring
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % p.ring, use = i / p.ring;
+                if (use > 0 && !mbar_wait_bounded(empty + s, uint32_t(use - 1) & 1u, abort)) break;
+                const long long tau = lo + i;
+                const int item = int(tau / tiles_per_expert), tile = int(tau % tiles_per_expert);
+                const uint8_t* src = p.items[item].blob + section + size_t(tile) * tile_bytes;
+                mbar_expect_tx(full + s, tile_bytes);
+                bulk_g2s(smem + sp.ring + size_t(s) * tile_bytes, src, tile_bytes, full + s);
+                issued = i + 1;
+            }
+            if (*abort) {
+                // Let the copies still in flight land before the block's shared memory is released.
+                const int first = issued > p.ring ? issued - p.ring : 0;
+                for (int i = first; i < issued; ++i) {
+                    const uint64_t t0 = global_ns();
+                    while (!mbar_try_wait(full + i % p.ring, uint32_t(i / p.ring) & 1u) && global_ns() - t0 < kWaitLimitNs) {
+                    }
+                }
+                p.status[0] = kDevWaitTimeout;
+            }
+        }
+    } else if (ntiles > 0) {
+        // ---- consumers: segments of consecutive tiles that belong to one item
+        const int first_item = int(lo / tiles_per_expert), last_item = int((hi - 1) / tiles_per_expert);
+        const int nseg = last_item - first_item + 1;
+        const int ctid = threadIdx.x;   // 0 .. NW*32-1
+
+        auto build = [&](int q) {
+            const Item* it = p.items + first_item + q;
+            const int buf = q & 1;
+            uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag[buf]);
+            float* daw = reinterpret_cast<float*>(smem + sp.da[buf]);
+            int* ciw = reinterpret_cast<int*>(smem + sp.ci[buf]);
+            if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
+            const int m = it->n_tok;
+            if (GATE_UP) {
+                const int wpt = nb * 16;   // words per token
+                for (int idx = ctid; idx < m * wpt; idx += NW * 32) {
+                    const int g = idx / wpt, r = idx % wpt;
+                    const int b = r >> 4, s = (r >> 3) & 1, hi2 = (r >> 2) & 1, t4 = r & 3;
+                    const uint32_t v = reinterpret_cast<const uint32_t*>(p.xq + size_t(slot_token(it->slot[g], p.K, p.TK)) * p.n)[r];
+                    bw[(b * 32 + g * 4 + t4) * 4 + s * 2 + hi2] = v;
+                }
+                for (int idx = ctid; idx < m * nb * 2; idx += NW * 32) {
+                    const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
+                    const size_t src = size_t(slot_token(it->slot[g], p.K, p.TK)) * (p.n / kQ8) + r;
+                    const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
+                    daw[dst] = p.xd[src];
+                    ciw[dst] = kMagicBits - p.xs[src];
+                }
+            } else {
+                const int bpt = p.ff / kQ8;   // Q8 blocks per token
+                int8_t* bb = reinterpret_cast<int8_t*>(bw);
+                for (int idx = warp; idx < m * bpt; idx += NW) {
+                    const int g = idx / bpt, blk = idx % bpt;
+                    const size_t row = size_t(it->slot[g]) * p.ff;
+                    float d;
+                    int sm;
+                    const int q8 = q8_block(p.h[row + blk * kQ8 + lane], d, sm);
+                    const int b = blk >> 1, s = blk & 1, hi2 = lane >> 4, t4 = (lane >> 2) & 3;
+                    bb[((b * 32 + g * 4 + t4) * 4 + s * 2 + hi2) * 4 + (lane & 3)] = int8_t(q8);
+                    if (lane == 0) {
+                        const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
+                        daw[dst] = d;
+                        ciw[dst] = kMagicBits - sm;
+                    }
+                }
+            }
+        };
+
+        build(0);
+        named_bar_sync(1, NW * 32);
+        for (int q = 0; q < nseg; ++q) {
+            const int item = first_item + q, buf = q & 1;
+            const long long seg_lo = max(lo, (long long)item * tiles_per_expert);
+            const long long seg_hi = min(hi, (long long)(item + 1) * tiles_per_expert);
+            const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
+            const float4* da = reinterpret_cast<const float4*>(smem + sp.da[buf]);
+            const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci[buf]);
+            const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
+            const int m = its->n_tok;
+            const int g = lane >> 2, t4 = lane & 3;
+            const int c0 = 2 * t4, c1 = 2 * t4 + 1;
+            for (long long tau = seg_lo + warp; tau < seg_hi; tau += NW) {
+                const int i = int(tau - lo), s = i % p.ring, use = i / p.ring;
+                const int tile = int(tau % tiles_per_expert);
+                mbar_wait_bounded(full + s, uint32_t(use) & 1u, abort);
+                const uint8_t* tp = smem + sp.ring + size_t(s) * tile_bytes;
+                float sum[4];
+                if (GATE_UP) {
+                    group_mma(tp, units, bfrag, da, ci, lane, sum);
+                    const int row = tile * 8 + g;
+                    if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
+                    if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
+                } else {
+#pragma unroll 1
+                    for (int gd = 0; gd < kDownGroups; ++gd) {
+                        group_mma(tp + size_t(gd) * group_bytes, units, bfrag, da, ci, lane, sum);
+                        const int row = (tile * kDownGroups + gd) * 16 + g;
+                        if (c0 < m) {
+                            const int sl = its->slot[c0];
+                            float* o = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
+                            o[row] = sum[0];
+                            o[row + 8] = sum[2];
+                        }
+                        if (c1 < m) {
+                            const int sl = its->slot[c1];
+                            float* o = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
+                            o[row] = sum[1];
+                            o[row + 8] = sum[3];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + s);
+            }
+            if (q + 1 < nseg) build(q + 1);
+            named_bar_sync(1, NW * 32);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort) p.status[0] = kDevWaitTimeout;
+}
+
+// out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate)
+__global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out, const float* __restrict__ y,
+                                                         const float* __restrict__ wts, const int32_t* __restrict__ order,
+                                                         const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= n) return;
+    float acc = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const int s = order[t * K + k];
+        acc = __fadd_rn(acc, __fmul_rn(wts[s], y[size_t(s) * n + i]));
+    }
+    if (ysh) {
+        const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
+        acc = __fadd_rn(acc, __fmul_rn(ysh[size_t(t) * n + i], g));
+    }
+    out[size_t(t) * n + i] = acc;
+}
+
+// k_moe_combine / k_stream_combine semantics: k order, as the hit list gives it
+__global__ void __launch_bounds__(256) k_combine_hits(float* __restrict__ out, const float* __restrict__ yh,
+                                                      const float* __restrict__ w, const int32_t* __restrict__ hit_n,
+                                                      const float* __restrict__ shexp, const float* __restrict__ gate, int n, int K) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= n) return;
+    const int kn = hit_n ? hit_n[t] : K;
+    float acc = 0.0f;
+    for (int k = 0; k < kn; ++k) acc = __fadd_rn(acc, __fmul_rn(w[t * K + k], yh[(size_t(t) * K + k) * n + i]));
+    if (shexp) {
+        const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
+        acc = __fadd_rn(acc, __fmul_rn(shexp[size_t(t) * n + i], g));
+    }
+    out[size_t(t) * n + i] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// moe_hits grouping: items from per-token lists of expert pointers. Slots s = t * K + k with
+// k < hit_n[t] are live; live slots with the same pointer form one group (an expert several
+// tokens hit is read once), groups ordered by first appearance, members in slot order.
+// One block; S = T * K <= 1024.
+__global__ void __launch_bounds__(1024) k_group_ptr(const uint8_t* const* __restrict__ hit_ptr, const int32_t* __restrict__ hit_n,
+                                                    int T, int K, Item* __restrict__ items, int* __restrict__ status) {
+    __shared__ const uint8_t* ptr[1024];
+    __shared__ int scan[1024];
+    const int s = threadIdx.x, S = T * K;
+    if (s == 0 && status[3] != kCookie) {
+        status[0] = kDevOk;
+        status[2] = 0;
+        status[3] = kCookie;
+    }
+    const bool live = s < S && (s % K) < hit_n[s / K];
+    ptr[s] = live ? hit_ptr[s] : nullptr;
+    __syncthreads();
+    int leader = s, rank = 0, size = 0;
+    if (live) {
+        const uint8_t* mine = ptr[s];
+        leader = -1;
+        for (int j = 0; j < S; ++j)
+            if (ptr[j] == mine) {
+                if (leader < 0) leader = j;
+                if (j < s) ++rank;
+                ++size;
+            }
+    }
+    const int my_items = (live && leader == s) ? (size + kTokPerItem - 1) / kTokPerItem : 0;
+    scan[s] = my_items;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+        const int v = s >= o ? scan[s - o] : 0;
+        __syncthreads();
+        scan[s] += v;
+        __syncthreads();
+    }
+    if (s == 0) status[1] = scan[1023];
+    if (live) {
+        const int base = scan[leader] - (size + kTokPerItem - 1) / kTokPerItem;   // exclusive offset of the group
+        Item* it = items + base + rank / kTokPerItem;
+        it->slot[rank % kTokPerItem] = s;
+        if (rank % kTokPerItem == 0) {
+            it->blob = ptr[s];
+            it->expert = leader;
+            const int m = min(kTokPerItem, size - rank);
+            it->n_tok = m;
+            for (int j = m; j < kTokPerItem; ++j) it->slot[j] = 0;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouping for any number of tokens (the prefill-sized entry): stable in slot order, no host
+// synchronisation, the same result on every run. Slots are cut into chunks of 1024.
+constexpr int kChunkSlots = 1024;
+
+// per chunk: how many of its slots go to each expert
+__global__ void __launch_bounds__(256) k_pf_hist(const int32_t* __restrict__ ids, int S, int E, int* __restrict__ chunk_cnt,
+                                                 int* __restrict__ status) {
+    extern __shared__ int hist[];
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status[3] != kCookie) {
+        status[0] = kDevOk;
+        status[2] = 0;
+        status[3] = kCookie;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int s0 = blockIdx.x * kChunkSlots;
+    for (int s = s0 + threadIdx.x; s < min(S, s0 + kChunkSlots); s += blockDim.x) {
+        const int e = ids[s];
+        if (e < 0 || e >= E) {
+            status[0] = kDevBadExpertId;
+            status[2] = s;
+        } else {
+            atomicAdd(&hist[e], 1);   // integer counts: exact whatever the order
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_cnt[size_t(blockIdx.x) * E + e] = hist[e];
+}
+
+// per expert: exclusive offsets of its slots over the chunks (written back into chunk_cnt), its
+// bounds in the grouped order, and the range of its items. bounds, item_off: [E + 1].
+__global__ void __launch_bounds__(1024) k_pf_scan(int* __restrict__ chunk_cnt, int n_chunks, int E, int* __restrict__ bounds,
+                                                  int* __restrict__ item_off, int* __restrict__ status, int max_items) {
+    __shared__ int scan_s[1024], scan_i[1024];
+    const int tid = threadIdx.x;
+    const int per = (E + 1023) / 1024, e0 = tid * per, e1 = min(E, e0 + per);
+    int slots = 0, items = 0;
+    for (int e = e0; e < e1; ++e) {
+        int run = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int v = chunk_cnt[size_t(c) * E + e];
+            chunk_cnt[size_t(c) * E + e] = run;
+            run += v;
+        }
+        bounds[e] = run;   // the count for now
+        slots += run;
+        items += (run + kTokPerItem - 1) / kTokPerItem;
+    }
+    scan_s[tid] = slots;
+    scan_i[tid] = items;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+        const int a = tid >= o ? scan_s[tid - o] : 0, b = tid >= o ? scan_i[tid - o] : 0;
+        __syncthreads();
+        scan_s[tid] += a;
+        scan_i[tid] += b;
+        __syncthreads();
+    }
+    int at_s = scan_s[tid] - slots, at_i = scan_i[tid] - items;
+    for (int e = e0; e < e1; ++e) {
+        const int c = bounds[e];
+        bounds[e] = at_s;
+        item_off[e] = at_i;
+        at_s += c;
+        at_i += (c + kTokPerItem - 1) / kTokPerItem;
+    }
+    if (tid == 0) {
+        bounds[E] = scan_s[1023];
+        item_off[E] = scan_i[1023];
+        if (scan_i[1023] > max_items) {
+            status[0] = kDevTooManyItems;
+            status[1] = 0;
+        } else {
+            status[1] = scan_i[1023];
+        }
+    }
+}
+
+// per chunk, one warp: every slot's position in the grouped order (by expert, then slot order)
+__global__ void __launch_bounds__(32) k_pf_place(const int32_t* __restrict__ ids, int S, int E, const int* __restrict__ chunk_off,
+                                                 const int* __restrict__ bounds, int32_t* __restrict__ perm) {
+    extern __shared__ int cursor[];
+    const int lane = threadIdx.x, c = blockIdx.x;
+    for (int e = lane; e < E; e += 32) cursor[e] = bounds[e] + chunk_off[size_t(c) * E + e];
+    __syncwarp();
+    for (int it = 0; it < kChunkSlots / 32; ++it) {
+        const int s = c * kChunkSlots + it * 32 + lane;
+        const int e = s < S ? ids[s] : -1;
+        const bool ok = e >= 0 && e < E;
+        const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        const int rank = __popc(peers & ((1u << lane) - 1));
+        int pos = 0;
+        if (ok) pos = cursor[e] + rank;
+        __syncwarp();
+        if (ok) {
+            perm[pos] = s;
+            if (rank == 0) cursor[e] += __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
+// one thread per item: its expert (binary search over item_off) and its slots
+__global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds, const int* __restrict__ item_off, int E,
+                                                  const int32_t* __restrict__ perm, const uint8_t* __restrict__ experts, size_t stride,
+                                                  const int* __restrict__ status, Item* __restrict__ items) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= status[1]) return;
+    int lo = 0, hi = E;   // the e with item_off[e] <= i < item_off[e + 1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (item_off[mid] <= i) lo = mid; else hi = mid;
+    }
+    const int e = lo, base = bounds[e] + (i - item_off[e]) * kTokPerItem, m = min(kTokPerItem, bounds[e + 1] - base);
+    Item it;
+    it.blob = experts + size_t(e) * stride;
+    it.expert = e;
+    it.n_tok = m;
+    for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? perm[base + j] : 0;
+    items[i] = it;
+}
+
+// ---------------------------------------------------------------------------------------------
+constexpr int kNW = 8;
+
+struct StreamCfg {
+    int ring_gu = 0, ring_dn = 0;
+    uint32_t smem_gu = 0, smem_dn = 0;
+};
+
+int stream_cfg(int n, int ff, StreamCfg& c) {
+    const int budget = max_smem_optin() - 1024;
+    if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
+    auto fit = [&](int kdim, uint32_t tile_bytes, int& ring, uint32_t& bytes) {
+        for (ring = 24; ring >= 2; --ring) {
+            bytes = smem_plan(kdim, tile_bytes, ring).total;
+            if (int(bytes) <= budget) return true;
+        }
+        return false;
+    };
+    if (!fit(n, uint32_t(n / kUnitK) * kUnitBytes, c.ring_gu, c.smem_gu) ||
+        !fit(ff, uint32_t(ff / kUnitK) * kUnitBytes * kDownGroups, c.ring_dn, c.smem_dn))
+        return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
+    return FRX_OK;
+}
+
+int set_smem_attr() {
+    static std::once_flag once;
+    static cudaError_t err = cudaSuccess;
+    std::call_once(once, [] {
+        const int lim = max_smem_optin();
+        err = cudaFuncSetAttribute(k_stream<true, kNW>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(k_stream<false, kNW>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    });
+    if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(k_stream)");
+    return FRX_OK;
+}
+
+int check_moe_shape(const char* who, int n, int ff, int K) {
+    if (n < kUnitK || ff < kUnitK || n % kUnitK || ff % kUnitK || n > 8192 || ff > 8192)
+        return fail(FRX_ERR_SHAPE, "%s: n %d and ff %d must be multiples of %d, at most 8192", who, n, ff, kUnitK);
+    if (K < 1 || K > 32) return fail(FRX_ERR_SHAPE, "%s: K %d outside [1, 32]", who, K);
+    return FRX_OK;
+}
+
+}  // namespace
+}  // namespace frx
+
+using namespace frx;
+
+extern "C" {
+
+int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q, float* d) {
+    if (!x || !q || !d) return fail(FRX_ERR_ARG, "frx_quantize_q8: null pointer");
+    if (T < 0 || n < kQ8 || n % kQ8) return fail(FRX_ERR_SHAPE, "frx_quantize_q8: T %d, n %d", T, n);
+    const size_t nblk = size_t(T) * (n / kQ8);
+    if (nblk == 0) return FRX_OK;
+    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr);
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+size_t frx_moe_decode_workspace_bytes(int T, int K, int n, int ff) {
+    if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK) return 0;
+    return make_layout(T, K, n, ff).total;
+}
+
+int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
+                   const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out, float* yslot,
+                   void* ws, size_t ws_bytes, frx_stream_t stream) {
+    if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
+    if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
+    if (int rc = check_moe_shape("frx_moe_decode", n, ff, K)) return rc;
+    if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
+        return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
+    if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_decode: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
+    if (T == 0) return FRX_OK;
+    const Layout L = make_layout(T, K, n, ff);
+    if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_decode: workspace %zu < %zu", ws_bytes, L.total);
+    StreamCfg cfg;
+    if (int rc = stream_cfg(n, ff, cfg)) return rc;
+    if (int rc = set_smem_attr()) return rc;
+    const int sms = sm_count();
+    auto* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + L.status);
+    Item* items = reinterpret_cast<Item*>(base + L.items);
+    int32_t* order = reinterpret_cast<int32_t*>(base + L.order);
+
+    for (int t0 = 0; t0 < T; t0 += kMaxChunkTokens) {
+        const int Tc = T - t0 < kMaxChunkTokens ? T - t0 : kMaxChunkTokens;
+        const float* xc = x + size_t(t0) * n;
+        const int32_t* idc = ids + size_t(t0) * K;
+        const size_t nblk = size_t(Tc) * (n / kQ8);
+        k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xc, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                                reinterpret_cast<float*>(base + L.xd),
+                                                                reinterpret_cast<int32_t*>(base + L.xs));
+        k_group<<<1, 1024, size_t(E) * 8, stream>>>(idc, Tc, K, E, static_cast<const uint8_t*>(experts), stride,
+                                                    static_cast<const uint8_t*>(shared), items, status, order, L.max_items);
+        StreamParams p{};
+        p.items = items;
+        p.status = status;
+        p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
+        p.xd = reinterpret_cast<const float*>(base + L.xd);
+        p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
+        p.h = reinterpret_cast<float*>(base + L.h);
+        p.y = yslot ? yslot + size_t(t0) * K * n : reinterpret_cast<float*>(base + L.y);
+        p.ysh = reinterpret_cast<float*>(base + L.ysh);
+        p.n = n;
+        p.ff = ff;
+        p.K = K;
+        p.TK = Tc * K;
+        p.ring = cfg.ring_gu;
+        k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+        p.ring = cfg.ring_dn;
+        k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
+        k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
+                                                                        shared ? p.ysh : nullptr,
+                                                                        gate_logit ? gate_logit + t0 : nullptr, n, K);
+    }
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+size_t frx_moe_layer_workspace_bytes(int T, int K, int n, int ff) {
+    const size_t d = frx_moe_decode_workspace_bytes(T, K, n, ff);
+    if (!d) return 0;
+    return d + 2 * align_up(size_t(T) * K * 4);
+}
+
+int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
+                  const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out, float* wts_out,
+                  void* ws, size_t ws_bytes, frx_stream_t stream) {
+    if (!logits || !ws) return fail(FRX_ERR_ARG, "frx_moe_layer: null pointer");
+    if (int rc = check_moe_shape("frx_moe_layer", n, ff, K)) return rc;
+    if (T < 0) return fail(FRX_ERR_ARG, "frx_moe_layer: T %d", T);
+    if (T == 0) return FRX_OK;
+    const size_t d = frx_moe_decode_workspace_bytes(T, K, n, ff), r = align_up(size_t(T) * K * 4);
+    if (ws_bytes < d + 2 * r) return fail(FRX_ERR_WORKSPACE, "frx_moe_layer: workspace %zu < %zu", ws_bytes, d + 2 * r);
+    auto* base = static_cast<uint8_t*>(ws);
+    int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
+    float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
+    if (int rc = frx_route_topk(stream, logits, T, E, K, ids, wts, nullptr, nullptr, 1 << 30)) return rc;
+    return frx_moe_decode(experts, stride, E, shared, n, ff, x, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
+}
+
+size_t frx_moe_layer_host_workspace_bytes(int T, int K, int n, int ff, int E) {
+    const size_t l = frx_moe_layer_workspace_bytes(T, K, n, ff);
+    if (!l || E < 1) return 0;
+    return l + align_up(size_t(T) * n * 4) * 2 + align_up(size_t(T) * E * 4) + align_up(size_t(T) * 4);
+}
+
+int frx_moe_layer_host(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x_host,
+                       const float* logits_host, const float* gate_logit_host, int T, int K, float* out_host, void* ws,
+                       size_t ws_bytes, frx_stream_t stream) {
+    if (!x_host || !logits_host || !out_host || !ws) return fail(FRX_ERR_ARG, "frx_moe_layer_host: null pointer");
+    if (int rc = check_moe_shape("frx_moe_layer_host", n, ff, K)) return rc;
+    if (T < 1 || E < 1) return fail(FRX_ERR_ARG, "frx_moe_layer_host: T %d, E %d", T, E);
+    const size_t need = frx_moe_layer_host_workspace_bytes(T, K, n, ff, E);
+    if (ws_bytes < need) return fail(FRX_ERR_WORKSPACE, "frx_moe_layer_host: workspace %zu < %zu", ws_bytes, need);
+    const size_t l = frx_moe_layer_workspace_bytes(T, K, n, ff);
+    auto* base = static_cast<uint8_t*>(ws);
+    float* dx = reinterpret_cast<float*>(base + l);
+    float* dout = reinterpret_cast<float*>(base + l + align_up(size_t(T) * n * 4));
+    float* dlog = reinterpret_cast<float*>(base + l + 2 * align_up(size_t(T) * n * 4));
+    float* dgate = reinterpret_cast<float*>(base + l + 2 * align_up(size_t(T) * n * 4) + align_up(size_t(T) * E * 4));
+    FRX_CUDA(cudaMemcpyAsync(dx, x_host, size_t(T) * n * 4, cudaMemcpyHostToDevice, stream));
+    FRX_CUDA(cudaMemcpyAsync(dlog, logits_host, size_t(T) * E * 4, cudaMemcpyHostToDevice, stream));
+    if (gate_logit_host) FRX_CUDA(cudaMemcpyAsync(dgate, gate_logit_host, size_t(T) * 4, cudaMemcpyHostToDevice, stream));
+    if (int rc = frx_moe_layer(experts, stride, E, shared, n, ff, dx, dlog, gate_logit_host ? dgate : nullptr, T, K, dout, nullptr,
+                               nullptr, ws, l, stream))
+        return rc;
+    FRX_CUDA(cudaMemcpyAsync(out_host, dout, size_t(T) * n * 4, cudaMemcpyDeviceToHost, stream));
+    FRX_CUDA(cudaStreamSynchronize(stream));
+    return FRX_OK;
+}
+
+int frx_workspace_status(const void* ws, frx_stream_t stream) {
+    if (!ws) return fail(FRX_ERR_ARG, "frx_workspace_status: null workspace");
+    int st[4] = {0, 0, 0, 0};
+    FRX_CUDA(cudaMemcpyAsync(st, ws, sizeof st, cudaMemcpyDeviceToHost, stream));
+    FRX_CUDA(cudaStreamSynchronize(stream));
+    if (st[3] != kCookie || st[0] == kDevOk) return FRX_OK;
+    switch (st[0]) {
+        case kDevBadExpertId: return fail(FRX_ERR_DEVICE, "expert id out of range at slot %d", st[2]);
+        case kDevWaitTimeout: return fail(FRX_ERR_DEVICE, "a kernel's wait on a shared-memory barrier ran out");
+        case kDevTooManyItems: return fail(FRX_ERR_DEVICE, "more work items than the workspace holds");
+        default: return fail(FRX_ERR_DEVICE, "device error %d", st[0]);
+    }
+}
+
+int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* hit_n, const float* shexp, const float* gate,
+                    int n, int K, int T, frx_stream_t stream) {
+    if (!out || !yh || !w) return fail(FRX_ERR_ARG, "frx_moe_combine: null pointer");
+    if (n < 1 || K < 1 || T < 0) return fail(FRX_ERR_ARG, "frx_moe_combine: n %d, K %d, T %d", n, K, T);
+    if (T == 0) return FRX_OK;
+    k_combine_hits<<<dim3((n + 255) / 256, T), 256, 0, stream>>>(out, yh, w, hit_n, shexp, gate, n, K);
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what) {
+    if (!what || T < 1 || K < 1 || n < kUnitK || ff < kUnitK) return size_t(-1);
+    const Layout L = make_layout(T, K, n, ff);
+    const struct { const char* name; size_t off; } tab[] = {{"status", L.status}, {"items", L.items}, {"order", L.order}, {"xq", L.xq},
+                                                            {"xd", L.xd}, {"xs", L.xs}, {"h", L.h}, {"y", L.y}, {"ysh", L.ysh}};
+    for (const auto& t : tab)
+        if (!std::strcmp(t.name, what)) return t.off;
+    return size_t(-1);
+}
+
+// ---- moe_hits
+namespace {
+struct HitsLayout {
+    size_t status, items, xq, xd, xs, h, total;
+};
+HitsLayout hits_layout(int K, int n, int ff, int T) {
+    HitsLayout L{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += align_up(bytes);
+        return o;
+    };
+    L.status = take(64);
+    L.items = take(size_t(T) * K * sizeof(Item));
+    L.xq = take(size_t(T) * n);
+    L.xd = take(size_t(T) * (n / kQ8) * 4);
+    L.xs = take(size_t(T) * (n / kQ8) * 4);
+    L.h = take(size_t(T) * K * ff * 4);
+    L.total = off;
+    return L;
+}
+}  // namespace
+
+size_t frx_moe_hits_scratch_bytes(int K, int n, int ff, int T) {
+    if (K < 1 || T < 1 || n < kUnitK || ff < kUnitK) return 0;
+    return hits_layout(K, n, ff, T).total;
+}
+
+int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, const float* x, int n, int ff, void* scratch,
+                 size_t scratch_bytes, float* yh, frx_stream_t stream, int T) {
+    if (!hit_ptr || !hit_n || !x || !scratch || !yh) return fail(FRX_ERR_ARG, "frx_moe_hits: null pointer");
+    if (int rc = check_moe_shape("frx_moe_hits", n, ff, K)) return rc;
+    if (T < 1 || T * K > 1024) return fail(FRX_ERR_SHAPE, "frx_moe_hits: unsupported window T %d x K %d (T * K <= 1024)", T, K);
+    if (uintptr_t(scratch) % kAlign) return fail(FRX_ERR_ARG, "frx_moe_hits: scratch must be 256-byte aligned");
+    const HitsLayout L = hits_layout(K, n, ff, T);
+    if (scratch_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_hits: scratch %zu < %zu", scratch_bytes, L.total);
+    StreamCfg cfg;
+    if (int rc = stream_cfg(n, ff, cfg)) return rc;
+    if (int rc = set_smem_attr()) return rc;
+    auto* base = static_cast<uint8_t*>(scratch);
+    const size_t nblk = size_t(T) * (n / kQ8);
+    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs));
+    k_group_ptr<<<1, 1024, 0, stream>>>(hit_ptr, hit_n, T, K, reinterpret_cast<Item*>(base + L.items), reinterpret_cast<int*>(base + L.status));
+    StreamParams p{};
+    p.items = reinterpret_cast<const Item*>(base + L.items);
+    p.status = reinterpret_cast<int*>(base + L.status);
+    p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
+    p.xd = reinterpret_cast<const float*>(base + L.xd);
+    p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
+    p.h = reinterpret_cast<float*>(base + L.h);
+    p.y = yh;
+    p.ysh = nullptr;
+    p.n = n;
+    p.ff = ff;
+    p.K = K;
+    p.TK = T * K;
+    const int sms = sm_count();
+    p.ring = cfg.ring_gu;
+    k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+    p.ring = cfg.ring_dn;
+    k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+// ---- prefill-sized entry, streaming form: the general grouping feeding the same expert kernel
+namespace {
+struct PfLayout {
+    size_t status, chunk_cnt, bounds, item_off, perm, items, xq, xd, xs, h, total;
+    int n_chunks, max_items;
+};
+PfLayout pf_layout(int T, int K, int n, int ff, int E) {
+    PfLayout L{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += align_up(bytes);
+        return o;
+    };
+    const size_t S = size_t(T) * K;
+    L.n_chunks = int((S + kChunkSlots - 1) / kChunkSlots);
+    L.max_items = int(S / kTokPerItem) + E;
+    L.status = take(64);
+    L.chunk_cnt = take(size_t(L.n_chunks) * E * 4);
+    L.bounds = take(size_t(E + 1) * 4);
+    L.item_off = take(size_t(E + 1) * 4);
+    L.perm = take(S * 4);
+    L.items = take(size_t(L.max_items) * sizeof(Item));
+    L.xq = take(size_t(T) * n);
+    L.xd = take(size_t(T) * (n / kQ8) * 4);
+    L.xs = take(size_t(T) * (n / kQ8) * 4);
+    L.h = take(S * ff * 4);
+    L.total = off;
+    return L;
+}
+}  // namespace
+
+size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E) {
+    if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK || E < 1) return 0;
+    return pf_layout(T, K, n, ff, E).total;
+}
+
+int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                    float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    if (!experts || !x || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
+    if (int rc = check_moe_shape("frx_moe_prefill", n, ff, K)) return rc;
+    if (T < 0 || E < 1 || E > 4096 || size_t(T) * K > (size_t(1) << 30)) return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, E %d", T, E);
+    if ((uintptr_t(experts) | stride) % 16 || uintptr_t(ws) % kAlign)
+        return fail(FRX_ERR_ARG, "frx_moe_prefill: experts and stride must be 16-byte aligned, ws 256-byte aligned");
+    if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_prefill: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
+    if (T == 0) return FRX_OK;
+    const PfLayout L = pf_layout(T, K, n, ff, E);
+    if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_prefill: workspace %zu < %zu", ws_bytes, L.total);
+    StreamCfg cfg;
+    if (int rc = stream_cfg(n, ff, cfg)) return rc;
+    if (int rc = set_smem_attr()) return rc;
+    auto* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + L.status);
+    int* chunk_cnt = reinterpret_cast<int*>(base + L.chunk_cnt);
+    int* bounds = reinterpret_cast<int*>(base + L.bounds);
+    int* item_off = reinterpret_cast<int*>(base + L.item_off);
+    int32_t* perm = reinterpret_cast<int32_t*>(base + L.perm);
+    Item* items = reinterpret_cast<Item*>(base + L.items);
+    const int S = T * K;
+    const size_t nblk = size_t(T) * (n / kQ8);
+    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs));
+    k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status);
+    k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items);
+    k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm);
+    k_pf_items<<<(L.max_items + 255) / 256, 256, 0, stream>>>(bounds, item_off, E, perm, static_cast<const uint8_t*>(experts), stride,
+                                                             status, items);
+    StreamParams p{};
+    p.items = items;
+    p.status = status;
+    p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
+    p.xd = reinterpret_cast<const float*>(base + L.xd);
+    p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
+    p.h = reinterpret_cast<float*>(base + L.h);
+    p.y = yd;
+    p.ysh = nullptr;
+    p.n = n;
+    p.ff = ff;
+    p.K = K;
+    p.TK = S;
+    const int sms = sm_count();
+    p.ring = cfg.ring_gu;
+    k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+    p.ring = cfg.ring_dn;
+    k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+}  // extern "C"

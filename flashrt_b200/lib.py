@@ -1,0 +1,80 @@
+"""ctypes binding of libfrx.so, the C ABI declared in include/frx.h.
+
+There is no fallback: if the library has not been built, importing this module raises, and every
+call that fails raises FrxError with the library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libfrx.so")
+
+OK, ERR_ARG, ERR_SHAPE, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = range(6)
+
+
+class FrxError(RuntimeError):
+    """A libfrx call returned a non-zero status (the reference throws std::runtime_error there)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libfrx error {code}: {message}")
+        self.code = code
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} is missing: build it with `python -m flashrt_b200.build` (needs nvcc); "
+                      "there is no CPU fallback")
+
+lib = C.CDLL(LIB_PATH)
+
+_vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+
+# name -> (restype, argtypes); every symbol include/frx.h declares
+SIGNATURES = {
+    "frx_version": (_i, []),
+    "frx_last_error": (C.c_char_p, []),
+    "frx_q2_mat_bytes": (_sz, [_i, _i]),
+    "frx_q2_expert_bytes": (_sz, [_i, _i]),
+    "frx_q2_expert_stride": (_sz, [_i, _i]),
+    "frx_q2_repack": (_i, [_vp, _i, _i, _vp, _vp]),
+    "frx_q2_tile_experts": (_i, [_vp, _sz, _vp, _sz, _i, _i, _i, _vp]),
+    "frx_q2_untile_experts": (_i, [_vp, _sz, _vp, _sz, _i, _i, _i, _vp]),
+    "frx_q2_dequant_expert": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
+    "frx_arena_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i]),
+    "frx_arena_destroy": (_i, [_vp]),
+    "frx_arena_base": (_vp, [_vp]),
+    "frx_arena_blob": (_vp, [_vp, _i, _i]),
+    "frx_arena_stride": (_sz, [_vp]),
+    "frx_arena_total_bytes": (_sz, [_vp]),
+    "frx_arena_load_planar": (_i, [_vp, _i, _i, _i, _vp, _sz, _vp]),
+    "frx_route_topk": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i]),
+    "frx_quantize_q8": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "frx_moe_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "frx_moe_decode_workspace_offset": (_sz, [_i, _i, _i, _i, C.c_char_p]),
+    "frx_moe_decode": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "frx_moe_layer_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_workspace_status": (_i, [_vp, _vp]),
+    "frx_moe_hits_scratch_bytes": (_sz, [_i, _i, _i, _i]),
+    "frx_moe_hits": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _sz, _vp, _vp, _i]),
+    "frx_moe_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "frx_moe_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "frx_moe_prefill": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)   # AttributeError here means the header and the library disagree
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.frx_last_error().decode()
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise FrxError(rc, last_error())

@@ -1,0 +1,302 @@
+"""Host-side mirror of the reference's operator interface for the Q2_0 MoE expert path.
+
+Function names and argument meanings follow the reference (``moe_route_topk``, ``moe_hits``,
+``moe_q2.run`` / ``workspace_bytes``, ``ExpertArena.blob``, ``q2_0`` helpers); errors surface as
+``FrxError`` where the reference throws ``std::runtime_error``. torch supplies device memory and
+streams only: all compute is in libfrx (hand-written sm_100a kernels), and nothing here runs on
+the CPU instead when the library or the GPU is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import lib as _l
+from .lib import FrxError, check, lib  # noqa: F401
+
+Q2_0_TYPE = 42          # ggml type id (core/formats.hpp:11-18)
+BLOCK, BLOCK_BYTES, Q8_BLOCK = 64, 18, 32
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(stream=None):
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def _dev(*ts):
+    for t in ts:
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
+            raise FrxError(_l.ERR_ARG, "tensors must be contiguous CUDA tensors")
+
+
+# ---- q2_0 storage ------------------------------------------------------------------------------
+
+def mat_bytes(rows: int, cols: int) -> int:
+    return int(lib.frx_q2_mat_bytes(rows, cols))
+
+
+def expert_bytes(n: int, ff: int) -> int:
+    return int(lib.frx_q2_expert_bytes(n, ff))
+
+
+def expert_stride(n: int, ff: int) -> int:
+    return int(lib.frx_q2_expert_stride(n, ff))
+
+
+def repack(ggml_rows: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
+    """q2_0::repack on the device: ggml blocks (uint8) -> planar matrix (uint8)."""
+    _dev(ggml_rows)
+    out = torch.empty(mat_bytes(rows, cols), dtype=torch.uint8, device=ggml_rows.device)
+    check(lib.frx_q2_repack(_ptr(ggml_rows), rows, cols, _ptr(out), _stream(stream)))
+    return out
+
+
+def tile_experts(planar: torch.Tensor, n: int, ff: int, n_experts: int, src_stride: int | None = None,
+                 dst_stride: int | None = None, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """Planar expert blobs -> the tiled layout the kernels read."""
+    _dev(planar, out)
+    src_stride = expert_bytes(n, ff) if src_stride is None else src_stride
+    dst_stride = expert_stride(n, ff) if dst_stride is None else dst_stride
+    if out is None:
+        out = torch.zeros(n_experts * dst_stride, dtype=torch.uint8, device=planar.device)
+    check(lib.frx_q2_tile_experts(_ptr(planar), src_stride, _ptr(out), dst_stride, n_experts, n, ff, _stream(stream)))
+    return out
+
+
+def untile_experts(tiled: torch.Tensor, n: int, ff: int, n_experts: int, src_stride: int | None = None,
+                   dst_stride: int | None = None, stream=None) -> torch.Tensor:
+    _dev(tiled)
+    src_stride = expert_stride(n, ff) if src_stride is None else src_stride
+    dst_stride = expert_bytes(n, ff) if dst_stride is None else dst_stride
+    out = torch.zeros(n_experts * dst_stride, dtype=torch.uint8, device=tiled.device)
+    check(lib.frx_q2_untile_experts(_ptr(tiled), src_stride, _ptr(out), dst_stride, n_experts, n, ff, _stream(stream)))
+    return out
+
+
+def dequant_expert(tiled_blob: torch.Tensor, n: int, ff: int, stream=None):
+    """(q - 1) * d of one tiled expert: gate [ff][n], up [ff][n], down [n][ff] fp32."""
+    _dev(tiled_blob)
+    dev = tiled_blob.device
+    g = torch.empty(ff, n, dtype=torch.float32, device=dev)
+    u = torch.empty(ff, n, dtype=torch.float32, device=dev)
+    d = torch.empty(n, ff, dtype=torch.float32, device=dev)
+    check(lib.frx_q2_dequant_expert(_ptr(tiled_blob), n, ff, _ptr(g), _ptr(u), _ptr(d), _stream(stream)))
+    return g, u, d
+
+
+class ExpertArena:
+    """HBM-resident expert arena: ``blob(layer, expert)`` as core/expert_arena.hpp, on the device."""
+
+    def __init__(self, n_layer: int, n_expert: int, n: int, ff: int):
+        self._h = C.c_void_p()
+        check(lib.frx_arena_create(C.byref(self._h), n_layer, n_expert, n, ff))
+        self.n_layer, self.n_expert, self.n, self.ff = n_layer, n_expert, n, ff
+        self.stride = int(lib.frx_arena_stride(self._h))
+        self.blob_bytes = expert_bytes(n, ff)
+        self.layer_stride = self.stride * n_expert
+
+    def base(self) -> int:
+        return int(lib.frx_arena_base(self._h))
+
+    def blob(self, layer: int, expert: int) -> int:
+        p = lib.frx_arena_blob(self._h, layer, expert)
+        if not p:
+            raise FrxError(_l.ERR_ARG, f"blob({layer}, {expert}) outside the arena")
+        return int(p)
+
+    def total_bytes(self) -> int:
+        return int(lib.frx_arena_total_bytes(self._h))
+
+    def load_planar(self, layer: int, expert0: int, count: int, planar: torch.Tensor, src_stride: int | None = None,
+                    stream=None) -> None:
+        """planar: uint8 tensor (host or device) of `count` planar blobs."""
+        if not planar.is_contiguous():
+            raise FrxError(_l.ERR_ARG, "planar must be contiguous")
+        src_stride = self.blob_bytes if src_stride is None else src_stride
+        check(lib.frx_arena_load_planar(self._h, layer, expert0, count, _ptr(planar), src_stride, _stream(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            lib.frx_arena_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- routing and quantization ------------------------------------------------------------------
+
+def moe_route_topk(logits: torch.Tensor, k: int, counts: torch.Tensor | None = None,
+                   tail_counts: torch.Tensor | None = None, tail_from: int = 1 << 30, stream=None):
+    """qwen4exp::moe_route_topk: ids int32 [T][k] (descending probability, ties to the lower
+    index) and weights float [T][k]."""
+    _dev(logits, counts, tail_counts)
+    T, E = logits.shape
+    ids = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    wts = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    check(lib.frx_route_topk(_stream(stream), _ptr(logits), T, E, k, _ptr(ids), _ptr(wts), _ptr(counts), _ptr(tail_counts),
+                             tail_from))
+    return ids, wts
+
+
+def quantize_q8(x: torch.Tensor, stream=None):
+    """q2_0::quantize_q8 for every row of x [T][n]: codes int8 [T][n], scales float [T][n/32]."""
+    _dev(x)
+    T, n = x.shape
+    q = torch.empty(T, n, dtype=torch.int8, device=x.device)
+    d = torch.empty(T, n // Q8_BLOCK, dtype=torch.float32, device=x.device)
+    check(lib.frx_quantize_q8(_stream(stream), _ptr(x), T, n, _ptr(q), _ptr(d)))
+    return q, d
+
+
+# ---- the layer ---------------------------------------------------------------------------------
+
+def moe_decode_workspace_bytes(T: int, K: int, n: int, ff: int) -> int:
+    return int(lib.frx_moe_decode_workspace_bytes(T, K, n, ff))
+
+
+def moe_layer_workspace_bytes(T: int, K: int, n: int, ff: int) -> int:
+    return int(lib.frx_moe_layer_workspace_bytes(T, K, n, ff))
+
+
+def workspace(nbytes: int, device="cuda") -> torch.Tensor:
+    """A zeroed, 256-byte-aligned device workspace."""
+    return torch.zeros(nbytes + 256, dtype=torch.uint8, device=device)
+
+
+def _ws_ptr(ws: torch.Tensor):
+    p = ws.data_ptr()
+    a = (p + 255) // 256 * 256
+    return C.c_void_p(a), ws.numel() - (a - p)
+
+
+def workspace_status(ws: torch.Tensor, stream=None) -> None:
+    """Raises FrxError if a kernel of a call that used this workspace reported an error."""
+    p, _ = _ws_ptr(ws)
+    check(lib.frx_workspace_status(p, _stream(stream)))
+
+
+def moe_decode(experts: int, stride: int, E: int, shared: int | None, n: int, ff: int, x: torch.Tensor, ids: torch.Tensor,
+               wts: torch.Tensor, gate_logit: torch.Tensor | None, out: torch.Tensor | None = None,
+               yslot: torch.Tensor | None = None, ws: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """out[t] = sum_k w * expert(x_t) (+ shared(x_t) * sigmoid(gate_logit[t])). `experts` and
+    `shared` are device addresses of tiled blobs (ExpertArena.blob)."""
+    _dev(x, ids, wts, gate_logit, out, yslot)
+    T, K = ids.shape
+    if out is None:
+        out = torch.empty(T, n, dtype=torch.float32, device=x.device)
+    if ws is None:
+        ws = workspace(moe_decode_workspace_bytes(T, K, n, ff), x.device)
+    wp, wb = _ws_ptr(ws)
+    check(lib.frx_moe_decode(C.c_void_p(experts), stride, E, C.c_void_p(shared) if shared else None, n, ff, _ptr(x), _ptr(ids),
+                             _ptr(wts), _ptr(gate_logit), T, K, _ptr(out), _ptr(yslot), wp, wb, _stream(stream)))
+    return out
+
+
+def moe_layer(experts: int, stride: int, E: int, shared: int | None, n: int, ff: int, x: torch.Tensor, logits: torch.Tensor,
+              gate_logit: torch.Tensor | None, K: int, out: torch.Tensor | None = None, ids_out: torch.Tensor | None = None,
+              wts_out: torch.Tensor | None = None, ws: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """Router + experts + combine in one call (device tensors)."""
+    _dev(x, logits, gate_logit, out, ids_out, wts_out)
+    T = x.shape[0]
+    if out is None:
+        out = torch.empty(T, n, dtype=torch.float32, device=x.device)
+    if ws is None:
+        ws = workspace(moe_layer_workspace_bytes(T, K, n, ff), x.device)
+    wp, wb = _ws_ptr(ws)
+    check(lib.frx_moe_layer(C.c_void_p(experts), stride, E, C.c_void_p(shared) if shared else None, n, ff, _ptr(x), _ptr(logits),
+                            _ptr(gate_logit), T, K, _ptr(out), _ptr(ids_out), _ptr(wts_out), wp, wb, _stream(stream)))
+    return out
+
+
+def moe_layer_host_workspace_bytes(T: int, K: int, n: int, ff: int, E: int) -> int:
+    return int(lib.frx_moe_layer_host_workspace_bytes(T, K, n, ff, E))
+
+
+def moe_layer_host(experts: int, stride: int, E: int, shared: int | None, n: int, ff: int, x_host: torch.Tensor,
+                   logits_host: torch.Tensor, gate_logit_host: torch.Tensor | None, K: int, out_host: torch.Tensor,
+                   ws: torch.Tensor, stream=None) -> torch.Tensor:
+    """The same with host tensors (pinned for speed): copies in, runs, copies out, synchronises."""
+    for t in (x_host, logits_host, gate_logit_host, out_host):
+        if t is not None and (t.is_cuda or not t.is_contiguous()):
+            raise FrxError(_l.ERR_ARG, "moe_layer_host takes contiguous host tensors")
+    T = x_host.shape[0]
+    wp, wb = _ws_ptr(ws)
+    check(lib.frx_moe_layer_host(C.c_void_p(experts), stride, E, C.c_void_p(shared) if shared else None, n, ff, _ptr(x_host),
+                                 _ptr(logits_host), _ptr(gate_logit_host), T, K, _ptr(out_host), wp, wb, _stream(stream)))
+    return out_host
+
+
+def decode_workspace_view(ws: torch.Tensor, T: int, K: int, n: int, ff: int, what: str) -> torch.Tensor:
+    """A typed view of one buffer inside a moe_decode workspace (tests, debugging)."""
+    off = int(lib.frx_moe_decode_workspace_offset(T, K, n, ff, what.encode()))
+    if off == 2 ** 64 - 1:
+        raise FrxError(_l.ERR_ARG, f"no workspace buffer named {what}")
+    wp, _ = _ws_ptr(ws)
+    start = wp.value - ws.data_ptr() + off
+    shapes = {"xq": (torch.int8, (T, n)), "xd": (torch.float32, (T, n // 32)), "xs": (torch.int32, (T, n // 32)),
+              "h": (torch.float32, (T * K + T, ff)), "y": (torch.float32, (T * K, n)), "ysh": (torch.float32, (T, n)),
+              "order": (torch.int32, (T, K)), "status": (torch.int32, (4,))}
+    dt, shape = shapes[what]
+    count = 1
+    for s in shape:
+        count *= s
+    nbytes = count * torch.empty(0, dtype=dt).element_size()
+    return ws[start:start + nbytes].view(dt).view(shape)
+
+
+def moe_hits_scratch_bytes(K: int, n: int, ff: int, T: int = 1) -> int:
+    return int(lib.frx_moe_hits_scratch_bytes(K, n, ff, T))
+
+
+def moe_hits(hit_ptr: torch.Tensor, hit_n: torch.Tensor, K: int, x: torch.Tensor, n: int, ff: int, yh: torch.Tensor,
+             scratch: torch.Tensor | None = None, T: int = 1, stream=None) -> torch.Tensor:
+    """qwen4exp::moe_hits: hit_ptr int64 [T][K] device addresses of tiled blobs, hit_n int32 [T];
+    yh [T][K][n], rows k >= hit_n[t] are left untouched."""
+    _dev(hit_ptr, hit_n, x, yh, scratch)
+    if scratch is None:
+        scratch = workspace(moe_hits_scratch_bytes(K, n, ff, T), x.device)
+    sp, sb = _ws_ptr(scratch)
+    check(lib.frx_moe_hits(_ptr(hit_ptr), _ptr(hit_n), K, _ptr(x), n, ff, sp, sb, _ptr(yh), _stream(stream), T))
+    return yh
+
+
+def moe_combine(yh: torch.Tensor, w: torch.Tensor, hit_n: torch.Tensor | None, shexp: torch.Tensor | None,
+                gate: torch.Tensor | None, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """k_moe_combine: out[t] = sum_{k < hit_n[t]} w[t][k] * yh[t][k] + shexp[t] * sigmoid(gate[t])."""
+    _dev(yh, w, hit_n, shexp, gate, out)
+    T, K, n = yh.shape
+    if out is None:
+        out = torch.empty(T, n, dtype=torch.float32, device=yh.device)
+    check(lib.frx_moe_combine(_ptr(out), _ptr(yh), _ptr(w), _ptr(hit_n), _ptr(shexp), _ptr(gate), n, K, T, _stream(stream)))
+    return out
+
+
+class moe_q2:
+    """moe_q2::workspace_bytes / moe_q2::run (kernels/cuda/moe_q2.h:21-30)."""
+
+    @staticmethod
+    def workspace_bytes(T: int, K: int, n: int, ff: int, E: int) -> int:
+        return int(lib.frx_moe_prefill_workspace_bytes(T, K, n, ff, E))
+
+    @staticmethod
+    def run(experts: int, stride: int, E: int, n: int, ff: int, x: torch.Tensor, ids: torch.Tensor, yd: torch.Tensor | None = None,
+            ws: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+        """yd[t*K + k] = down(silu(gate x_t) * up x_t) of expert ids[t][k], fp32 [T*K][n]."""
+        _dev(x, ids, yd)
+        T, K = ids.shape
+        if yd is None:
+            yd = torch.empty(T * K, n, dtype=torch.float32, device=x.device)
+        if ws is None:
+            ws = workspace(moe_q2.workspace_bytes(T, K, n, ff, E), x.device)
+        wp, wb = _ws_ptr(ws)
+        check(lib.frx_moe_prefill(C.c_void_p(experts), stride, E, n, ff, _ptr(x), _ptr(ids), T, K, _ptr(yd), wp, wb, _stream(stream)))
+        return yd

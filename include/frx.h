@@ -1,0 +1,186 @@
+/*
+ * libfrx: the Q2_0 MoE expert path of flashrt on B200 (sm_100a), as a C ABI over CUDA.
+ *
+ * The reference has no plugin or FFI layer: the path is reached through C++ free functions that
+ * its MoE blocks call (moe_q2::run, qwen4exp::moe_route_topk, qwen4exp::moe_hits, the combine
+ * kernels). Every entry point here names the reference interface it stands in for; frx_shim.hpp
+ * re-declares those functions with the reference's own signatures on top of this header.
+ *
+ * Conventions (the reference's, arch/qwen4exp/blocks.hpp and kernels/cuda/moe_q2.h):
+ *   - every pointer is a device pointer unless its name ends in _host;
+ *   - row-major, token-major layouts; the caller owns inputs, outputs and workspaces and asks
+ *     the *_bytes functions for sizes; nothing is allocated by a compute call;
+ *   - work is enqueued on the caller's stream, with no host synchronisation;
+ *   - a call returns FRX_OK or an error code and never throws; frx_last_error() gives the text
+ *     of the calling thread's last error.
+ *
+ * Expert weights are Q2_0 (ggml type 42): blocks of 64 weights, one fp16 scale d and 64 two-bit
+ * codes q, a weight being (q - 1) * d. Compute entry points take experts in the *tiled* layout
+ * described at frx_q2_tile_experts, which holds the same 18 bytes per block as the reference's
+ * planar layout, reordered.
+ *
+ * Numerics: activations are quantized to int8 per 32 values exactly as the reference's CPU path
+ * does (quant/q2_0/q2_0.cpp:101-113), the integer dot products are exact, and the float scaling
+ * and summation follow the order of the reference's scalar matvec (quant/q2_0/q2_0.cpp:119-140).
+ */
+#ifndef FRX_H
+#define FRX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* frx_stream_t; /* a cudaStream_t */
+
+enum {
+    FRX_OK = 0,
+    FRX_ERR_ARG = 1,       /* null pointer, negative size, misaligned pointer */
+    FRX_ERR_SHAPE = 2,     /* a shape the kernels do not support */
+    FRX_ERR_WORKSPACE = 3, /* workspace smaller than *_workspace_bytes says */
+    FRX_ERR_CUDA = 4,      /* a CUDA runtime call or launch failed */
+    FRX_ERR_DEVICE = 5     /* a kernel reported an error (bad expert id, a wait that ran out) */
+};
+
+int frx_version(void);
+const char* frx_last_error(void);
+
+/* ---- Q2_0 storage (quant/q2_0/q2_0.hpp:27-56, quant/q2_0/q2_0.cpp:43-71) ---- */
+
+/* q2_0::mat_bytes, q2_0::expert_bytes: rows * (cols / 64) * 18; gate + up + down. */
+size_t frx_q2_mat_bytes(int rows, int cols);
+size_t frx_q2_expert_bytes(int n, int ff);
+/* ExpertArena's stride rule (core/expert_arena.hpp:14-24): the blob rounded up to 4 KiB. */
+size_t frx_q2_expert_stride(int n, int ff);
+
+/* q2_0::repack (quant/q2_0/q2_0.cpp:51-62) on the device: `rows` rows of ggml blocks
+ * {fp16 d; 16 code bytes, element j in byte j/4 at bit 2*(j%4)} to the planar layout
+ * (codes [rows][cols/64][16], element j in byte j%16 at bit 2*(j/16); then scales [rows][cols/64]). */
+int frx_q2_repack(const void* ggml_rows, int rows, int cols, void* planar, frx_stream_t stream);
+
+/* Planar expert blobs (q2_0::expert_view: gate [ff][n], up [ff][n], down [n][ff]) to the tiled
+ * layout the kernels read, and back. Needs n % 128 == 0, ff % 128 == 0. Blob e is read at
+ * src + e * src_stride and written at dst + e * dst_stride; both hold frx_q2_expert_bytes(n, ff).
+ *
+ * Tiled layout. A *unit* is 16 matrix rows ("M rows") by 2 blocks (128 weights of K), 576 bytes:
+ *   bytes [0, 512): for lane L = 0..31 (g = L >> 2, t = L & 3) four 32-bit words [h][j],
+ *                   h, j in {0, 1}: bytes 4t..4t+3 of the planar 16-byte block of M row g + 8h,
+ *                   block 2u + j (so field p of byte i holds element 16p + 4t + i of the block);
+ *   bytes [512, 576): fp16 scales [g][h][j] of the same blocks.
+ * A *group* is the units u = 0..K/128-1 of 16 M rows, back to back. The blob is
+ *   gate/up groups G = 0..ff/8-1: M row m < 8 is gate row 8G + m, M row 8 + m is up row 8G + m,
+ *                                  K = n;
+ *   down groups G = 0..n/16-1:    M row m is down row 16G + m, K = ff.
+ * One lane's 16-byte load of a unit yields the int8 MMA A fragments of two blocks by shifts and a
+ * mask; a group is one contiguous, 64-byte-aligned stream for a bulk copy. */
+int frx_q2_tile_experts(const void* src_planar, size_t src_stride, void* dst_tiled, size_t dst_stride, int n_experts,
+                        int n, int ff, frx_stream_t stream);
+int frx_q2_untile_experts(const void* src_tiled, size_t src_stride, void* dst_planar, size_t dst_stride, int n_experts,
+                          int n, int ff, frx_stream_t stream);
+
+/* Dequantised weights (q - 1) * float(d) of one tiled expert: gate, up [ff][n], down [n][ff]
+ * fp32 (any of the three may be null). The values the reference's tests compute element by
+ * element (tests/test_q2_0.cpp:56-60). */
+int frx_q2_dequant_expert(const void* tiled_blob, int n, int ff, float* gate, float* up, float* down,
+                          frx_stream_t stream);
+
+/* ---- HBM-resident expert arena (replaces core/expert_arena.hpp:14-30, which is host memory) ---- */
+
+typedef struct frx_arena frx_arena;
+/* One device allocation of n_layer * n_expert tiled blobs, blob (l, e) at
+ * base + (l * n_expert + e) * stride, stride = frx_q2_expert_stride(n, ff). */
+int frx_arena_create(frx_arena** out, int n_layer, int n_expert, int n, int ff);
+int frx_arena_destroy(frx_arena* a);
+void* frx_arena_base(const frx_arena* a);
+void* frx_arena_blob(const frx_arena* a, int layer, int expert); /* ExpertArena::blob */
+size_t frx_arena_stride(const frx_arena* a);
+size_t frx_arena_total_bytes(const frx_arena* a);
+/* Copies `count` planar blobs (host or device memory, src_stride apart) into blobs
+ * (layer, expert0 ..) of the arena, converting them to the tiled layout on the way. */
+int frx_arena_load_planar(frx_arena* a, int layer, int expert0, int count, const void* src_planar, size_t src_stride,
+                          frx_stream_t stream);
+
+/* ---- routing: qwen4exp::moe_route_topk (arch/qwen4exp/blocks.hpp:134-135, moe_ref.cu:21-86) ----
+ * Softmax over E <= 1024 logits per token, the k <= 32 most probable experts in descending
+ * probability with ties to the lower index, weights p / max(sum of the selected p, 6.103515625e-5).
+ * ids, wts [T][k]. counts [E] (may be null): each selection adds 1. tail_counts [E] (may be null):
+ * rows t >= tail_from also add 1 there. */
+int frx_route_topk(frx_stream_t stream, const float* logits, int T, int E, int k, int32_t* ids, float* wts,
+                   uint32_t* counts, uint32_t* tail_counts, int tail_from);
+
+/* ---- activation quantizer: q2_0::quantize_q8 (quant/q2_0/q2_0.cpp:101-117) ----
+ * Per 32 values: d = amax / 127, q = roundf(x / d) (half away from zero), d stored after a
+ * round trip through fp16. x [T][n]; q [T][n] int8; d [T][n/32] float. n % 32 == 0. */
+int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q, float* d);
+
+/* ---- decode-sized MoE layer (T tokens, any T; tuned for T <= 64) ----
+ * Stands in for the MoE block of a decode step (arch/qwen4exp/moe_fast.cu:1015-1108 and
+ * arch/qwen4exp/moe_ref.cu:106-190) with every expert resident in device memory:
+ *   out[t] = sum over the token's K experts, in ascending expert id, of wts * expert(x_t)
+ *            (the accumulation order of quant/q2_0/moe_cpu.cpp:70-79)
+ *          + shared(x_t) * sigmoid(gate_logit[t])        (moe_ref.cu:91-97), if shared != null.
+ * experts: tiled blobs at experts + e * stride, e < E. shared: one tiled blob or null.
+ * gate_logit [T] or null (weight 1). ids, wts [T][K] as frx_route_topk writes them.
+ * yslot (may be null): per-slot expert outputs [T*K][n], slot t*K+k, the moe_q2::run / moe_hits
+ * output contract. n % 128 == 0, ff % 128 == 0, K <= 32, n <= 8192, ff <= 8192. */
+size_t frx_moe_decode_workspace_bytes(int T, int K, int n, int ff);
+int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
+                   const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out, float* yslot,
+                   void* ws, size_t ws_bytes, frx_stream_t stream);
+
+/* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging):
+ * "xq" int8 [T][n] and "xd" float [T][n/32] (the Q8 form of x), "h" float [T*K + T][ff] (the
+ * hidden activations silu(gate x) * up x per slot, shared-expert slots last), "y" float [T*K][n],
+ * "ysh" float [T][n], "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
+size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what);
+
+/* Router + layer in one call: logits [T][E] -> top-K -> frx_moe_decode. ids_out / wts_out [T][K]
+ * (may be null) receive the routing. Workspace: frx_moe_layer_workspace_bytes. */
+size_t frx_moe_layer_workspace_bytes(int T, int K, int n, int ff);
+int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
+                  const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out,
+                  float* wts_out, void* ws, size_t ws_bytes, frx_stream_t stream);
+
+/* The same with host buffers: x_host [T][n], logits_host [T][E], gate_logit_host [T] or null are
+ * copied to the device, the layer runs, out_host [T][n] is copied back, and the call returns after
+ * the stream has drained. `ws` is a device workspace of frx_moe_layer_host_workspace_bytes. */
+size_t frx_moe_layer_host_workspace_bytes(int T, int K, int n, int ff, int E);
+int frx_moe_layer_host(const void* experts, size_t stride, int E, const void* shared, int n, int ff,
+                       const float* x_host, const float* logits_host, const float* gate_logit_host, int T, int K,
+                       float* out_host, void* ws, size_t ws_bytes, frx_stream_t stream);
+
+/* After the stream has drained: FRX_OK, or FRX_ERR_DEVICE if a kernel of a call that used this
+ * workspace reported an error (then frx_last_error() says which). */
+int frx_workspace_status(const void* ws, frx_stream_t stream);
+
+/* ---- qwen4exp::moe_hits (arch/qwen4exp/moe_fast.hpp:134-142) ----
+ * yh[t][k] [n] = down_k(silu(gate_k x_t) * up_k x_t) for k < hit_n[t], expert k's tiled blob at
+ * hit_ptr[t*K + k] (device array of device pointers); rows k >= hit_n[t] are not written. An
+ * expert that several tokens of the window hit is read once. x [T][n]; yh [T][K][n]. T*K <= 1024.
+ * Unlike the reference's kernel, activations are quantized per 32 with round-half-away, which is
+ * what the reference's CPU path does. */
+size_t frx_moe_hits_scratch_bytes(int K, int n, int ff, int T);
+int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, const float* x, int n, int ff, void* scratch,
+                 size_t scratch_bytes, float* yh, frx_stream_t stream, int T);
+
+/* ---- combine: k_moe_combine (arch/qwen4exp/moe_fast.cu:499-508), k_stream_combine
+ * (arch/qwen4exp/moe_stream.cu:40-46) ----
+ * out[t] = sum_{k < hit_n[t]} w[t][k] * yh[t][k] (in k order) + shexp[t] * sigmoid(gate[t]).
+ * hit_n null means K for every token; shexp / gate null drop the shared term / use weight 1. */
+int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* hit_n, const float* shexp,
+                    const float* gate, int n, int K, int T, frx_stream_t stream);
+
+/* ---- prefill-sized grouped expert product: moe_q2::run (kernels/cuda/moe_q2.h:21-30) ----
+ * yd[t*K + k] [n] = down(silu(gate x_t) * up x_t) of expert ids[t*K + k], fp32.
+ * Grouping by expert, the tile list and every launch size are computed on the device: no host
+ * synchronisation. n % 128 == 0, ff % 128 == 0, E <= 4096. */
+size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E);
+int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
+                    int K, float* yd, void* ws, size_t ws_bytes, frx_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,62 @@
+"""The C-ABI library loads on a machine without a GPU, exports every symbol include/frx.h
+declares, answers its size queries and rejects bad arguments before touching CUDA. CPU only."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from flashrt_b200 import lib
+    return lib
+
+
+def declared():
+    text = open(os.path.join(ROOT, "include", "frx.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(frx_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(L):
+    names = declared()
+    assert len(names) >= 25
+    for name in names:
+        assert hasattr(L.lib, name), f"{name} declared in frx.h but not exported"
+        assert name in L.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(L.SIGNATURES) == set(names)
+
+
+def test_sizes(L):
+    assert L.lib.frx_q2_mat_bytes(512, 2048) == 294912
+    assert L.lib.frx_q2_expert_bytes(2048, 512) == 884736
+    assert L.lib.frx_q2_expert_bytes(2560, 640) == 1382400      # tests/test_q2_0.cpp:141
+    assert L.lib.frx_q2_expert_stride(2560, 640) == 1384448     # rounded up to 4 KiB
+    assert L.lib.frx_moe_decode_workspace_bytes(64, 10, 2048, 512) > 0
+    assert L.lib.frx_moe_decode_workspace_bytes(0, 10, 2048, 512) == 0
+    assert L.lib.frx_moe_prefill_workspace_bytes(4096, 10, 2048, 512, 512) > 4096 * 10 * 512 * 4
+    assert L.lib.frx_moe_hits_scratch_bytes(10, 2560, 640, 3) > 0
+    assert L.lib.frx_moe_layer_workspace_bytes(8, 10, 2048, 512) > L.lib.frx_moe_decode_workspace_bytes(8, 10, 2048, 512)
+
+
+def test_bad_arguments_are_rejected_with_a_message(L):
+    one = C.c_void_p(256)   # never dereferenced: validation fails first
+    assert L.lib.frx_q2_repack(None, 4, 256, one, None) == L.ERR_ARG
+    assert "null" in L.last_error()
+    assert L.lib.frx_q2_repack(one, 4, 100, one, None) == L.ERR_SHAPE
+    assert L.lib.frx_q2_tile_experts(one, 1 << 20, one, 1 << 20, 1, 2048, 500, None) == L.ERR_SHAPE
+    assert L.lib.frx_route_topk(None, one, 4, 2048, 10, one, one, None, None, 0) == L.ERR_SHAPE
+    assert "unsupported shape" in L.last_error()
+    assert L.lib.frx_route_topk(None, one, 4, 512, 40, one, one, None, None, 0) == L.ERR_SHAPE
+    assert L.lib.frx_quantize_q8(None, one, 4, 48, one, one) == L.ERR_SHAPE
+    assert L.lib.frx_moe_decode(one, 884736, 512, None, 2048, 500, one, one, one, None, 1, 10, one, None, one, 1 << 30, None) == L.ERR_SHAPE
+    assert L.lib.frx_moe_decode(one, 1000, 512, None, 2048, 512, one, one, one, None, 1, 10, one, None, one, 1 << 30, None) == L.ERR_ARG
+    assert L.lib.frx_moe_decode(one, 884736, 512, None, 2048, 512, one, one, one, None, 1, 10, one, None, one, 16, None) == L.ERR_WORKSPACE
+    assert "workspace" in L.last_error()
+    assert L.lib.frx_moe_prefill(one, 884736, 512, 2048, 512, one, one, 8, 10, one, one, 16, None) == L.ERR_WORKSPACE
+    assert L.lib.frx_moe_hits(one, one, 10, one, 2560, 640, one, 1 << 30, one, None, 200) == L.ERR_SHAPE
+    with pytest.raises(L.FrxError):
+        L.check(L.ERR_SHAPE)
