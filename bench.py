@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the Q2_0 MoE layer: tokens/s through one MoE layer and achieved HBM bandwidth.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+Workload (BASELINE.json configs[1]): one MoE layer decode, hidden 2048, 512 experts of
+intermediate 512 plus one shared expert, all Q2_0; router logits fp32 N(0,1), softmax top-10;
+batch B tokens (default 64; --batch 1/4/16 give the other decode batches). A *step* is one pass
+of B tokens through 48 layers with distinct weights, activations and logits (21.8 GB of experts,
+far more than L2, so every layer's weights come from HBM). The value is layer-tokens per second:
+B * 48 / step time.
+
+The JSON line carries: `value` with inputs resident in HBM (the 48 layer calls replayed from one
+CUDA graph); `e2e` through frx_moe_layer_host with pinned host buffers, copies inside the timed
+region; `roofline` of the gate/up streaming kernel from CUDA events around each of its launches;
+`cpu_baseline`, the reference's own CPU path (oracle/_ref, AVX-512 moe_cpu on all physical cores)
+on a bounded sample of the same workload.
+
+With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the experts of every layer
+are sharded over the ranks (expert parallel), activations and routing are replicated, and each
+layer ends in an all-reduce of the [B][2048] partial sums; total work is fixed ("strong").
+
+--impl reference times the reference's CPU implementation alone, on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
+EXPERT_BYTES = 884736
+GU_BYTES = 589824          # gate + up of one expert
+FALLBACK_HBM_GBS = 6650.0
+METRIC = "q2_0_moe_layer_tokens_per_s"
+UNIT = "layer-tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def cpu_moe_setup(oracle, n_layers: int, B: int, seed: int):
+    """Host-side planar experts (E routed + the shared expert as expert E), activations and routing
+    for the CPU legs."""
+    from flashrt_b200 import synth
+    port = oracle.port()
+    rng = np.random.default_rng(seed)
+    planar = synth.planar_experts_random(rng, n_layers * (E + 1), N_MODEL, FF).reshape(n_layers, E + 1, EXPERT_BYTES)
+    x = rng.standard_normal((n_layers, B, N_MODEL), dtype=np.float32)
+    ids = np.empty((n_layers, B, K + 1), np.int32)
+    wts = np.empty((n_layers, B, K + 1), np.float32)
+    for l in range(n_layers):
+        i, w, _ = port.route(rng.standard_normal((B, E), dtype=np.float32), K)
+        gate = rng.standard_normal(B).astype(np.float32)
+        ids[l, :, :K], wts[l, :, :K] = i, w
+        ids[l, :, K] = E                                         # the shared expert: one more entry,
+        wts[l, :, K] = 1.0 / (1.0 + np.exp(-gate))               # weighted by sigmoid(gate)
+    return planar, x, ids, wts
+
+
+def time_cpu(ref, planar, x, ids, wts, workers: int, reps: int) -> float:
+    n_layers, B = x.shape[0], x.shape[1]
+    return ref.moe_cpu_timed(planar, EXPERT_BYTES, (E + 1) * EXPERT_BYTES, n_layers, E + 1, N_MODEL, FF, x, ids, wts, workers, reps)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    ref = oracle.ref()
+    B = args.batch
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libfrx_ref.so was not built (needs the reference tree)"}))
+        return
+    cpu_layers = 3
+    planar, x, ids, wts = cpu_moe_setup(oracle, cpu_layers, B, seed=20260927)
+    workers = max(1, ref.physical_cpus())
+    for _ in range(args.warmup):
+        time_cpu(ref, planar, x, ids, wts, workers, cpu_layers)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        time_cpu(ref, planar, x, ids, wts, workers, cpu_layers)
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    value = B * cpu_layers / (dt / args.steps)
+    sample = f"{cpu_layers} layers x {B} tokens per step (1.36 GB of experts), quantize + entry lists + moe_cpu per layer"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 x 2-bit dot, fp32 scale/accumulate", "data": "synthetic",
+        "config": {"workload": f"configs[1]: one Q2_0 MoE layer decode, batch {B}, hidden 2048, 512 experts + shared, top-10",
+                   "batch": B, "layers_per_step": cpu_layers},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": workers, "kind": "reference", "sample": sample,
+                         "avx512_vnni": ref.have_avx512()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_frx(args):
+    import torch
+    import torch.distributed as dist
+
+    from flashrt_b200 import moe
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, L = args.batch, args.layers
+    e_lo, e_hi = rank * E // world, (rank + 1) * E // world
+    e_local = e_hi - e_lo
+
+    # ---- weights: per layer, this rank's experts plus the shared expert, generated on the device
+    arena = moe.ExpertArena(L, e_local + 1, N_MODEL, FF)
+    gen = torch.Generator(device=dev)
+    nb_gu, nb_dn = FF * (N_MODEL // 64), N_MODEL * (FF // 64)
+
+    def layer_planar(l: int) -> torch.Tensor:
+        """Layer l's E + 1 planar blobs (the same bytes on every rank): uniform codes, scales |N(0, 0.02)|."""
+        gen.manual_seed(20260927 + l)
+        p = torch.randint(0, 256, (E + 1, EXPERT_BYTES), dtype=torch.uint8, device=dev, generator=gen)
+        off = 0
+        for nblk in (nb_gu, nb_gu, nb_dn):
+            d = (torch.randn(E + 1, nblk, device=dev, generator=gen) * 0.02).abs().to(torch.float16)
+            d[d == 0] = 6.103515625e-05
+            p[:, off + nblk * 16:off + nblk * 18] = d.view(torch.uint8).view(E + 1, nblk * 2)
+            off += nblk * 18
+        return p
+
+    keep = {}
+    for l in range(L):
+        p = layer_planar(l)
+        mine = torch.cat([p[e_lo:e_hi], p[E:E + 1]]).contiguous()
+        arena.load_planar(l, 0, e_local + 1, mine.view(-1))
+        if l < 2 and rank == 0:
+            keep[l] = p.cpu().numpy()
+        del p, mine
+    torch.cuda.synchronize()
+
+    gen.manual_seed(7)
+    x = torch.randn(L, B, N_MODEL, device=dev, generator=gen)
+    gen.manual_seed(9)
+    logits = torch.randn(L, B, E, device=dev, generator=gen)
+    gate = torch.randn(L, B, device=dev, generator=gen)
+    out = torch.empty(L, B, N_MODEL, device=dev)
+    ids = torch.empty(L, B, K, dtype=torch.int32, device=dev)
+    wts = torch.empty(L, B, K, device=dev)
+    ws = moe.workspace(moe.moe_layer_workspace_bytes(B, K, N_MODEL, FF), dev)
+
+    def layer_call(l: int):
+        if world == 1:
+            moe.moe_layer(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, x[l], logits[l], gate[l], K,
+                          out=out[l], ids_out=ids[l], wts_out=wts[l], ws=ws)
+        else:
+            from flashrt_b200 import ep
+            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, arena.blob(l, e_local) if rank == 0 else None, N_MODEL, FF,
+                            x[l], logits[l], gate[l], K, out[l], ids[l], wts[l], ws)
+
+    def step():
+        for l in range(L):
+            layer_call(l)
+
+    step()
+    moe.workspace_status(ws)
+    torch.cuda.synchronize()
+    distinct = [int(torch.unique(ids[l]).numel()) for l in range(L)]
+    local_distinct = [int(((torch.unique(ids[l]) >= e_lo) & (torch.unique(ids[l]) < e_hi)).sum()) for l in range(L)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: the 48 layer calls replayed from one CUDA graph (single GPU), inputs resident in HBM
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+    else:
+        run = step
+    for _ in range(args.warmup):
+        run()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    moe.workspace_status(ws)
+    value = B * L / (ms * 1e-3)
+    launches_per_layer = 6 if world == 1 else 7
+
+    # ---- per-kernel device time: CUDA events around every launch, the same K steps without the graph
+    ncls = 7
+    pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
+    moe.check(moe.lib.frx_profile_begin())
+    for _ in range(args.steps):
+        step()
+    moe.check(moe.lib.frx_profile_end(pms, pn, ncls))
+    clocks = sampler.stop() if sampler else None
+    names = [moe.lib.frx_profile_class_name(i).decode() for i in range(ncls)]
+    kernels = {names[i]: {"launches": int(pn[i]), "ms_total": round(float(pms[i]), 4),
+                          "us_per_launch": round(1e3 * float(pms[i]) / max(1, int(pn[i])), 3)} for i in range(ncls) if pn[i]}
+    gu_us = kernels["gate_up"]["us_per_launch"]
+    peak, peak_src = peaks()
+    mean_local = float(np.mean(local_distinct)) + (1.0 if rank == 0 or world == 1 else 0.0)
+    gu_alg_bytes = mean_local * GU_BYTES + B * (N_MODEL + N_MODEL // 32 * 8) + B * (K + 1) * FF * 4
+    achieved = gu_alg_bytes / (gu_us * 1e-6) / 1e9
+    layer_bytes = float(np.mean([(d + 1) * EXPERT_BYTES for d in distinct])) + B * (E * 4 + N_MODEL * 8) + B * K * 8
+    roofline = {"bound": "hbm", "kernel": "k_stream<gate_up>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "peak_source": peak_src, "traffic": None,
+                "algorithmic_bytes_per_launch": int(gu_alg_bytes), "us_per_launch": gu_us,
+                "timing": "CUDA events around each launch, a separate pass of the same steps without the CUDA graph",
+                "layer": {"algorithmic_bytes": int(layer_bytes), "us": round(ms * 1e3 / L, 3),
+                          "achieved_GBps": round(layer_bytes / world / (ms * 1e-3 / L) / 1e9, 1),
+                          "frac_of_peak": round(layer_bytes / world / (ms * 1e-3 / L) / 1e9 / peak, 4)}}
+
+    # ---- e2e: host buffers through frx_moe_layer_host, copies in the timed region (single GPU)
+    e2e = None
+    if world == 1:
+        xh, lh, gh = x.cpu().pin_memory(), logits.cpu().pin_memory(), gate.cpu().pin_memory()
+        oh = torch.empty(L, B, N_MODEL).pin_memory()
+        hws = moe.workspace(moe.moe_layer_host_workspace_bytes(B, K, N_MODEL, FF, E), dev)
+
+        def host_step():
+            for l in range(L):
+                moe.moe_layer_host(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, xh[l], lh[l], gh[l], K, oh[l], hws)
+
+        for _ in range(max(1, args.warmup // 2)):
+            host_step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            host_step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+        assert torch.equal(oh.to(dev), out), "host entry and device entry disagree"
+        e2e = {"value": B * L / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
+               "h2d_bytes_per_step": L * B * (N_MODEL + E + 1) * 4, "d2h_bytes_per_step": L * B * N_MODEL * 4}
+
+    # ---- CPU baseline: the reference's CPU path on a bounded sample (rank 0, single GPU runs only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import oracle
+        ref = oracle.ref()
+        if ref is not None:
+            nl = len(keep)
+            planar = np.stack([keep[l] for l in range(nl)])
+            idh = np.concatenate([ids[:nl].cpu().numpy(), np.full((nl, B, 1), E, np.int32)], axis=2)
+            gsig = torch.sigmoid(gate[:nl]).cpu().numpy()[..., None]
+            wth = np.concatenate([wts[:nl].cpu().numpy(), gsig], axis=2).astype(np.float32)
+            workers = max(1, ref.physical_cpus())
+            xs = x[:nl].cpu().numpy()
+            t1 = time_cpu(ref, planar, xs, idh, wth, workers, nl)
+            reps = int(min(400, max(2 * nl, 12.0 / max(t1, 1e-6))))
+            sec = time_cpu(ref, planar, xs, idh, wth, workers, reps)
+            cpu = {"value": B / sec, "unit": UNIT, "cores": workers, "kind": "reference",
+                   "sample": f"{reps} moe_cpu layer calls over {nl} layers x {B} tokens (same weights, routing and activations "
+                             f"as the GPU run), {sec * 1e3:.3f} ms per layer", "avx512_vnni": ref.have_avx512()}
+            # the GPU result against the reference's CPU result on the same inputs
+            o = ref.moe_cpu(planar[0], EXPERT_BYTES, E + 1, N_MODEL, FF, xs[0], idh[0], wth[0], workers=workers)
+            got = out[0].cpu().numpy()
+            cpu["gpu_vs_cpu_max_err_over_rms"] = float(np.abs(got - o).max() / np.sqrt(np.mean(o.astype(np.float64) ** 2)))
+        else:
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 x 2-bit dot, fp32 scale/accumulate", "data": "synthetic",
+            "config": {"workload": f"configs[1]: one Q2_0 MoE layer decode, batch {B}, hidden 2048, 512 experts + shared, top-10",
+                       "batch": B, "layers_per_step": L, "l2": "inputs larger than L2: 48 distinct layers, 21.8 GB of experts",
+                       "distinct_experts_per_layer_mean": float(np.mean(distinct)), "parallelism": f"ep{world}",
+                       "cuda_graph": use_graph},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_layer * L * args.steps, "kernels": kernels,
+            "roofline": roofline, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="frx", choices=["frx", "reference"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_frx(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -3,7 +3,9 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 #include <new>
+#include <vector>
 
 namespace frx {
 
@@ -37,6 +39,43 @@ int max_smem_optin() {
     return n;
 }
 
+// ---- per-kernel timing
+bool g_profile_on = false;
+namespace {
+struct ProfRec {
+    int cls;
+    cudaEvent_t start, stop;
+};
+std::mutex g_prof_mu;
+std::vector<ProfRec> g_prof;
+std::vector<cudaEvent_t> g_prof_pool;
+cudaEvent_t prof_event() {
+    if (!g_prof_pool.empty()) {
+        cudaEvent_t e = g_prof_pool.back();
+        g_prof_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+}  // namespace
+
+void profile_mark(int cls, cudaStream_t stream, bool start) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    if (start) {
+        ProfRec r{cls, prof_event(), prof_event()};
+        cudaEventRecord(r.start, stream);
+        g_prof.push_back(r);
+    } else {
+        for (size_t i = g_prof.size(); i-- > 0;)
+            if (g_prof[i].cls == cls) {
+                cudaEventRecord(g_prof[i].stop, stream);
+                break;
+            }
+    }
+}
+
 }  // namespace frx
 
 using namespace frx;
@@ -50,6 +89,47 @@ struct frx_arena {
 };
 
 extern "C" {
+
+int frx_profile_begin(void) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    for (auto& r : g_prof) {
+        g_prof_pool.push_back(r.start);
+        g_prof_pool.push_back(r.stop);
+    }
+    g_prof.clear();
+    g_profile_on = true;
+    return FRX_OK;
+}
+
+int frx_profile_end(float* ms, int* launches, int n_classes) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_profile_on = false;
+    if (!ms || !launches || n_classes < 1) return fail(FRX_ERR_ARG, "frx_profile_end: null output");
+    for (int i = 0; i < n_classes; ++i) {
+        ms[i] = 0.0f;
+        launches[i] = 0;
+    }
+    int rc = FRX_OK;
+    for (auto& r : g_prof) {
+        float t = 0.0f;
+        cudaError_t e = cudaEventSynchronize(r.stop);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.start, r.stop);
+        if (e != cudaSuccess) rc = cuda_fail(e, "frx_profile_end");
+        else if (r.cls >= 0 && r.cls < n_classes) {
+            ms[r.cls] += t;
+            ++launches[r.cls];
+        }
+        g_prof_pool.push_back(r.start);
+        g_prof_pool.push_back(r.stop);
+    }
+    g_prof.clear();
+    return rc;
+}
+
+const char* frx_profile_class_name(int cls) {
+    static const char* names[kNumKernelClasses] = {"route_topk", "quant_q8", "group", "gate_up", "down", "combine", "layout"};
+    return cls >= 0 && cls < kNumKernelClasses ? names[cls] : "";
+}
 
 int frx_version(void) { return 1; }
 const char* frx_last_error(void) { return g_err; }

@@ -45,6 +45,18 @@ int cuda_fail(cudaError_t e, const char* what);
 int sm_count();
 int max_smem_optin();
 
+// Optional per-kernel timing (frx_profile_begin / frx_profile_end): when switched on, every
+// launch made through FRX_LAUNCH is bracketed by two CUDA events on its own stream.
+enum KernelClass : int { kKRoute = 0, kKQuant, kKGroup, kKGateUp, kKDown, kKCombine, kKLayout, kNumKernelClasses };
+extern bool g_profile_on;
+void profile_mark(int cls, cudaStream_t stream, bool start);
+#define FRX_LAUNCH(cls, stream, ...)                                   \
+    do {                                                               \
+        if (::frx::g_profile_on) ::frx::profile_mark(cls, stream, true);  \
+        __VA_ARGS__;                                                   \
+        if (::frx::g_profile_on) ::frx::profile_mark(cls, stream, false); \
+    } while (0)
+
 // Device-side error codes written to a workspace's status word.
 enum : int {
     kDevOk = 0,

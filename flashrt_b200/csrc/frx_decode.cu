@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 // the order in which its slots are summed (ascending expert id, the order in which the
 // reference's CPU path adds them, quant/q2_0/moe_cpu.cpp:70-79). One block, no atomics on data:
 // the result does not depend on thread timing.
-__global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids, int T, int K, int E,
+__global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids, int T, int K, int E, int e_lo, int e_hi,
                                                 const uint8_t* __restrict__ experts, size_t stride,
                                                 const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                 int* __restrict__ status, int32_t* __restrict__ order, int max_items) {
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
         if (e < 0 || e >= E) {
             status[0] = kDevBadExpertId;
             status[2] = s;
-        } else {
+        } else if (e >= e_lo && e < e_hi) {   // expert parallel: only the experts held here
             atomicOr(&mask[e], 1ull << (s / K));
         }
     }
@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
         unsigned long long bits = mask[e];
         while (bits) {
             Item it;
-            it.blob = experts + size_t(e) * stride;
+            it.blob = experts + size_t(e - e_lo) * stride;
             it.expert = e;
             int m = 0;
             while (bits && m < kTokPerItem) {
@@ -184,6 +184,10 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
                 --j;
             }
             o[j] = tid * K + k;
+        }
+        for (int k = 0; k < K; ++k) {   // slots of experts held elsewhere take no part in this rank's sum
+            const int e = ids[o[k]];
+            if (e < e_lo || e >= e_hi) o[k] = -1 - o[k];
         }
     }
 }
@@ -451,7 +455,7 @@ __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out
     float acc = 0.0f;
     for (int k = 0; k < K; ++k) {
         const int s = order[t * K + k];
-        acc = __fadd_rn(acc, __fmul_rn(wts[s], y[size_t(s) * n + i]));
+        if (s >= 0) acc = __fadd_rn(acc, __fmul_rn(wts[s], y[size_t(s) * n + i]));
     }
     if (ysh) {
         const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
@@ -707,7 +711,7 @@ int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q
     if (T < 0 || n < kQ8 || n % kQ8) return fail(FRX_ERR_SHAPE, "frx_quantize_q8: T %d, n %d", T, n);
     const size_t nblk = size_t(T) * (n / kQ8);
     if (nblk == 0) return FRX_OK;
-    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr);
+    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
@@ -720,8 +724,15 @@ size_t frx_moe_decode_workspace_bytes(int T, int K, int n, int ff) {
 int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
                    const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out, float* yslot,
                    void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_decode_ep(experts, stride, E, 0, E, shared, n, ff, x, ids, wts, gate_logit, T, K, out, yslot, ws, ws_bytes, stream);
+}
+
+int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
+                      const float* x, const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
+                      float* yslot, void* ws, size_t ws_bytes, frx_stream_t stream) {
     if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
     if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
+    if (e_lo < 0 || e_hi > E || e_lo > e_hi) return fail(FRX_ERR_ARG, "frx_moe_decode: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
     if (int rc = check_moe_shape("frx_moe_decode", n, ff, K)) return rc;
     if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
@@ -743,11 +754,11 @@ int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared
         const float* xc = x + size_t(t0) * n;
         const int32_t* idc = ids + size_t(t0) * K;
         const size_t nblk = size_t(Tc) * (n / kQ8);
-        k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xc, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+        FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xc, nblk, reinterpret_cast<int8_t*>(base + L.xq),
                                                                 reinterpret_cast<float*>(base + L.xd),
-                                                                reinterpret_cast<int32_t*>(base + L.xs));
-        k_group<<<1, 1024, size_t(E) * 8, stream>>>(idc, Tc, K, E, static_cast<const uint8_t*>(experts), stride,
-                                                    static_cast<const uint8_t*>(shared), items, status, order, L.max_items);
+                                                                reinterpret_cast<int32_t*>(base + L.xs)));
+        FRX_LAUNCH(kKGroup, stream, k_group<<<1, 1024, size_t(E) * 8, stream>>>(idc, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
+                                                    static_cast<const uint8_t*>(shared), items, status, order, L.max_items));
         StreamParams p{};
         p.items = items;
         p.status = status;
@@ -762,12 +773,12 @@ int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared
         p.K = K;
         p.TK = Tc * K;
         p.ring = cfg.ring_gu;
-        k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+        FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
         p.ring = cfg.ring_dn;
-        k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
-        k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
+        FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
+        FRX_LAUNCH(kKCombine, stream, k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
                                                                         shared ? p.ysh : nullptr,
-                                                                        gate_logit ? gate_logit + t0 : nullptr, n, K);
+                                                                        gate_logit ? gate_logit + t0 : nullptr, n, K));
     }
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
@@ -845,7 +856,7 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
     if (!out || !yh || !w) return fail(FRX_ERR_ARG, "frx_moe_combine: null pointer");
     if (n < 1 || K < 1 || T < 0) return fail(FRX_ERR_ARG, "frx_moe_combine: n %d, K %d, T %d", n, K, T);
     if (T == 0) return FRX_OK;
-    k_combine_hits<<<dim3((n + 255) / 256, T), 256, 0, stream>>>(out, yh, w, hit_n, shexp, gate, n, K);
+    FRX_LAUNCH(kKCombine, stream, k_combine_hits<<<dim3((n + 255) / 256, T), 256, 0, stream>>>(out, yh, w, hit_n, shexp, gate, n, K));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
@@ -902,9 +913,9 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     if (int rc = set_smem_attr()) return rc;
     auto* base = static_cast<uint8_t*>(scratch);
     const size_t nblk = size_t(T) * (n / kQ8);
-    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
-                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs));
-    k_group_ptr<<<1, 1024, 0, stream>>>(hit_ptr, hit_n, T, K, reinterpret_cast<Item*>(base + L.items), reinterpret_cast<int*>(base + L.status));
+    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs)));
+    FRX_LAUNCH(kKGroup, stream, k_group_ptr<<<1, 1024, 0, stream>>>(hit_ptr, hit_n, T, K, reinterpret_cast<Item*>(base + L.items), reinterpret_cast<int*>(base + L.status)));
     StreamParams p{};
     p.items = reinterpret_cast<const Item*>(base + L.items);
     p.status = reinterpret_cast<int*>(base + L.status);
@@ -920,9 +931,9 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     p.TK = T * K;
     const int sms = sm_count();
     p.ring = cfg.ring_gu;
-    k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+    FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
     p.ring = cfg.ring_dn;
-    k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
+    FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
@@ -987,13 +998,13 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     Item* items = reinterpret_cast<Item*>(base + L.items);
     const int S = T * K;
     const size_t nblk = size_t(T) * (n / kQ8);
-    k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
-                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs));
-    k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status);
-    k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items);
-    k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm);
-    k_pf_items<<<(L.max_items + 255) / 256, 256, 0, stream>>>(bounds, item_off, E, perm, static_cast<const uint8_t*>(experts), stride,
-                                                             status, items);
+    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs)));
+    FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
+    FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items));
+    FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
+    FRX_LAUNCH(kKGroup, stream, k_pf_items<<<(L.max_items + 255) / 256, 256, 0, stream>>>(bounds, item_off, E, perm, static_cast<const uint8_t*>(experts), stride,
+                                                             status, items));
     StreamParams p{};
     p.items = items;
     p.status = status;
@@ -1009,9 +1020,9 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     p.TK = S;
     const int sms = sm_count();
     p.ring = cfg.ring_gu;
-    k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p);
+    FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
     p.ring = cfg.ring_dn;
-    k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p);
+    FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }

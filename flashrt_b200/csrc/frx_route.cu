@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
 #pragma unroll
     for (int i = 0; i < V; ++i) {
         const int e = 32 * i + lane;
-        key[i] = e < E ? order_key(l[e]) : 0u;
+        key[i] = e < E ? order_key(l[e] + 0.0f) : 0u;   // + 0.0f: -0.0 and +0.0 tie, as they do when compared as floats
         if (key[i] > best) {   // ascending index within a lane: the first maximum wins
             best = key[i];
             best_i = e;
@@ -92,11 +92,11 @@ extern "C" int frx_route_topk(frx_stream_t stream, const float* logits, int T, i
     if (T == 0) return FRX_OK;
     const unsigned grid = unsigned((T + 7) / 8);
     if (E <= 128)
-        k_route_topk<4><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from);
+        FRX_LAUNCH(kKRoute, stream, k_route_topk<4><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     else if (E <= 512)
-        k_route_topk<16><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from);
+        FRX_LAUNCH(kKRoute, stream, k_route_topk<16><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     else
-        k_route_topk<32><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from);
+        FRX_LAUNCH(kKRoute, stream, k_route_topk<32><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }

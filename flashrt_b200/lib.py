@@ -34,6 +34,9 @@ _vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
 SIGNATURES = {
     "frx_version": (_i, []),
     "frx_last_error": (C.c_char_p, []),
+    "frx_profile_begin": (_i, []),
+    "frx_profile_end": (_i, [_vp, _vp, _i]),
+    "frx_profile_class_name": (C.c_char_p, [_i]),
     "frx_q2_mat_bytes": (_sz, [_i, _i]),
     "frx_q2_expert_bytes": (_sz, [_i, _i]),
     "frx_q2_expert_stride": (_sz, [_i, _i]),
@@ -53,6 +56,7 @@ SIGNATURES = {
     "frx_moe_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_decode_workspace_offset": (_sz, [_i, _i, _i, _i, C.c_char_p]),
     "frx_moe_decode": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_decode_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -47,6 +47,16 @@ enum {
 int frx_version(void);
 const char* frx_last_error(void);
 
+/* Per-kernel timing for benchmarks; no counterpart in the reference (it profiles with nsys).
+ * Between frx_profile_begin() and frx_profile_end(), every kernel the library launches is bracketed
+ * by two CUDA events on its stream. frx_profile_end waits for them and returns, per kernel class c
+ * (frx_profile_class_name(c): "route_topk", "quant_q8", "group", "gate_up", "down", "combine",
+ * "layout"), the summed device time ms[c] and the launch count launches[c]. Not for use while a
+ * stream is being captured into a CUDA graph. */
+int frx_profile_begin(void);
+int frx_profile_end(float* ms, int* launches, int n_classes);
+const char* frx_profile_class_name(int cls);
+
 /* ---- Q2_0 storage (quant/q2_0/q2_0.hpp:27-56, quant/q2_0/q2_0.cpp:43-71) ---- */
 
 /* q2_0::mat_bytes, q2_0::expert_bytes: rows * (cols / 64) * 18; gate + up + down. */
@@ -129,6 +139,15 @@ size_t frx_moe_decode_workspace_bytes(int T, int K, int n, int ff);
 int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
                    const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out, float* yslot,
                    void* ws, size_t ws_bytes, frx_stream_t stream);
+
+/* Expert-parallel form; no counterpart in the reference, which runs on one GPU. This rank holds
+ * the experts [e_lo, e_hi) of E, expert e at experts + (e - e_lo) * stride; ids still name experts
+ * in [0, E). out[t] is the partial sum over the token's slots whose expert lives here (plus the
+ * shared term if shared != null: give the shared expert to one rank only); the sum of the ranks'
+ * outputs is the layer output. yslot rows of experts held elsewhere are not written. */
+int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
+                      const float* x, const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
+                      float* yslot, void* ws, size_t ws_bytes, frx_stream_t stream);
 
 /* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging):
  * "xq" int8 [T][n] and "xd" float [T][n/32] (the Q8 form of x), "h" float [T*K + T][ff] (the

@@ -171,3 +171,30 @@ def test_combine_in_hit_order(port):
         g = np.float32(1.0) / (np.float32(1.0) + np.exp(-gate[t], dtype=np.float32))
         acc = acc + sh[t] * g
         assert np.abs(out[t] - acc).max() <= 1e-6 * max(1.0, np.abs(acc).max())
+
+
+def test_expert_parallel_partial_sums_add_up(port):
+    # two expert ranges computed one after the other on one GPU (what two ranks would compute):
+    # the partial sums add up to the full layer, and each range writes only its own slots
+    from flashrt_b200 import ep
+    n, ff, E, K, T = 512, 256, 16, 4, 9
+    ex = Experts(port, n, ff, E)
+    x = synth.activations(T, n)
+    ids, wts, _ = port.route(synth.router_logits(T, E), K)
+    gate = np.linspace(-1, 1, T).astype(np.float32)
+    full, ys_full = run_decode(ex, x, ids, wts, gate)
+    total = np.zeros((T, n), np.float32)
+    for rank in range(2):
+        lo, hi = ep.expert_range(rank, 2, E)
+        ws = moe.workspace(moe.moe_decode_workspace_bytes(T, K, n, ff))
+        out = torch.empty(T, n, device="cuda")
+        yslot = torch.full((T * K, n), float("nan"), device="cuda")
+        ep.moe_decode_ep(ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr if rank == 0 else None, n, ff, cuda(x), cuda(ids),
+                         cuda(wts), cuda(gate) if rank == 0 else None, out, ws, yslot=yslot)
+        moe.workspace_status(ws)
+        ys = yslot.cpu().numpy()
+        local = ((ids >= lo) & (ids < hi)).reshape(-1)
+        assert np.array_equal(ys[local], ys_full[local])
+        assert np.all(np.isnan(ys[~local]))
+        total += out.cpu().numpy()
+    assert rel_max(total, full) < 1e-6
