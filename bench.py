@@ -160,6 +160,8 @@ def run_frx(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     B, L = args.batch, args.layers
+    if args.nw:
+        moe.check(moe.lib.frx_debug_set_consumer_warps(args.nw))
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     e_local = e_hi - e_lo
 
@@ -358,6 +360,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

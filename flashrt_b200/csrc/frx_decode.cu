@@ -250,41 +250,53 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t tile_bytes, int
 
 // 16 M rows x kdim of one group against the item's tokens: sums[0..1] = M row g, columns
 // 2*t4 and 2*t4+1; sums[2..3] = M row g + 8, same columns.
+//
+// Per 64-weight block two MMAs, one per 32-value activation block. The 2-bit fields of a code
+// word sit at bits 0, 2, 4, 6 of each byte; the first MMA takes fields 0 and 1 (w and w >> 2
+// masked with 0x03), the second takes fields 2 and 3 *in place* (masked with 0x30, i.e. the
+// codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
+// scale table, which holds d / 16 for the second half, and the accumulator bias table holds
+// kMagicBits - 16 * (sum of the activation codes) there.
 __device__ __forceinline__ void group_mma(const uint8_t* __restrict__ grp, int units, const uint4* __restrict__ bfrag,
-                                          const float4* __restrict__ da, const int4* __restrict__ ci, int lane, float (&sum)[4]) {
+                                          const ulonglong2* __restrict__ da, const int4* __restrict__ ci, int lane, float (&sum)[4]) {
     const int g = lane >> 2, t4 = lane & 3;
-    constexpr uint32_t M = 0x03030303u;
-    sum[0] = sum[1] = sum[2] = sum[3] = 0.0f;
+    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
+    const uint64_t magic2 = pack2(kMagic, kMagic);
+    uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
 #pragma unroll 2
     for (int u = 0; u < units; ++u) {
         const uint4 c = *reinterpret_cast<const uint4*>(grp + u * kUnitBytes + lane * 16);
         const uint2 sc = *reinterpret_cast<const uint2*>(grp + u * kUnitBytes + kUnitCodeBytes + g * 8);
+        const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const uint32_t w0 = j ? c.y : c.x, w1 = j ? c.w : c.z;
+            const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
             const int b = 2 * u + j;
             const uint4 bf = bfrag[b * 32 + lane];
             const int4 c0 = ci[b * 4 + t4];
-            const float4 a = da[b * 4 + t4];
-            int acc0[4] = {c0.x, c0.y, c0.x, c0.y};
-            int acc1[4] = {c0.z, c0.w, c0.z, c0.w};
-            mma_u8s8(acc0, w0 & M, w1 & M, (w0 >> 2) & M, (w1 >> 2) & M, bf.x, bf.y);
-            mma_u8s8(acc1, (w0 >> 4) & M, (w1 >> 4) & M, (w0 >> 6) & M, (w1 >> 6) & M, bf.z, bf.w);
-            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
+            const ulonglong2 a = da[b * 4 + t4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
+            uint64_t lo0, hi0, lo1, hi1;
+            mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, c0.x, c0.y);
+            mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, c0.z, c0.w);
             const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
             const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float a0 = (i & 1) ? a.y : a.x, a1 = (i & 1) ? a.w : a.z;
-                const float s0 = __fsub_rn(__int_as_float(acc0[i]), kMagic);
-                const float s1 = __fsub_rn(__int_as_float(acc1[i]), kMagic);
-                // a0 * s0 and a1 * s1 are exact (11-bit scale x 13-bit integer), so one fused
-                // multiply-add rounds exactly where the reference's two statements round once.
-                const float sumi = __fmaf_rn(a1, s1, __fmul_rn(a0, s0));
-                sum[i] = __fadd_rn(sum[i], __fmul_rn(i < 2 ? d_lo : d_hi, sumi));
-            }
+            // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
+            // multiply-add rounds exactly where the reference's two statements round once.
+            const uint64_t sumi_lo = fma2(a.y, sub2(lo1, magic2), mul2(a.x, sub2(lo0, magic2)));
+            const uint64_t sumi_hi = fma2(a.y, sub2(hi1, magic2), mul2(a.x, sub2(hi0, magic2)));
+            // The weight scale is applied with scalar multiplies: a packed multiply followed by a
+            // packed add is contracted into one fused multiply-add by the assembler, which would
+            // round once where the reference rounds twice.
+            float s0, s1, s2, s3;
+            unpack2(sumi_lo, s0, s1);
+            unpack2(sumi_hi, s2, s3);
+            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
+            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
         }
     }
+    unpack2(acc_lo, sum[0], sum[1]);
+    unpack2(acc_hi, sum[2], sum[3]);
 }
 
 template <bool GATE_UP, int NW>
@@ -322,15 +334,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
         // ---- producer: one lane streams this block's tiles through the ring
         if (lane == 0) {
             int issued = 0;
+            int item = int(lo / tiles_per_expert), tile = int(lo % tiles_per_expert), s = 0, use = 0;
+            const uint8_t* blob = ntiles > 0 ? p.items[item].blob + section : nullptr;
             for (int i = 0; i < ntiles; ++i) {
-                const int s = i % p.ring, use = i / p.ring;
                 if (use > 0 && !mbar_wait_bounded(empty + s, uint32_t(use - 1) & 1u, abort)) break;
-                const long long tau = lo + i;
-                const int item = int(tau / tiles_per_expert), tile = int(tau % tiles_per_expert);
-                const uint8_t* src = p.items[item].blob + section + size_t(tile) * tile_bytes;
                 mbar_expect_tx(full + s, tile_bytes);
-                bulk_g2s(smem + sp.ring + size_t(s) * tile_bytes, src, tile_bytes, full + s);
+                bulk_g2s(smem + sp.ring + size_t(s) * tile_bytes, blob + size_t(tile) * tile_bytes, tile_bytes, full + s);
                 issued = i + 1;
+                if (++s == p.ring) {
+                    s = 0;
+                    ++use;
+                }
+                if (++tile == tiles_per_expert && i + 1 < ntiles) {
+                    tile = 0;
+                    blob = p.items[++item].blob + section;
+                }
             }
             if (*abort) {
                 // Let the copies still in flight land before the block's shared memory is released.
@@ -369,8 +387,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
                     const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
                     const size_t src = size_t(slot_token(it->slot[g], p.K, p.TK)) * (p.n / kQ8) + r;
                     const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-                    daw[dst] = p.xd[src];
-                    ciw[dst] = kMagicBits - p.xs[src];
+                    daw[dst] = s ? p.xd[src] * 0.0625f : p.xd[src];
+                    ciw[dst] = kMagicBits - (s ? 16 * p.xs[src] : p.xs[src]);
                 }
             } else {
                 const int bpt = p.ff / kQ8;   // Q8 blocks per token
@@ -385,8 +403,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
                     bb[((b * 32 + g * 4 + t4) * 4 + s * 2 + hi2) * 4 + (lane & 3)] = int8_t(q8);
                     if (lane == 0) {
                         const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-                        daw[dst] = d;
-                        ciw[dst] = kMagicBits - sm;
+                        daw[dst] = s ? d * 0.0625f : d;
+                        ciw[dst] = kMagicBits - (s ? 16 * sm : sm);
                     }
                 }
             }
@@ -399,13 +417,17 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
             const long long seg_lo = max(lo, (long long)item * tiles_per_expert);
             const long long seg_hi = min(hi, (long long)(item + 1) * tiles_per_expert);
             const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
-            const float4* da = reinterpret_cast<const float4*>(smem + sp.da[buf]);
+            const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da[buf]);
             const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci[buf]);
             const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
             const int m = its->n_tok;
             const int g = lane >> 2, t4 = lane & 3;
             const int c0 = 2 * t4, c1 = 2 * t4 + 1;
-            for (long long tau = seg_lo + warp; tau < seg_hi; tau += NW) {
+            // Tile i of this block always goes to warp i % NW, and the ring size is a multiple of NW,
+            // so every ring slot has one consumer warp, which takes the slot's tiles in order: a
+            // warp never waits on a barrier phase before it has consumed the phase before it.
+            const int i_lo = int(seg_lo - lo), first = i_lo + (warp - i_lo % NW + NW) % NW;
+            for (long long tau = lo + first; tau < seg_hi; tau += NW) {
                 const int i = int(tau - lo), s = i % p.ring, use = i / p.ring;
                 const int tile = int(tau % tiles_per_expert);
                 mbar_wait_bounded(full + s, uint32_t(use) & 1u, abort);
@@ -657,7 +679,8 @@ __global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds
 }
 
 // ---------------------------------------------------------------------------------------------
-constexpr int kNW = 8;
+
+int g_nw = 8;   // consumer warps of k_stream (8, 12 or 16)
 
 struct StreamCfg {
     int ring_gu = 0, ring_dn = 0;
@@ -667,8 +690,9 @@ struct StreamCfg {
 int stream_cfg(int n, int ff, StreamCfg& c) {
     const int budget = max_smem_optin() - 1024;
     if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
+    // the ring holds a whole number of tiles per consumer warp (see k_stream), at most three
     auto fit = [&](int kdim, uint32_t tile_bytes, int& ring, uint32_t& bytes) {
-        for (ring = 24; ring >= 2; --ring) {
+        for (ring = 3 * g_nw; ring >= g_nw; ring -= g_nw) {
             bytes = smem_plan(kdim, tile_bytes, ring).total;
             if (int(bytes) <= budget) return true;
         }
@@ -685,11 +709,35 @@ int set_smem_attr() {
     static cudaError_t err = cudaSuccess;
     std::call_once(once, [] {
         const int lim = max_smem_optin();
-        err = cudaFuncSetAttribute(k_stream<true, kNW>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        if (err == cudaSuccess) err = cudaFuncSetAttribute(k_stream<false, kNW>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        auto set = [&](const void* f) {
+            if (err == cudaSuccess) err = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        };
+        set(reinterpret_cast<const void*>(k_stream<true, 8>));
+        set(reinterpret_cast<const void*>(k_stream<false, 8>));
+        set(reinterpret_cast<const void*>(k_stream<true, 12>));
+        set(reinterpret_cast<const void*>(k_stream<false, 12>));
+        set(reinterpret_cast<const void*>(k_stream<true, 16>));
+        set(reinterpret_cast<const void*>(k_stream<false, 16>));
     });
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(k_stream)");
     return FRX_OK;
+}
+
+// Both halves of the expert FFN over the items of p: gate/up + SwiGLU, then down.
+void launch_stream(StreamParams p, const StreamCfg& cfg, cudaStream_t stream) {
+    const int sms = sm_count();
+    p.ring = cfg.ring_gu;
+    switch (g_nw) {
+        case 16: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 16><<<sms, 17 * 32, cfg.smem_gu, stream>>>(p)); break;
+        case 12: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 12><<<sms, 13 * 32, cfg.smem_gu, stream>>>(p)); break;
+        default: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 8><<<sms, 9 * 32, cfg.smem_gu, stream>>>(p)); break;
+    }
+    p.ring = cfg.ring_dn;
+    switch (g_nw) {
+        case 16: FRX_LAUNCH(kKDown, stream, k_stream<false, 16><<<sms, 17 * 32, cfg.smem_dn, stream>>>(p)); break;
+        case 12: FRX_LAUNCH(kKDown, stream, k_stream<false, 12><<<sms, 13 * 32, cfg.smem_dn, stream>>>(p)); break;
+        default: FRX_LAUNCH(kKDown, stream, k_stream<false, 8><<<sms, 9 * 32, cfg.smem_dn, stream>>>(p)); break;
+    }
 }
 
 int check_moe_shape(const char* who, int n, int ff, int K) {
@@ -707,10 +755,10 @@ using namespace frx;
 extern "C" {
 
 int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q, float* d) {
-    if (!x || !q || !d) return fail(FRX_ERR_ARG, "frx_quantize_q8: null pointer");
     if (T < 0 || n < kQ8 || n % kQ8) return fail(FRX_ERR_SHAPE, "frx_quantize_q8: T %d, n %d", T, n);
+    if (T == 0) return FRX_OK;   // an empty batch: nothing to do, pointers may be null
+    if (!x || !q || !d) return fail(FRX_ERR_ARG, "frx_quantize_q8: null pointer");
     const size_t nblk = size_t(T) * (n / kQ8);
-    if (nblk == 0) return FRX_OK;
     FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
@@ -743,7 +791,6 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
     StreamCfg cfg;
     if (int rc = stream_cfg(n, ff, cfg)) return rc;
     if (int rc = set_smem_attr()) return rc;
-    const int sms = sm_count();
     auto* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + L.status);
     Item* items = reinterpret_cast<Item*>(base + L.items);
@@ -772,10 +819,7 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
         p.ff = ff;
         p.K = K;
         p.TK = Tc * K;
-        p.ring = cfg.ring_gu;
-        FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
-        p.ring = cfg.ring_dn;
-        FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
+        launch_stream(p, cfg, stream);
         FRX_LAUNCH(kKCombine, stream, k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
                                                                         shared ? p.ysh : nullptr,
                                                                         gate_logit ? gate_logit + t0 : nullptr, n, K));
@@ -861,6 +905,13 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
     return FRX_OK;
 }
 
+// Tuning knob for experiments (not part of the public header): consumer warps per block.
+int frx_debug_set_consumer_warps(int nw) {
+    if (nw != 8 && nw != 12 && nw != 16) return FRX_ERR_ARG;
+    g_nw = nw;
+    return FRX_OK;
+}
+
 size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what) {
     if (!what || T < 1 || K < 1 || n < kUnitK || ff < kUnitK) return size_t(-1);
     const Layout L = make_layout(T, K, n, ff);
@@ -929,11 +980,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     p.ff = ff;
     p.K = K;
     p.TK = T * K;
-    const int sms = sm_count();
-    p.ring = cfg.ring_gu;
-    FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
-    p.ring = cfg.ring_dn;
-    FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
+    launch_stream(p, cfg, stream);
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
@@ -1018,11 +1065,7 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     p.ff = ff;
     p.K = K;
     p.TK = S;
-    const int sms = sm_count();
-    p.ring = cfg.ring_gu;
-    FRX_LAUNCH(kKGateUp, stream, k_stream<true, kNW><<<sms, (kNW + 1) * 32, cfg.smem_gu, stream>>>(p));
-    p.ring = cfg.ring_dn;
-    FRX_LAUNCH(kKDown, stream, k_stream<false, kNW><<<sms, (kNW + 1) * 32, cfg.smem_dn, stream>>>(p));
+    launch_stream(p, cfg, stream);
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
