@@ -32,7 +32,7 @@ __host__ __device__ inline int slot_token(int slot, int K, int TK) { return slot
 
 // Workspace status words: [0] device error, [1] items of the current chunk, [2] detail, [3] cookie.
 struct Layout {
-    size_t status, items, order, xq, xd, xs, h, y, ysh, total;
+    size_t status, items, order, xq, xa, xc, h, hq, ha, hc, y, ysh, total;
     int max_items;
 };
 
@@ -50,9 +50,12 @@ Layout make_layout(int T, int K, int n, int ff) {
     L.items = take(size_t(L.max_items) * sizeof(Item));
     L.order = take(size_t(Tc) * K * 4);
     L.xq = take(size_t(Tc) * n);
-    L.xd = take(size_t(Tc) * (n / kQ8) * 4);
-    L.xs = take(size_t(Tc) * (n / kQ8) * 4);
+    L.xa = take(size_t(Tc) * (n / kQ8) * 4);
+    L.xc = take(size_t(Tc) * (n / kQ8) * 4);
     L.h = take(size_t(Tc) * (K + 1) * ff * 4);
+    L.hq = take(size_t(Tc) * (K + 1) * ff);
+    L.ha = take(size_t(Tc) * (K + 1) * (ff / kQ8) * 4);
+    L.hc = take(size_t(Tc) * (K + 1) * (ff / kQ8) * 4);
     L.y = take(size_t(Tc) * K * n * 4);
     L.ysh = take(size_t(Tc) * n * 4);
     L.total = off;
@@ -90,6 +93,32 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
     if (lane == 0) {
         d[blk] = dd;
         if (sums) sums[blk] = ss;
+    }
+}
+
+// Activations in the form the expert kernel consumes, one row per token (x) or per slot (h):
+//   q [row][k]     int8 codes in MMA-B fragment order: the four bytes of element group
+//                  (b, s, hi, t) -- elements 64b + 32s + 16hi + 4t .. +3 -- are word
+//                  (b * 4 + t) * 4 + s * 2 + hi, so lane (g, t) of a warp finds the B fragments of
+//                  block b for its token in one 16-byte load;
+//   a [row][k/32]  the block scale d (through fp16), divided by 16 for the second half of a
+//                  64-block (see group_mma);
+//   c [row][k/32]  the accumulator bias kMagicBits - sum(codes), the sum times 16 for the second half.
+__global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
+                                                    float* __restrict__ a, int32_t* __restrict__ c) {
+    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= n_blocks) return;
+    float d;
+    int sum;
+    const int code = q8_block(x[blk * kQ8 + lane], d, sum);
+    const int bpr = k / kQ8;
+    const size_t row = blk / bpr;
+    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
+    q[row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
+    if (lane == 0) {
+        a[blk] = s ? d * 0.0625f : d;
+        c[blk] = kMagicBits - (s ? 16 * sum : sum);
     }
 }
 
@@ -203,11 +232,11 @@ constexpr int kDownGroups = 4;
 struct StreamParams {
     const Item* items;
     int* status;
-    // activations: GATE_UP reads xq/xd/xs; down reads h
-    const int8_t* xq;
-    const float* xd;
-    const int32_t* xs;
-    float* h;          // [slots][ff]   written by GATE_UP, read by down
+    // activations in k_quant_frag's form: of x (rows = tokens) for GATE_UP, of h (rows = slots) for down
+    const int8_t* aq;
+    const float* aa;
+    const int32_t* ac;
+    float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by GATE_UP
     float* y;          // [T*K][n]      routed slots (down)
     float* ysh;        // [T][n]        shared-expert slots (down)
     int n, ff, K, TK;
@@ -375,38 +404,37 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
             int* ciw = reinterpret_cast<int*>(smem + sp.ci[buf]);
             if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
             const int m = it->n_tok;
-            if (GATE_UP) {
-                const int wpt = nb * 16;   // words per token
-                for (int idx = ctid; idx < m * wpt; idx += NW * 32) {
-                    const int g = idx / wpt, r = idx % wpt;
-                    const int b = r >> 4, s = (r >> 3) & 1, hi2 = (r >> 2) & 1, t4 = r & 3;
-                    const uint32_t v = reinterpret_cast<const uint32_t*>(p.xq + size_t(slot_token(it->slot[g], p.K, p.TK)) * p.n)[r];
-                    bw[(b * 32 + g * 4 + t4) * 4 + s * 2 + hi2] = v;
-                }
-                for (int idx = ctid; idx < m * nb * 2; idx += NW * 32) {
-                    const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
-                    const size_t src = size_t(slot_token(it->slot[g], p.K, p.TK)) * (p.n / kQ8) + r;
-                    const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-                    daw[dst] = s ? p.xd[src] * 0.0625f : p.xd[src];
-                    ciw[dst] = kMagicBits - (s ? 16 * p.xs[src] : p.xs[src]);
-                }
-            } else {
-                const int bpt = p.ff / kQ8;   // Q8 blocks per token
-                int8_t* bb = reinterpret_cast<int8_t*>(bw);
-                for (int idx = warp; idx < m * bpt; idx += NW) {
-                    const int g = idx / bpt, blk = idx % bpt;
-                    const size_t row = size_t(it->slot[g]) * p.ff;
-                    float d;
-                    int sm;
-                    const int q8 = q8_block(p.h[row + blk * kQ8 + lane], d, sm);
-                    const int b = blk >> 1, s = blk & 1, hi2 = lane >> 4, t4 = (lane >> 2) & 3;
-                    bb[((b * 32 + g * 4 + t4) * 4 + s * 2 + hi2) * 4 + (lane & 3)] = int8_t(q8);
-                    if (lane == 0) {
-                        const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-                        daw[dst] = s ? d * 0.0625f : d;
-                        ciw[dst] = kMagicBits - (s ? 16 * sm : sm);
+            // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
+            constexpr int NT = NW * 32;
+            const int vpr = nb * 4;   // 16-byte vectors per row
+            for (int base = ctid; base < m * vpr; base += 4 * NT) {
+                uint4 v[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int idx = base + k * NT;
+                    if (idx < m * vpr) {
+                        const int g = idx / vpr, r = idx % vpr;
+                        const int slot = it->slot[g];
+                        const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
+                        v[k] = reinterpret_cast<const uint4*>(p.aq + row * kdim)[r];
                     }
                 }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int idx = base + k * NT;
+                    if (idx < m * vpr) {
+                        const int g = idx / vpr, r = idx % vpr;
+                        reinterpret_cast<uint4*>(bw)[(r >> 2) * 32 + g * 4 + (r & 3)] = v[k];
+                    }
+                }
+            }
+            for (int idx = ctid; idx < m * nb * 2; idx += NT) {
+                const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
+                const int slot = it->slot[g];
+                const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
+                const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
+                daw[dst] = p.aa[row * (nb * 2) + r];
+                ciw[dst] = p.ac[row * (nb * 2) + r];
             }
         };
 
@@ -723,21 +751,51 @@ int set_smem_attr() {
     return FRX_OK;
 }
 
-// Both halves of the expert FFN over the items of p: gate/up + SwiGLU, then down.
-void launch_stream(StreamParams p, const StreamCfg& cfg, cudaStream_t stream) {
+struct ActBufs {
+    int8_t* q;
+    float* a;
+    int32_t* c;
+};
+
+// The expert FFN over the items of p: quantize x, gate/up + SwiGLU into p.h, quantize the
+// hidden rows, down. x has x_rows rows of p.n values; p.h has h_rows rows of p.ff values.
+// (The grouping kernel that fills p.items may be enqueued before or after the first quantizer.)
+void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaStream_t stream) {
+    const size_t nblk = size_t(x_rows) * (n / kQ8);
+    FRX_LAUNCH(kKQuant, stream, k_quant_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, n, nblk, xb.q, xb.a, xb.c));
+}
+
+void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
     const int sms = sm_count();
     p.ring = cfg.ring_gu;
+    p.aq = xb.q;
+    p.aa = xb.a;
+    p.ac = xb.c;
     switch (g_nw) {
         case 16: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 16><<<sms, 17 * 32, cfg.smem_gu, stream>>>(p)); break;
         case 12: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 12><<<sms, 13 * 32, cfg.smem_gu, stream>>>(p)); break;
         default: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 8><<<sms, 9 * 32, cfg.smem_gu, stream>>>(p)); break;
     }
+    const size_t nblk = h_rows * (p.ff / kQ8);
+    FRX_LAUNCH(kKQuant, stream, k_quant_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(p.h, p.ff, nblk, hb.q, hb.a, hb.c));
     p.ring = cfg.ring_dn;
+    p.aq = hb.q;
+    p.aa = hb.a;
+    p.ac = hb.c;
     switch (g_nw) {
         case 16: FRX_LAUNCH(kKDown, stream, k_stream<false, 16><<<sms, 17 * 32, cfg.smem_dn, stream>>>(p)); break;
         case 12: FRX_LAUNCH(kKDown, stream, k_stream<false, 12><<<sms, 13 * 32, cfg.smem_dn, stream>>>(p)); break;
         default: FRX_LAUNCH(kKDown, stream, k_stream<false, 8><<<sms, 9 * 32, cfg.smem_dn, stream>>>(p)); break;
     }
+}
+
+template <class LayoutT>
+ActBufs act_x(uint8_t* base, const LayoutT& L) {
+    return ActBufs{reinterpret_cast<int8_t*>(base + L.xq), reinterpret_cast<float*>(base + L.xa), reinterpret_cast<int32_t*>(base + L.xc)};
+}
+template <class LayoutT>
+ActBufs act_h(uint8_t* base, const LayoutT& L) {
+    return ActBufs{reinterpret_cast<int8_t*>(base + L.hq), reinterpret_cast<float*>(base + L.ha), reinterpret_cast<int32_t*>(base + L.hc)};
 }
 
 int check_moe_shape(const char* who, int n, int ff, int K) {
@@ -800,18 +858,12 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
         const int Tc = T - t0 < kMaxChunkTokens ? T - t0 : kMaxChunkTokens;
         const float* xc = x + size_t(t0) * n;
         const int32_t* idc = ids + size_t(t0) * K;
-        const size_t nblk = size_t(Tc) * (n / kQ8);
-        FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xc, nblk, reinterpret_cast<int8_t*>(base + L.xq),
-                                                                reinterpret_cast<float*>(base + L.xd),
-                                                                reinterpret_cast<int32_t*>(base + L.xs)));
+        launch_quant_x(xc, Tc, n, act_x(base, L), stream);
         FRX_LAUNCH(kKGroup, stream, k_group<<<1, 1024, size_t(E) * 8, stream>>>(idc, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
                                                     static_cast<const uint8_t*>(shared), items, status, order, L.max_items));
         StreamParams p{};
         p.items = items;
         p.status = status;
-        p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
-        p.xd = reinterpret_cast<const float*>(base + L.xd);
-        p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
         p.h = reinterpret_cast<float*>(base + L.h);
         p.y = yslot ? yslot + size_t(t0) * K * n : reinterpret_cast<float*>(base + L.y);
         p.ysh = reinterpret_cast<float*>(base + L.ysh);
@@ -819,7 +871,7 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
         p.ff = ff;
         p.K = K;
         p.TK = Tc * K;
-        launch_stream(p, cfg, stream);
+        launch_ffn(p, act_x(base, L), act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
         FRX_LAUNCH(kKCombine, stream, k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
                                                                         shared ? p.ysh : nullptr,
                                                                         gate_logit ? gate_logit + t0 : nullptr, n, K));
@@ -916,7 +968,8 @@ size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* 
     if (!what || T < 1 || K < 1 || n < kUnitK || ff < kUnitK) return size_t(-1);
     const Layout L = make_layout(T, K, n, ff);
     const struct { const char* name; size_t off; } tab[] = {{"status", L.status}, {"items", L.items}, {"order", L.order}, {"xq", L.xq},
-                                                            {"xd", L.xd}, {"xs", L.xs}, {"h", L.h}, {"y", L.y}, {"ysh", L.ysh}};
+                                                            {"xa", L.xa}, {"xc", L.xc}, {"h", L.h}, {"hq", L.hq}, {"ha", L.ha}, {"hc", L.hc},
+                                                            {"y", L.y}, {"ysh", L.ysh}};
     for (const auto& t : tab)
         if (!std::strcmp(t.name, what)) return t.off;
     return size_t(-1);
@@ -925,7 +978,7 @@ size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* 
 // ---- moe_hits
 namespace {
 struct HitsLayout {
-    size_t status, items, xq, xd, xs, h, total;
+    size_t status, items, xq, xa, xc, h, hq, ha, hc, total;
 };
 HitsLayout hits_layout(int K, int n, int ff, int T) {
     HitsLayout L{};
@@ -938,9 +991,12 @@ HitsLayout hits_layout(int K, int n, int ff, int T) {
     L.status = take(64);
     L.items = take(size_t(T) * K * sizeof(Item));
     L.xq = take(size_t(T) * n);
-    L.xd = take(size_t(T) * (n / kQ8) * 4);
-    L.xs = take(size_t(T) * (n / kQ8) * 4);
+    L.xa = take(size_t(T) * (n / kQ8) * 4);
+    L.xc = take(size_t(T) * (n / kQ8) * 4);
     L.h = take(size_t(T) * K * ff * 4);
+    L.hq = take(size_t(T) * K * ff);
+    L.ha = take(size_t(T) * K * (ff / kQ8) * 4);
+    L.hc = take(size_t(T) * K * (ff / kQ8) * 4);
     L.total = off;
     return L;
 }
@@ -963,16 +1019,11 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     if (int rc = stream_cfg(n, ff, cfg)) return rc;
     if (int rc = set_smem_attr()) return rc;
     auto* base = static_cast<uint8_t*>(scratch);
-    const size_t nblk = size_t(T) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
-                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs)));
+    launch_quant_x(x, T, n, act_x(base, L), stream);
     FRX_LAUNCH(kKGroup, stream, k_group_ptr<<<1, 1024, 0, stream>>>(hit_ptr, hit_n, T, K, reinterpret_cast<Item*>(base + L.items), reinterpret_cast<int*>(base + L.status)));
     StreamParams p{};
     p.items = reinterpret_cast<const Item*>(base + L.items);
     p.status = reinterpret_cast<int*>(base + L.status);
-    p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
-    p.xd = reinterpret_cast<const float*>(base + L.xd);
-    p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
     p.h = reinterpret_cast<float*>(base + L.h);
     p.y = yh;
     p.ysh = nullptr;
@@ -980,7 +1031,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     p.ff = ff;
     p.K = K;
     p.TK = T * K;
-    launch_stream(p, cfg, stream);
+    launch_ffn(p, act_x(base, L), act_h(base, L), size_t(T) * K, cfg, stream);
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
@@ -988,7 +1039,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
 // ---- prefill-sized entry, streaming form: the general grouping feeding the same expert kernel
 namespace {
 struct PfLayout {
-    size_t status, chunk_cnt, bounds, item_off, perm, items, xq, xd, xs, h, total;
+    size_t status, chunk_cnt, bounds, item_off, perm, items, xq, xa, xc, h, hq, ha, hc, total;
     int n_chunks, max_items;
 };
 PfLayout pf_layout(int T, int K, int n, int ff, int E) {
@@ -1009,9 +1060,12 @@ PfLayout pf_layout(int T, int K, int n, int ff, int E) {
     L.perm = take(S * 4);
     L.items = take(size_t(L.max_items) * sizeof(Item));
     L.xq = take(size_t(T) * n);
-    L.xd = take(size_t(T) * (n / kQ8) * 4);
-    L.xs = take(size_t(T) * (n / kQ8) * 4);
+    L.xa = take(size_t(T) * (n / kQ8) * 4);
+    L.xc = take(size_t(T) * (n / kQ8) * 4);
     L.h = take(S * ff * 4);
+    L.hq = take(S * ff);
+    L.ha = take(S * (ff / kQ8) * 4);
+    L.hc = take(S * (ff / kQ8) * 4);
     L.total = off;
     return L;
 }
@@ -1044,9 +1098,7 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     int32_t* perm = reinterpret_cast<int32_t*>(base + L.perm);
     Item* items = reinterpret_cast<Item*>(base + L.items);
     const int S = T * K;
-    const size_t nblk = size_t(T) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
-                                                            reinterpret_cast<float*>(base + L.xd), reinterpret_cast<int32_t*>(base + L.xs)));
+    launch_quant_x(x, T, n, act_x(base, L), stream);
     FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
     FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items));
     FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
@@ -1055,9 +1107,6 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     StreamParams p{};
     p.items = items;
     p.status = status;
-    p.xq = reinterpret_cast<const int8_t*>(base + L.xq);
-    p.xd = reinterpret_cast<const float*>(base + L.xd);
-    p.xs = reinterpret_cast<const int32_t*>(base + L.xs);
     p.h = reinterpret_cast<float*>(base + L.h);
     p.y = yd;
     p.ysh = nullptr;
@@ -1065,7 +1114,7 @@ int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, co
     p.ff = ff;
     p.K = K;
     p.TK = S;
-    launch_stream(p, cfg, stream);
+    launch_ffn(p, act_x(base, L), act_h(base, L), size_t(S), cfg, stream);
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }

@@ -235,22 +235,46 @@ def moe_layer_host(experts: int, stride: int, E: int, shared: int | None, n: int
     return out_host
 
 
-def decode_workspace_view(ws: torch.Tensor, T: int, K: int, n: int, ff: int, what: str) -> torch.Tensor:
-    """A typed view of one buffer inside a moe_decode workspace (tests, debugging)."""
-    off = int(lib.frx_moe_decode_workspace_offset(T, K, n, ff, what.encode()))
-    if off == 2 ** 64 - 1:
-        raise FrxError(_l.ERR_ARG, f"no workspace buffer named {what}")
+def _raw_view(ws: torch.Tensor, off: int, dt, shape):
     wp, _ = _ws_ptr(ws)
     start = wp.value - ws.data_ptr() + off
-    shapes = {"xq": (torch.int8, (T, n)), "xd": (torch.float32, (T, n // 32)), "xs": (torch.int32, (T, n // 32)),
-              "h": (torch.float32, (T * K + T, ff)), "y": (torch.float32, (T * K, n)), "ysh": (torch.float32, (T, n)),
-              "order": (torch.int32, (T, K)), "status": (torch.int32, (4,))}
-    dt, shape = shapes[what]
     count = 1
     for s in shape:
         count *= s
     nbytes = count * torch.empty(0, dtype=dt).element_size()
     return ws[start:start + nbytes].view(dt).view(shape)
+
+
+def _codes_natural(q: torch.Tensor) -> torch.Tensor:
+    """Fragment-order int8 codes [rows][k] -> element order (inverse of the quantizer's permutation)."""
+    rows, k = q.shape
+    w = q.view(rows, k // 64, 4, 2, 2, 4)          # [row][b][t][s][h][byte]
+    return w.permute(0, 1, 3, 4, 2, 5).reshape(rows, k)   # element 64b + 32s + 16h + 4t + byte
+
+
+def decode_workspace_view(ws: torch.Tensor, T: int, K: int, n: int, ff: int, what: str) -> torch.Tensor:
+    """One buffer of a moe_decode workspace (tests, debugging). "xq"/"xd" and "hq"/"hd" are given
+    in element order with plain block scales, i.e. as q2_0::quantize_q8 would write them."""
+    def off(name):
+        o = int(lib.frx_moe_decode_workspace_offset(T, K, n, ff, name.encode()))
+        if o == 2 ** 64 - 1:
+            raise FrxError(_l.ERR_ARG, f"no workspace buffer named {name}")
+        return o
+    S = T * K + T
+    if what in ("xq", "hq"):
+        rows, k = (T, n) if what == "xq" else (S, ff)
+        return _codes_natural(_raw_view(ws, off(what), torch.int8, (rows, k)))
+    if what in ("xd", "hd"):
+        rows, k = (T, n) if what == "xd" else (S, ff)
+        a = _raw_view(ws, off("xa" if what == "xd" else "ha"), torch.float32, (rows, k // 32)).clone()
+        a[:, 1::2] *= 16.0
+        return a
+    shapes = {"h": (torch.float32, (S, ff)), "y": (torch.float32, (T * K, n)), "ysh": (torch.float32, (T, n)),
+              "order": (torch.int32, (T, K)), "status": (torch.int32, (4,))}
+    if what not in shapes:
+        raise FrxError(_l.ERR_ARG, f"no workspace buffer named {what}")
+    dt, shape = shapes[what]
+    return _raw_view(ws, off(what), dt, shape)
 
 
 def moe_hits_scratch_bytes(K: int, n: int, ff: int, T: int = 1) -> int:

@@ -149,10 +149,14 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
                       const float* x, const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
                       float* yslot, void* ws, size_t ws_bytes, frx_stream_t stream);
 
-/* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging):
- * "xq" int8 [T][n] and "xd" float [T][n/32] (the Q8 form of x), "h" float [T*K + T][ff] (the
- * hidden activations silu(gate x) * up x per slot, shared-expert slots last), "y" float [T*K][n],
- * "ysh" float [T][n], "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
+/* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging).
+ * "xq" int8 [T][n], "xa" float [T][n/32], "xc" int32 [T][n/32]: the Q8 form of x as the expert
+ * kernel reads it -- the four codes of elements 64b + 32s + 16h + 4t .. +3 of a row are word
+ * (b*4 + t)*4 + s*2 + h; xa is the block scale, divided by 16 for odd blocks; xc is
+ * 0x4B400000 - sum(codes), the sum times 16 for odd blocks. "hq", "ha", "hc": the same for the
+ * hidden activations, one row of ff per slot. "h" float [T*K + T][ff]: the hidden activations
+ * silu(gate x) * up x per slot (shared-expert slots last). "y" float [T*K][n], "ysh" float [T][n],
+ * "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
 size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what);
 
 /* Router + layer in one call: logits [T][E] -> top-K -> frx_moe_decode. ids_out / wts_out [T][K]

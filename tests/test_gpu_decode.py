@@ -65,11 +65,14 @@ def test_layer_config_shape(port, T):
     # hidden activations: Q8 codes bit-exact for a sample of slots
     h = moe.decode_workspace_view(ws, T, K, n, ff, "h").cpu().numpy()
     xq, xd = port.quantize_q8(x)
+    hq_gpu = moe.decode_workspace_view(ws, T, K, n, ff, "hq").cpu().numpy()
+    hd_gpu = moe.decode_workspace_view(ws, T, K, n, ff, "hd").cpu().numpy()
+    assert np.array_equal(moe.decode_workspace_view(ws, T, K, n, ff, "xq").cpu().numpy(), xq)
+    assert np.array_equal(moe.decode_workspace_view(ws, T, K, n, ff, "xd").cpu().numpy(), xd)
     for s in list(range(0, T * K, max(1, T * K // 12)))[:12]:
         t = s // K
         _, rh, rhq, rhd = port.expert_ffn(ex.planar[ids[t, s % K]], n, ff, xq[t], xd[t], want_hidden=True)
-        hq, hd = port.quantize_q8(h[s])
-        assert np.array_equal(hq, rhq) and np.array_equal(hd, rhd)
+        assert np.array_equal(hq_gpu[s], rhq) and np.array_equal(hd_gpu[s], rhd)
         assert np.abs(h[s] - rh).max() <= 1e-6 * np.abs(rh).max()
     # the matvec arithmetic is bit-faithful: hidden values differ from the oracle's only where the
     # GPU's exp() and the C library's round differently (a small fraction), and wherever a slot's
