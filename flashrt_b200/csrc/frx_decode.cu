@@ -732,22 +732,21 @@ int stream_cfg(int n, int ff, StreamCfg& c) {
     return FRX_OK;
 }
 
+// The streaming kernels need more dynamic shared memory than the default limit. The attribute
+// belongs to the function on one device, so it is set once per device that calls in.
 int set_smem_attr() {
-    static std::once_flag once;
-    static cudaError_t err = cudaSuccess;
-    std::call_once(once, [] {
-        const int lim = max_smem_optin();
-        auto set = [&](const void* f) {
-            if (err == cudaSuccess) err = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        };
-        set(reinterpret_cast<const void*>(k_stream<true, 8>));
-        set(reinterpret_cast<const void*>(k_stream<false, 8>));
-        set(reinterpret_cast<const void*>(k_stream<true, 12>));
-        set(reinterpret_cast<const void*>(k_stream<false, 12>));
-        set(reinterpret_cast<const void*>(k_stream<true, 16>));
-        set(reinterpret_cast<const void*>(k_stream<false, 16>));
-    });
-    if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(k_stream)");
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    FRX_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev >= 0 && dev < 64 && done[dev]) return FRX_OK;
+    const int lim = max_smem_optin();
+    const void* fns[] = {reinterpret_cast<const void*>(k_stream<true, 8>),  reinterpret_cast<const void*>(k_stream<false, 8>),
+                         reinterpret_cast<const void*>(k_stream<true, 12>), reinterpret_cast<const void*>(k_stream<false, 12>),
+                         reinterpret_cast<const void*>(k_stream<true, 16>), reinterpret_cast<const void*>(k_stream<false, 16>)};
+    for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
 }
 
