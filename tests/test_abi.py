@@ -60,3 +60,25 @@ def test_bad_arguments_are_rejected_with_a_message(L):
     assert L.lib.frx_moe_hits(one, one, 10, one, 2560, 640, one, 1 << 30, one, None, 200) == L.ERR_SHAPE
     with pytest.raises(L.FrxError):
         L.check(L.ERR_SHAPE)
+
+
+def test_cpp_shim_compiles_against_the_header():
+    # include/frx_shim.hpp re-declares the reference's C++ signatures over the C ABI
+    import shutil
+    import subprocess
+    import tempfile
+    gxx = shutil.which("g++")
+    cuda_inc = "/usr/local/cuda/include"
+    if gxx is None or not os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")):
+        pytest.skip("needs g++ and the CUDA headers")
+    src = ('#include "frx_shim.hpp"\n'
+           "void f(cudaStream_t s, const uint8_t* e, const float* x, const int32_t* ids, void* yd, void* ws, int32_t* o, float* w) {\n"
+           "  flashrt::moe_q2::run(e, 884736, 512, 2048, 512, x, ids, 8, 10, yd, ws, flashrt::moe_q2::workspace_bytes(8, 10, 2048, 512, 512), s);\n"
+           "  flashrt::qwen4exp::moe_route_topk(s, x, 8, 512, 10, o, w, nullptr);\n"
+           "  flashrt::qwen4exp::moe_hits(nullptr, ids, 10, x, 2560, 640, ws, w, s, 3);\n}\n")
+    with tempfile.NamedTemporaryFile("w", suffix=".cpp") as f:
+        f.write(src)
+        f.flush()
+        r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-I" + os.path.join(ROOT, "include"), "-I" + cuda_inc, f.name],
+                           capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
