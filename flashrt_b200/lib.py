@@ -56,6 +56,7 @@ SIGNATURES = {
     "frx_moe_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_decode_workspace_offset": (_sz, [_i, _i, _i, _i, C.c_char_p]),
     "frx_moe_decode": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_decode_static": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "frx_moe_decode_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -201,6 +201,17 @@ def moe_decode(experts: int, stride: int, E: int, shared: int | None, n: int, ff
     return out
 
 
+def moe_decode_static(experts: int, stride: int, E: int, shared: int | None, n: int, ff: int, x: torch.Tensor, ids: torch.Tensor,
+                      wts: torch.Tensor, gate_logit: torch.Tensor | None, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """moe_decode for callers that cannot allocate: no workspace argument, the library's built-in
+    4 MiB scratch is used (frx_moe_decode_static). Calls on one device must not overlap."""
+    _dev(x, ids, wts, gate_logit, out)
+    T, K = ids.shape
+    check(lib.frx_moe_decode_static(C.c_void_p(experts), stride, E, C.c_void_p(shared) if shared else None, n, ff, _ptr(x), _ptr(ids),
+                                    _ptr(wts), _ptr(gate_logit), T, K, _ptr(out), _stream(stream)))
+    return out
+
+
 def moe_layer(experts: int, stride: int, E: int, shared: int | None, n: int, ff: int, x: torch.Tensor, logits: torch.Tensor,
               gate_logit: torch.Tensor | None, K: int, out: torch.Tensor | None = None, ids_out: torch.Tensor | None = None,
               wts_out: torch.Tensor | None = None, ws: torch.Tensor | None = None, stream=None) -> torch.Tensor:

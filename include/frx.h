@@ -149,6 +149,26 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
                       const float* x, const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
                       float* yslot, void* ws, size_t ws_bytes, frx_stream_t stream);
 
+/* frx_moe_decode without a caller-supplied workspace, for hosts that cannot allocate device memory
+ * once they are running (an engine that gave all free device memory to its caches at start-up, a
+ * loop that must not call cudaMalloc after initialisation, a plugin host that owns the allocator).
+ * It has no counterpart in the reference. The scratch is a fixed 4 MiB array inside the library's
+ * device image (held by every GPU that loads the library, until the process exits); the call
+ * allocates and frees nothing. Same arguments and result as frx_moe_decode with yslot = null.
+ * Limits and rules:
+ *   - T, K, n, ff must satisfy frx_moe_decode_workspace_bytes(T, K, n, ff) <= 4 MiB (for n = 2048,
+ *     ff = 512, K = 10 that is up to 32 tokens); otherwise FRX_ERR_WORKSPACE, and the message
+ *     gives both sizes;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - all calls on a device share the one array: calls whose kernels can overlap on the GPU (two
+ *     streams, two host threads) race on it, so keep them on one stream or order them;
+ *   - a bad expert id is flagged in the scratch, which this entry gives no way to read: check ids
+ *     with frx_moe_decode + frx_workspace_status while debugging. */
+int frx_moe_decode_static(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
+                          const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
+                          frx_stream_t stream);
+
 /* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging).
  * "xq" int8 [T][n], "xa" float [T][n/32], "xc" int32 [T][n/32]: the Q8 form of x as the expert
  * kernel reads it -- the four codes of elements 64b + 32s + 16h + 4t .. +3 of a row are word
