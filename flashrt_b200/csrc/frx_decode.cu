@@ -223,10 +223,17 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
 
 // ---------------------------------------------------------------------------------------------
 // The streaming expert kernel, used for both halves of the FFN.
-//   GATE_UP: a tile is one gate/up group (8 gate + 8 up rows over K = n); the activations are the
-//            Q8 codes of x; the epilogue is SwiGLU and a float store of the hidden value.
-//   else   : a tile is kDownGroups down groups (16 rows each over K = ff); the activations are
-//            the hidden values, quantized here; the epilogue stores the expert's output rows.
+//   GATE_UP: a task is one gate/up group (8 gate + 8 up rows over K = n); the activations are the
+//            Q8 form of x; the epilogue is SwiGLU and a float store of the hidden value.
+//   else   : a task is kDownGroups down groups (16 rows each over K = ff); the activations are
+//            the Q8 form of the hidden rows; the epilogue stores the expert's output rows.
+// A task is one contiguous byte range of an expert blob. It is fetched as `cpt` equal chunks
+// (two when the task splits evenly, else one), each by one TMA bulk copy into a ring slot.
+// Task i of a block belongs to warp i % NW. Every warp owns `rpw` ring slots and is its own
+// producer: it issues the copy of a later chunk into a slot as soon as it has finished with the
+// chunk that was there, so slots are filled and drained strictly in order (a warp never waits on
+// an mbarrier phase before it has consumed the one before) and no "empty" barriers are needed.
+// While a warp computes on one chunk, its next rpw - 1 chunks are in flight.
 constexpr int kDownGroups = 4;
 
 struct StreamParams {
@@ -240,19 +247,21 @@ struct StreamParams {
     float* y;          // [T*K][n]      routed slots (down)
     float* ysh;        // [T][n]        shared-expert slots (down)
     int n, ff, K, TK;
-    int ring;          // ring slots
+    int cpt;           // chunks per task (1 or 2)
+    int rpw;           // ring slots per consumer warp
 };
 
 // Shared-memory plan of k_stream.
 struct SmemPlan {
     uint32_t ring, bfrag[2], da[2], ci[2], item[2], bars, abort, total;
 };
-__host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t tile_bytes, int ring) {
+__host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, int slots) {
     const uint32_t nb = uint32_t(kdim / kQK);
     SmemPlan s{};
     uint32_t off = 0;
     s.ring = off;
-    off += uint32_t(ring) * tile_bytes;
+    off += uint32_t(slots) * chunk_bytes;
+    off = (off + 127u) & ~127u;
     for (int i = 0; i < 2; ++i) {
         s.bfrag[i] = off;
         off += nb * 512;   // [block][lane] uint4
@@ -270,15 +279,16 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t tile_bytes, int
         off += 64;
     }
     s.bars = off;
-    off += uint32_t(ring) * 16;
+    off += uint32_t(slots) * 16;
     s.abort = off;
     off += 16;
     s.total = off;
     return s;
 }
 
-// 16 M rows x kdim of one group against the item's tokens: sums[0..1] = M row g, columns
-// 2*t4 and 2*t4+1; sums[2..3] = M row g + 8, same columns.
+// `count` units of 16 M rows against the item's tokens, continuing the running sums:
+// acc_lo = {M row g, column 2*t4; M row g, column 2*t4+1}, acc_hi = the same columns of M row g + 8.
+// `units` points at the first unit in shared memory, `b0` is the index of its first 64-block.
 //
 // Per 64-weight block two MMAs, one per 32-value activation block. The 2-bit fields of a code
 // word sit at bits 0, 2, 4, 6 of each byte; the first MMA takes fields 0 and 1 (w and w >> 2
@@ -286,25 +296,32 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t tile_bytes, int
 // codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
 // scale table, which holds d / 16 for the second half, and the accumulator bias table holds
 // kMagicBits - 16 * (sum of the activation codes) there.
-__device__ __forceinline__ void group_mma(const uint8_t* __restrict__ grp, int units, const uint4* __restrict__ bfrag,
-                                          const ulonglong2* __restrict__ da, const int4* __restrict__ ci, int lane, float (&sum)[4]) {
+template <int UPC>   // units per call when known at compile time, else 0
+__device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int count, int b0, const uint4* __restrict__ bfrag,
+                                          const ulonglong2* __restrict__ da, const int4* __restrict__ ci, int lane, uint64_t& acc_lo,
+                                          uint64_t& acc_hi) {
     const int g = lane >> 2, t4 = lane & 3;
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint64_t magic2 = pack2(kMagic, kMagic);
-    uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
-#pragma unroll 2
-    for (int u = 0; u < units; ++u) {
-        const uint4 c = *reinterpret_cast<const uint4*>(grp + u * kUnitBytes + lane * 16);
-        const uint2 sc = *reinterpret_cast<const uint2*>(grp + u * kUnitBytes + kUnitCodeBytes + g * 8);
+    const uint8_t* codes = units + lane * 16;
+    const uint8_t* scales = units + kUnitCodeBytes + g * 8;
+    const uint4* bf_p = bfrag + b0 * 32 + lane;
+    const int4* ci_p = ci + b0 * 4 + t4;
+    const ulonglong2* da_p = da + b0 * 4 + t4;
+    const int n_units = UPC ? UPC : count;
+#pragma unroll(UPC ? UPC : 2)
+    for (int u = 0; u < n_units; ++u) {
+        const uint4 c = *reinterpret_cast<const uint4*>(codes + u * kUnitBytes);
+        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
         const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const uint32_t w0 = j ? c.y : c.x, w1 = j ? c.w : c.z;
             const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
             const int b = 2 * u + j;
-            const uint4 bf = bfrag[b * 32 + lane];
-            const int4 c0 = ci[b * 4 + t4];
-            const ulonglong2 a = da[b * 4 + t4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
+            const uint4 bf = bf_p[b * 32];
+            const int4 c0 = ci_p[b * 4];
+            const ulonglong2 a = da_p[b * 4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
             uint64_t lo0, hi0, lo1, hi1;
             mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, c0.x, c0.y);
             mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, c0.z, c0.w);
@@ -324,153 +341,177 @@ __device__ __forceinline__ void group_mma(const uint8_t* __restrict__ grp, int u
             acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
         }
     }
-    unpack2(acc_lo, sum[0], sum[1]);
-    unpack2(acc_hi, sum[2], sum[3]);
 }
 
-template <bool GATE_UP, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams p) {
+// UPC: units per units_mma call when known at compile time (gate/up: units per chunk; down: units
+// per group), else 0.
+template <bool GATE_UP, int NW, int UPC>
+__global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
     const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
-    const int groups_per_tile = GATE_UP ? 1 : kDownGroups;
-    const uint32_t tile_bytes = group_bytes * groups_per_tile;
-    const int tiles_per_expert = GATE_UP ? p.ff / 8 : p.n / 16 / kDownGroups;
+    const uint32_t task_bytes = GATE_UP ? group_bytes : group_bytes * kDownGroups;
+    const int cpt = p.cpt, rpw = p.rpw;
+    const uint32_t chunk_bytes = task_bytes / uint32_t(cpt);
+    const int tasks_per_expert = GATE_UP ? p.ff / 8 : p.n / 16 / kDownGroups;
     const size_t section = GATE_UP ? 0 : size_t(p.ff / 8) * (size_t(p.n / kUnitK) * kUnitBytes);
-    const SmemPlan sp = smem_plan(kdim, tile_bytes, p.ring);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars);
-    uint64_t* empty = full + p.ring;
+    const int slots = NW * rpw;
+    const SmemPlan sp = smem_plan(kdim, chunk_bytes, slots);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars) + warp * rpw;   // this warp's barriers
+    uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;            // this warp's slots
     volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
 
     const int n_items = p.status[1];
-    const long long total = (long long)n_items * tiles_per_expert;
+    const long long total = (long long)n_items * tasks_per_expert;
     const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    const int ntiles = int(hi - lo);
+    const int ntasks = int(hi - lo);
+    if (ntasks <= 0) return;   // uniform for the block
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.ring; ++s) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, 1);
-        }
+        for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
         *abort = 0;
         mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == NW) {
-        // ---- producer: one lane streams this block's tiles through the ring
-        if (lane == 0) {
-            int issued = 0;
-            int item = int(lo / tiles_per_expert), tile = int(lo % tiles_per_expert), s = 0, use = 0;
-            const uint8_t* blob = ntiles > 0 ? p.items[item].blob + section : nullptr;
-            for (int i = 0; i < ntiles; ++i) {
-                if (use > 0 && !mbar_wait_bounded(empty + s, uint32_t(use - 1) & 1u, abort)) break;
-                mbar_expect_tx(full + s, tile_bytes);
-                bulk_g2s(smem + sp.ring + size_t(s) * tile_bytes, blob + size_t(tile) * tile_bytes, tile_bytes, full + s);
-                issued = i + 1;
-                if (++s == p.ring) {
-                    s = 0;
-                    ++use;
+    // ---- this warp's stream of chunks. Task i of the block (i = warp, warp + NW, ...) is fetched as
+    // cpt chunks; chunk j of the warp goes to its ring slot j % rpw. Lane 0 issues the TMA copies:
+    // the first rpw chunks up front, then chunk j + rpw into the slot that chunk j just left.
+    const int first_item = int(lo / tasks_per_expert), last_item = int((hi - 1) / tasks_per_expert);
+    int is_item = 0, is_task = 0, is_i = warp, is_c = 0, is_slot = 0;   // the next chunk to issue
+    const uint8_t* is_blob = nullptr;
+    if (lane == 0) {
+        const long long tau = lo + warp;
+        is_item = int(tau / tasks_per_expert);
+        is_task = int(tau % tasks_per_expert);
+        if (is_i < ntasks) is_blob = p.items[is_item].blob + section;
+    }
+    auto issue_next = [&]() {   // lane 0 only
+        if (is_i >= ntasks) return;
+        mbar_expect_tx(full + is_slot, chunk_bytes);
+        bulk_g2s(ring + size_t(is_slot) * chunk_bytes, is_blob + size_t(is_task) * task_bytes + size_t(is_c) * chunk_bytes, chunk_bytes,
+                 full + is_slot);
+        if (++is_slot == rpw) is_slot = 0;
+        if (++is_c == cpt) {
+            is_c = 0;
+            is_i += NW;
+            is_task += NW;
+            if (is_i < ntasks && is_task >= tasks_per_expert) {
+                while (is_task >= tasks_per_expert) {
+                    is_task -= tasks_per_expert;
+                    ++is_item;
                 }
-                if (++tile == tiles_per_expert && i + 1 < ntiles) {
-                    tile = 0;
-                    blob = p.items[++item].blob + section;
-                }
-            }
-            if (*abort) {
-                // Let the copies still in flight land before the block's shared memory is released.
-                const int first = issued > p.ring ? issued - p.ring : 0;
-                for (int i = first; i < issued; ++i) {
-                    const uint64_t t0 = global_ns();
-                    while (!mbar_try_wait(full + i % p.ring, uint32_t(i / p.ring) & 1u) && global_ns() - t0 < kWaitLimitNs) {
-                    }
-                }
-                p.status[0] = kDevWaitTimeout;
+                is_blob = p.items[is_item].blob + section;
             }
         }
-    } else if (ntiles > 0) {
-        // ---- consumers: segments of consecutive tiles that belong to one item
-        const int first_item = int(lo / tiles_per_expert), last_item = int((hi - 1) / tiles_per_expert);
-        const int nseg = last_item - first_item + 1;
-        const int ctid = threadIdx.x;   // 0 .. NW*32-1
+    };
+    if (lane == 0)
+        for (int k = 0; k < rpw; ++k) issue_next();
+    int cs_slot = 0;
+    uint32_t cs_phase = 0;   // the chunk being consumed: its slot and that slot's barrier phase
+    auto chunk_wait = [&]() -> const uint8_t* {
+        mbar_wait_bounded(full + cs_slot, cs_phase, abort);
+        return ring + size_t(cs_slot) * chunk_bytes;
+    };
+    auto chunk_done = [&]() {
+        __syncwarp();
+        if (lane == 0) issue_next();   // refills the slot this chunk just left
+        if (++cs_slot == rpw) {
+            cs_slot = 0;
+            cs_phase ^= 1u;
+        }
+    };
 
-        auto build = [&](int q) {
-            const Item* it = p.items + first_item + q;
-            const int buf = q & 1;
-            uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag[buf]);
-            float* daw = reinterpret_cast<float*>(smem + sp.da[buf]);
-            int* ciw = reinterpret_cast<int*>(smem + sp.ci[buf]);
-            if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
-            const int m = it->n_tok;
-            // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
-            constexpr int NT = NW * 32;
-            const int vpr = nb * 4;   // 16-byte vectors per row
-            for (int base = ctid; base < m * vpr; base += 4 * NT) {
-                uint4 v[4];
+    // ---- segments of consecutive tasks that belong to one item
+    const int nseg = last_item - first_item + 1;
+    const int ctid = threadIdx.x;
+
+    auto build = [&](int q) {
+        const Item* it = p.items + first_item + q;
+        const int buf = q & 1;
+        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag[buf]);
+        float* daw = reinterpret_cast<float*>(smem + sp.da[buf]);
+        int* ciw = reinterpret_cast<int*>(smem + sp.ci[buf]);
+        if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
+        const int m = it->n_tok;
+        // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
+        constexpr int NT = NW * 32;
+        const int vpr = nb * 4;   // 16-byte vectors per row
+        for (int base = ctid; base < m * vpr; base += 4 * NT) {
+            uint4 v[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int idx = base + k * NT;
-                    if (idx < m * vpr) {
-                        const int g = idx / vpr, r = idx % vpr;
-                        const int slot = it->slot[g];
-                        const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
-                        v[k] = reinterpret_cast<const uint4*>(p.aq + row * kdim)[r];
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int idx = base + k * NT;
-                    if (idx < m * vpr) {
-                        const int g = idx / vpr, r = idx % vpr;
-                        reinterpret_cast<uint4*>(bw)[(r >> 2) * 32 + g * 4 + (r & 3)] = v[k];
-                    }
+            for (int k = 0; k < 4; ++k) {
+                const int idx = base + k * NT;
+                if (idx < m * vpr) {
+                    const int g = idx / vpr, r = idx % vpr;
+                    const int slot = it->slot[g];
+                    const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
+                    v[k] = reinterpret_cast<const uint4*>(p.aq + row * kdim)[r];
                 }
             }
-            for (int idx = ctid; idx < m * nb * 2; idx += NT) {
-                const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
-                const int slot = it->slot[g];
-                const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
-                const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-                daw[dst] = p.aa[row * (nb * 2) + r];
-                ciw[dst] = p.ac[row * (nb * 2) + r];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = base + k * NT;
+                if (idx < m * vpr) {
+                    const int g = idx / vpr, r = idx % vpr;
+                    reinterpret_cast<uint4*>(bw)[(r >> 2) * 32 + g * 4 + (r & 3)] = v[k];
+                }
             }
-        };
+        }
+        for (int idx = ctid; idx < m * nb * 2; idx += NT) {
+            const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
+            const int slot = it->slot[g];
+            const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
+            const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
+            daw[dst] = p.aa[row * (nb * 2) + r];
+            ciw[dst] = p.ac[row * (nb * 2) + r];
+        }
+    };
 
-        build(0);
-        named_bar_sync(1, NW * 32);
-        for (int q = 0; q < nseg; ++q) {
-            const int item = first_item + q, buf = q & 1;
-            const long long seg_lo = max(lo, (long long)item * tiles_per_expert);
-            const long long seg_hi = min(hi, (long long)(item + 1) * tiles_per_expert);
-            const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
-            const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da[buf]);
-            const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci[buf]);
-            const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
-            const int m = its->n_tok;
-            const int g = lane >> 2, t4 = lane & 3;
-            const int c0 = 2 * t4, c1 = 2 * t4 + 1;
-            // Tile i of this block always goes to warp i % NW, and the ring size is a multiple of NW,
-            // so every ring slot has one consumer warp, which takes the slot's tiles in order: a
-            // warp never waits on a barrier phase before it has consumed the phase before it.
-            const int i_lo = int(seg_lo - lo), first = i_lo + (warp - i_lo % NW + NW) % NW;
-            for (long long tau = lo + first; tau < seg_hi; tau += NW) {
-                const int i = int(tau - lo), s = i % p.ring, use = i / p.ring;
-                const int tile = int(tau % tiles_per_expert);
-                mbar_wait_bounded(full + s, uint32_t(use) & 1u, abort);
-                const uint8_t* tp = smem + sp.ring + size_t(s) * tile_bytes;
+    build(0);
+    __syncthreads();
+    for (int q = 0; q < nseg; ++q) {
+        const int item = first_item + q, buf = q & 1;
+        const long long seg_lo = max(lo, (long long)item * tasks_per_expert);
+        const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
+        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
+        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da[buf]);
+        const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci[buf]);
+        const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
+        const int m = its->n_tok;
+        const int g = lane >> 2, t4 = lane & 3;
+        const int c0 = 2 * t4, c1 = 2 * t4 + 1;
+        const int i_lo = int(seg_lo - lo), first = i_lo + (warp - i_lo % NW + NW) % NW;
+        for (long long tau = lo + first; tau < seg_hi; tau += NW) {
+            const int task = int(tau % tasks_per_expert);
+            if (GATE_UP) {
+                uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
+                const int upc = units / cpt;
+                for (int c = 0; c < cpt; ++c) {
+                    const uint8_t* cp = chunk_wait();
+                    units_mma<UPC>(cp, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
+                    chunk_done();
+                }
                 float sum[4];
-                if (GATE_UP) {
-                    group_mma(tp, units, bfrag, da, ci, lane, sum);
-                    const int row = tile * 8 + g;
-                    if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
-                    if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
-                } else {
+                unpack2(acc_lo, sum[0], sum[1]);
+                unpack2(acc_hi, sum[2], sum[3]);
+                const int row = task * 8 + g;
+                if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
+                if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
+            } else {
+                const int gpc = kDownGroups / cpt;   // groups per chunk
+                for (int c = 0; c < cpt; ++c) {
+                    const uint8_t* cp = chunk_wait();
 #pragma unroll 1
-                    for (int gd = 0; gd < kDownGroups; ++gd) {
-                        group_mma(tp + size_t(gd) * group_bytes, units, bfrag, da, ci, lane, sum);
-                        const int row = (tile * kDownGroups + gd) * 16 + g;
+                    for (int gd = 0; gd < gpc; ++gd) {
+                        uint64_t acc_lo = 0ull, acc_hi = 0ull;
+                        units_mma<UPC>(cp + size_t(gd) * group_bytes, units, 0, bfrag, da, ci, lane, acc_lo, acc_hi);
+                        float sum[4];
+                        unpack2(acc_lo, sum[0], sum[1]);
+                        unpack2(acc_hi, sum[2], sum[3]);
+                        const int row = ((task * cpt + c) * gpc + gd) * 16 + g;
                         if (c0 < m) {
                             const int sl = its->slot[c0];
                             float* o = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
@@ -484,16 +525,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) k_stream(const StreamParams 
                             o[row + 8] = sum[3];
                         }
                     }
+                    chunk_done();
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty + s);
             }
-            if (q + 1 < nseg) build(q + 1);
-            named_bar_sync(1, NW * 32);
+        }
+        if (q + 1 < nseg) build(q + 1);
+        __syncthreads();
+    }
+    if (*abort) {
+        // A wait ran out: report it, and give copies still in flight time to land before the
+        // block's shared memory is released.
+        if (threadIdx.x == 0) p.status[0] = kDevWaitTimeout;
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) {
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0 && *abort) p.status[0] = kDevWaitTimeout;
 }
 
 // out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate)
@@ -708,28 +754,57 @@ __global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds
 
 // ---------------------------------------------------------------------------------------------
 
-int g_nw = 8;   // consumer warps of k_stream (8, 12 or 16)
+int g_nw = 16;   // consumer warps of k_stream (8, 12 or 16)
 
 struct StreamCfg {
-    int ring_gu = 0, ring_dn = 0;
+    int nw_gu = 8, nw_dn = 8;     // warps per block
+    int cpt_gu = 1, cpt_dn = 1;   // chunks per task
+    int rpw_gu = 2, rpw_dn = 2;   // ring slots per warp
     uint32_t smem_gu = 0, smem_dn = 0;
 };
 
 int stream_cfg(int n, int ff, StreamCfg& c) {
     const int budget = max_smem_optin() - 1024;
     if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
-    // the ring holds a whole number of tiles per consumer warp (see k_stream), at most three
-    auto fit = [&](int kdim, uint32_t tile_bytes, int& ring, uint32_t& bytes) {
-        for (ring = 3 * g_nw; ring >= g_nw; ring -= g_nw) {
-            bytes = smem_plan(kdim, tile_bytes, ring).total;
-            if (int(bytes) <= budget) return true;
+    // a task is fetched as two chunks when it splits evenly; the preferred warp count is kept if
+    // every warp can have at least two ring slots (up to four), else fewer warps are used
+    auto fit = [&](int kdim, uint32_t task_bytes, bool even, int& nw, int& cpt, int& rpw, uint32_t& bytes) {
+        cpt = even ? 2 : 1;
+        const uint32_t chunk = task_bytes / uint32_t(cpt);
+        const int prefs[3] = {g_nw, g_nw > 12 ? 12 : 8, 8};
+        for (int k = 0; k < 3; ++k) {
+            nw = prefs[k];
+            for (rpw = 4; rpw >= 2; --rpw) {
+                bytes = smem_plan(kdim, chunk, nw * rpw).total;
+                if (int(bytes) <= budget) return true;
+            }
         }
         return false;
     };
-    if (!fit(n, uint32_t(n / kUnitK) * kUnitBytes, c.ring_gu, c.smem_gu) ||
-        !fit(ff, uint32_t(ff / kUnitK) * kUnitBytes * kDownGroups, c.ring_dn, c.smem_dn))
+    const int gu_units = n / kUnitK, dn_units = ff / kUnitK;
+    if (!fit(n, uint32_t(gu_units) * kUnitBytes, gu_units % 2 == 0, c.nw_gu, c.cpt_gu, c.rpw_gu, c.smem_gu) ||
+        !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, true, c.nw_dn, c.cpt_dn, c.rpw_dn, c.smem_dn))
         return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
     return FRX_OK;
+}
+
+template <bool GATE_UP, int NW>
+void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_t stream) {
+    const int sms = sm_count();
+    constexpr int kFixed = GATE_UP ? 8 : 4;   // the benchmark shapes: n = 2048 in two chunks, ff = 512
+    if (upc == kFixed)
+        k_stream<GATE_UP, NW, kFixed><<<sms, NW * 32, smem, stream>>>(p);
+    else
+        k_stream<GATE_UP, NW, 0><<<sms, NW * 32, smem, stream>>>(p);
+}
+
+template <bool GATE_UP>
+void launch_stream(const StreamParams& p, int nw, int upc, uint32_t smem, cudaStream_t stream) {
+    switch (nw) {
+        case 8: launch_stream_nw<GATE_UP, 8>(p, upc, smem, stream); break;
+        case 12: launch_stream_nw<GATE_UP, 12>(p, upc, smem, stream); break;
+        default: launch_stream_nw<GATE_UP, 16>(p, upc, smem, stream); break;
+    }
 }
 
 // The streaming kernels need more dynamic shared memory than the default limit. The attribute
@@ -742,9 +817,13 @@ int set_smem_attr() {
     std::lock_guard<std::mutex> lk(mu);
     if (dev >= 0 && dev < 64 && done[dev]) return FRX_OK;
     const int lim = max_smem_optin();
-    const void* fns[] = {reinterpret_cast<const void*>(k_stream<true, 8>),  reinterpret_cast<const void*>(k_stream<false, 8>),
-                         reinterpret_cast<const void*>(k_stream<true, 12>), reinterpret_cast<const void*>(k_stream<false, 12>),
-                         reinterpret_cast<const void*>(k_stream<true, 16>), reinterpret_cast<const void*>(k_stream<false, 16>)};
+    const void* fns[] = {
+        reinterpret_cast<const void*>(k_stream<true, 8, 8>),   reinterpret_cast<const void*>(k_stream<true, 8, 0>),
+        reinterpret_cast<const void*>(k_stream<false, 8, 4>),  reinterpret_cast<const void*>(k_stream<false, 8, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 12, 8>),  reinterpret_cast<const void*>(k_stream<true, 12, 0>),
+        reinterpret_cast<const void*>(k_stream<false, 12, 4>), reinterpret_cast<const void*>(k_stream<false, 12, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 16, 8>),  reinterpret_cast<const void*>(k_stream<true, 16, 0>),
+        reinterpret_cast<const void*>(k_stream<false, 16, 4>), reinterpret_cast<const void*>(k_stream<false, 16, 0>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
@@ -765,27 +844,20 @@ void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaSt
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
-    const int sms = sm_count();
-    p.ring = cfg.ring_gu;
+    p.cpt = cfg.cpt_gu;
+    p.rpw = cfg.rpw_gu;
     p.aq = xb.q;
     p.aa = xb.a;
     p.ac = xb.c;
-    switch (g_nw) {
-        case 16: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 16><<<sms, 17 * 32, cfg.smem_gu, stream>>>(p)); break;
-        case 12: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 12><<<sms, 13 * 32, cfg.smem_gu, stream>>>(p)); break;
-        default: FRX_LAUNCH(kKGateUp, stream, k_stream<true, 8><<<sms, 9 * 32, cfg.smem_gu, stream>>>(p)); break;
-    }
+    FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
     FRX_LAUNCH(kKQuant, stream, k_quant_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(p.h, p.ff, nblk, hb.q, hb.a, hb.c));
-    p.ring = cfg.ring_dn;
+    p.cpt = cfg.cpt_dn;
+    p.rpw = cfg.rpw_dn;
     p.aq = hb.q;
     p.aa = hb.a;
     p.ac = hb.c;
-    switch (g_nw) {
-        case 16: FRX_LAUNCH(kKDown, stream, k_stream<false, 16><<<sms, 17 * 32, cfg.smem_dn, stream>>>(p)); break;
-        case 12: FRX_LAUNCH(kKDown, stream, k_stream<false, 12><<<sms, 13 * 32, cfg.smem_dn, stream>>>(p)); break;
-        default: FRX_LAUNCH(kKDown, stream, k_stream<false, 8><<<sms, 9 * 32, cfg.smem_dn, stream>>>(p)); break;
-    }
+    FRX_LAUNCH(kKDown, stream, launch_stream<false>(p, cfg.nw_dn, p.ff / kUnitK, cfg.smem_dn, stream));
 }
 
 template <class LayoutT>
