@@ -103,9 +103,11 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  block b for its token in one 16-byte load;
 //   a [row][k/32]  the block scale d (through fp16), divided by 16 for the second half of a
 //                  64-block (see group_mma);
-//   c [row][k/32]  the accumulator bias kMagicBits - sum(codes), the sum times 16 for the second half.
+//   c [row][k/32]  kMagic + sum(codes) as a float (the sum times 16 for the second half): what is
+//                  subtracted from an accumulator that started at kMagicBits, read as a float, to
+//                  get sum((q - 1) * code) exactly.
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
-                                                    float* __restrict__ a, int32_t* __restrict__ c) {
+                                                    float* __restrict__ a, float* __restrict__ c) {
     const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= n_blocks) return;
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
     q[row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
     if (lane == 0) {
         a[blk] = s ? d * 0.0625f : d;
-        c[blk] = kMagicBits - (s ? 16 * sum : sum);
+        c[blk] = kMagic + float(s ? 16 * sum : sum);
     }
 }
 
@@ -242,7 +244,7 @@ struct StreamParams {
     // activations in k_quant_frag's form: of x (rows = tokens) for GATE_UP, of h (rows = slots) for down
     const int8_t* aq;
     const float* aa;
-    const int32_t* ac;
+    const float* ac;
     float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by GATE_UP
     float* y;          // [T*K][n]      routed slots (down)
     float* ysh;        // [T][n]        shared-expert slots (down)
@@ -294,19 +296,19 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, in
 // word sit at bits 0, 2, 4, 6 of each byte; the first MMA takes fields 0 and 1 (w and w >> 2
 // masked with 0x03), the second takes fields 2 and 3 *in place* (masked with 0x30, i.e. the
 // codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
-// scale table, which holds d / 16 for the second half, and the accumulator bias table holds
-// kMagicBits - 16 * (sum of the activation codes) there.
+// scale table, which holds d / 16 for the second half. Every accumulator starts at kMagicBits;
+// read as a float it is kMagic + sum(q * a), and subtracting the bias table's kMagic + sum(a)
+// (times 16 for the second half) leaves sum((q - 1) * a), exactly.
 template <int UPC>   // units per call when known at compile time, else 0
 __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int count, int b0, const uint4* __restrict__ bfrag,
-                                          const ulonglong2* __restrict__ da, const int4* __restrict__ ci, int lane, uint64_t& acc_lo,
+                                          const ulonglong2* __restrict__ da, const ulonglong2* __restrict__ ci, int lane, uint64_t& acc_lo,
                                           uint64_t& acc_hi) {
     const int g = lane >> 2, t4 = lane & 3;
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
-    const uint64_t magic2 = pack2(kMagic, kMagic);
     const uint8_t* codes = units + lane * 16;
     const uint8_t* scales = units + kUnitCodeBytes + g * 8;
     const uint4* bf_p = bfrag + b0 * 32 + lane;
-    const int4* ci_p = ci + b0 * 4 + t4;
+    const ulonglong2* ci_p = ci + b0 * 4 + t4;
     const ulonglong2* da_p = da + b0 * 4 + t4;
     const int n_units = UPC ? UPC : count;
 #pragma unroll(UPC ? UPC : 2)
@@ -320,17 +322,17 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int
             const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
             const int b = 2 * u + j;
             const uint4 bf = bf_p[b * 32];
-            const int4 c0 = ci_p[b * 4];
+            const ulonglong2 cb = ci_p[b * 4];  // {bias0[c0], bias0[c1]}, {bias1[c0], bias1[c1]}
             const ulonglong2 a = da_p[b * 4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
             uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, c0.x, c0.y);
-            mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, c0.z, c0.w);
+            mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, kMagicBits);
+            mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, kMagicBits);
             const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
             const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
             // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
             // multiply-add rounds exactly where the reference's two statements round once.
-            const uint64_t sumi_lo = fma2(a.y, sub2(lo1, magic2), mul2(a.x, sub2(lo0, magic2)));
-            const uint64_t sumi_hi = fma2(a.y, sub2(hi1, magic2), mul2(a.x, sub2(hi0, magic2)));
+            const uint64_t sumi_lo = fma2(a.y, sub2(lo1, cb.y), mul2(a.x, sub2(lo0, cb.x)));
+            const uint64_t sumi_hi = fma2(a.y, sub2(hi1, cb.y), mul2(a.x, sub2(hi0, cb.x)));
             // The weight scale is applied with scalar multiplies: a packed multiply followed by a
             // packed add is contracted into one fused multiply-add by the assembler, which would
             // round once where the reference rounds twice.
@@ -433,7 +435,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const int buf = q & 1;
         uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag[buf]);
         float* daw = reinterpret_cast<float*>(smem + sp.da[buf]);
-        int* ciw = reinterpret_cast<int*>(smem + sp.ci[buf]);
+        float* ciw = reinterpret_cast<float*>(smem + sp.ci[buf]);
         if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
         const int m = it->n_tok;
         // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
@@ -478,7 +480,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
         const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da[buf]);
-        const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci[buf]);
+        const ulonglong2* ci = reinterpret_cast<const ulonglong2*>(smem + sp.ci[buf]);
         const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
         const int m = its->n_tok;
         const int g = lane >> 2, t4 = lane & 3;
@@ -832,7 +834,7 @@ int set_smem_attr() {
 struct ActBufs {
     int8_t* q;
     float* a;
-    int32_t* c;
+    float* c;
 };
 
 // The expert FFN over the items of p: quantize x, gate/up + SwiGLU into p.h, quantize the
@@ -862,11 +864,11 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
 
 template <class LayoutT>
 ActBufs act_x(uint8_t* base, const LayoutT& L) {
-    return ActBufs{reinterpret_cast<int8_t*>(base + L.xq), reinterpret_cast<float*>(base + L.xa), reinterpret_cast<int32_t*>(base + L.xc)};
+    return ActBufs{reinterpret_cast<int8_t*>(base + L.xq), reinterpret_cast<float*>(base + L.xa), reinterpret_cast<float*>(base + L.xc)};
 }
 template <class LayoutT>
 ActBufs act_h(uint8_t* base, const LayoutT& L) {
-    return ActBufs{reinterpret_cast<int8_t*>(base + L.hq), reinterpret_cast<float*>(base + L.ha), reinterpret_cast<int32_t*>(base + L.hc)};
+    return ActBufs{reinterpret_cast<int8_t*>(base + L.hq), reinterpret_cast<float*>(base + L.ha), reinterpret_cast<float*>(base + L.hc)};
 }
 
 int check_moe_shape(const char* who, int n, int ff, int K) {

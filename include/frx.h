@@ -170,10 +170,10 @@ int frx_moe_decode_static(const void* experts, size_t stride, int E, const void*
                           frx_stream_t stream);
 
 /* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging).
- * "xq" int8 [T][n], "xa" float [T][n/32], "xc" int32 [T][n/32]: the Q8 form of x as the expert
+ * "xq" int8 [T][n], "xa" float [T][n/32], "xc" float [T][n/32]: the Q8 form of x as the expert
  * kernel reads it -- the four codes of elements 64b + 32s + 16h + 4t .. +3 of a row are word
  * (b*4 + t)*4 + s*2 + h; xa is the block scale, divided by 16 for odd blocks; xc is
- * 0x4B400000 - sum(codes), the sum times 16 for odd blocks. "hq", "ha", "hc": the same for the
+ * 12582912 + sum(codes) as a float, the sum times 16 for odd blocks. "hq", "ha", "hc": the same for the
  * hidden activations, one row of ff per slot. "h" float [T*K + T][ff]: the hidden activations
  * silu(gate x) * up x per slot (shared-expert slots last). "y" float [T*K][n], "ysh" float [T][n],
  * "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
