@@ -68,6 +68,8 @@ SIGNATURES = {
     "frx_moe_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "frx_moe_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "frx_moe_prefill": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_moe_prefill_umma": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_moe_prefill_stream": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -324,8 +324,9 @@ class moe_q2:
 
     @staticmethod
     def run(experts: int, stride: int, E: int, n: int, ff: int, x: torch.Tensor, ids: torch.Tensor, yd: torch.Tensor | None = None,
-            ws: torch.Tensor | None = None, stream=None) -> torch.Tensor:
-        """yd[t*K + k] = down(silu(gate x_t) * up x_t) of expert ids[t][k], fp32 [T*K][n]."""
+            ws: torch.Tensor | None = None, stream=None, form: str = "auto") -> torch.Tensor:
+        """yd[t*K + k] = down(silu(gate x_t) * up x_t) of expert ids[t][k], fp32 [T*K][n].
+        form: "auto" (by size), "umma" (tcgen05 / tensor memory) or "stream"."""
         _dev(x, ids, yd)
         T, K = ids.shape
         if yd is None:
@@ -333,5 +334,6 @@ class moe_q2:
         if ws is None:
             ws = workspace(moe_q2.workspace_bytes(T, K, n, ff, E), x.device)
         wp, wb = _ws_ptr(ws)
-        check(lib.frx_moe_prefill(C.c_void_p(experts), stride, E, n, ff, _ptr(x), _ptr(ids), T, K, _ptr(yd), wp, wb, _stream(stream)))
+        fn = {"auto": lib.frx_moe_prefill, "umma": lib.frx_moe_prefill_umma, "stream": lib.frx_moe_prefill_stream}[form]
+        check(fn(C.c_void_p(experts), stride, E, n, ff, _ptr(x), _ptr(ids), T, K, _ptr(yd), wp, wb, _stream(stream)))
         return yd

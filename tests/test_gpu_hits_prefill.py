@@ -53,8 +53,9 @@ def test_hits_rejects_large_windows():
                      torch.zeros(200, 256, device="cuda"), 256, 128, torch.zeros(200, 10, 256, device="cuda"), T=200)
 
 
+@pytest.mark.parametrize("form", ["stream", "umma"])
 @pytest.mark.parametrize("T,E,K,zipf", [(96, 16, 4, False), (300, 24, 6, True), (1, 8, 2, False), (1200, 12, 3, True)])
-def test_prefill_per_slot_outputs(port, T, E, K, zipf):
+def test_prefill_per_slot_outputs(port, T, E, K, zipf, form):
     # moe_q2::run contract: yd[t*K + k] = expert ids[t][k] applied to x_t
     n, ff = 256, 128
     ex = Experts(port, n, ff, E, shared=False)
@@ -62,7 +63,7 @@ def test_prefill_per_slot_outputs(port, T, E, K, zipf):
     lg = synth.zipf_logits(T, E) if zipf else synth.router_logits(T, E)
     ids, wts, _ = port.route(lg, K)
     ws = moe.workspace(moe.moe_q2.workspace_bytes(T, K, n, ff, E))
-    yd = moe.moe_q2.run(ex.base, ex.stride, E, n, ff, cuda(x), cuda(ids), ws=ws)
+    yd = moe.moe_q2.run(ex.base, ex.stride, E, n, ff, cuda(x), cuda(ids), ws=ws, form=form)
     moe.workspace_status(ws)
     yd = yd.cpu().numpy()
     _, ref_ys, _ = port.moe_layer(ex.routed_planar(), ex.blob_bytes, None, n, ff, x, ids, wts, None, n_threads=8, want_slots=True)
@@ -70,12 +71,14 @@ def test_prefill_per_slot_outputs(port, T, E, K, zipf):
 
 
 def test_prefill_config_shape_sample(port):
-    # layer shape of the benchmark's prefill config, fewer experts and tokens; a sample of slots
+    # layer shape of the benchmark's prefill config, fewer experts and tokens; a sample of slots;
+    # the tensor-memory form (chosen by size) and the streaming form must agree to the bit
     n, ff, E, K, T = 2048, 512, 32, 10, 256
     ex = Experts(port, n, ff, E, shared=False, direct=True)
     x = synth.activations(T, n, through_bf16=True)
     ids, wts, _ = port.route(synth.zipf_logits(T, E), K)
     yd = moe.moe_q2.run(ex.base, ex.stride, E, n, ff, cuda(x), cuda(ids)).cpu().numpy()
+    assert np.array_equal(yd, moe.moe_q2.run(ex.base, ex.stride, E, n, ff, cuda(x), cuda(ids), form="stream").cpu().numpy())
     xq, xd = port.quantize_q8(x)
     for s in range(0, T * K, 97):
         t, k = divmod(s, K)
