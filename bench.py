@@ -374,7 +374,7 @@ def run_prefill(args):
     arena.load_planar(0, 0, E + 1, pl.view(-1))
     del pl
     x = torch.from_numpy(synth.activations(T, N_MODEL, through_bf16=True)).to(dev)
-    logits = torch.from_numpy(synth.zipf_logits(T, E)).to(dev)
+    logits = torch.from_numpy(synth.zipf_logits(T, E) if args.routing == "zipf" else synth.router_logits(T, E)).to(dev)
     ws = moe.workspace(moe.moe_q2.workspace_bytes(T, K, N_MODEL, FF, E), dev)
     yd = torch.empty(T * K, N_MODEL, device=dev)
     out = torch.empty(T, N_MODEL, device=dev)
@@ -416,7 +416,7 @@ def run_prefill(args):
         "metric": "q2_0_moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "fp16 operands holding exact integers, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": f"configs[2]: one Q2_0 MoE layer prefill, {T} tokens, hidden 2048, 512 experts top-10, Zipf(1.1) routing",
+        "config": {"workload": f"configs[2]: one Q2_0 MoE layer prefill, {T} tokens, hidden 2048, 512 experts top-10, {'Zipf(1.1)' if args.routing == 'zipf' else 'uniform'} routing",
                    "form": args.form, "l2": "453 MB of experts per step, larger than L2"},
         "clocks": clocks, "kernels": kernels,
         "roofline": {"bound": "tensor", "kernel": "k_pf_umma (gate/up + down)", "achieved": round(gemm_tf, 1), "peak": peak_tf,
@@ -437,6 +437,7 @@ def main():
     ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"], help="decode = configs[1] (default), prefill = configs[2]")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill tokens")
+    ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform"], help="prefill routing skew")
     ap.add_argument("--form", default="auto", choices=["auto", "umma", "stream"], help="prefill kernel form")
     args = ap.parse_args()
     if args.impl == "reference":

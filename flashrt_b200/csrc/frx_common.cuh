@@ -105,6 +105,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     const uint64_t t0 = global_ns();
     for (uint32_t polls = 1;; ++polls) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (polls > 4) __nanosleep(polls > 64 ? 256 : 32);   // a long wait must not take issue slots from working warps
         if ((polls & 63u) == 0) {
             if (*abort) return false;
             if (global_ns() - t0 > kWaitLimitNs) {

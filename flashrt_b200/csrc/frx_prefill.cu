@@ -11,8 +11,9 @@
 // sums held in registers, block after block.
 //
 // Per CTA (one per SM), warp roles: 0 = TMA producer, 1 = MMA issuer and tensor-memory owner,
-// 2-5 = dequant (2-bit codes of 128 rows x 64 weights -> fp16 core-matrix layout in shared
-// memory), 6-13 = epilogue (tensor memory -> registers, scaling, SwiGLU / output stores).
+// 2-9 = dequant (2-bit codes of 128 rows x 64 weights -> fp16 core-matrix layout in shared
+// memory), 10-25 = epilogue (tensor memory -> registers, scaling, SwiGLU / output stores): each
+// epilogue warp owns 32 rows (its quarter of the tensor-memory lanes) x 32 token columns.
 // All waits are bounded; a wait that runs out sets the workspace status word and the block drains.
 #include "frx_umma.cuh"
 
@@ -26,13 +27,17 @@ namespace {
 constexpr int kTileRows = 128;     // M of the MMA: 8 groups of 16 matrix rows
 constexpr int kTileTok = 128;      // most tokens of one tile (N of the MMA), a multiple of 16
 constexpr int kTokPad = 16;        // every expert's token count is padded to this
-constexpr int kStepBytesA = kTileRows * 64 * 2;   // fp16 A tile of one 64-block: 16 KB
+// fp16 A tile of one 64-block: 16 groups of 8 rows, each 8 core matrices (8 rows x 16 bytes) 192
+// bytes apart rather than 128, so that the dequant warps' 8-byte stores to two neighbouring
+// chunks fall into different banks
+constexpr int kALbo = 192, kASbo = 8 * kALbo;
+constexpr int kStepBytesA = (kTileRows / 8) * kASbo;   // 24 KB
 constexpr int kStepBytesB = kTileTok * 64 * 2;    // fp16 B tile of one 64-block: 16 KB
 constexpr int kStepBytesS = kTileTok * 8;         // activation scales of one 64-block: 1 KB
 constexpr int kUnitTileBytes = 8 * kUnitBytes;    // packed weights of 8 groups x one unit: 4608 B
-constexpr int kStagesW = 2, kStagesA = 2, kStagesB = 3, kStagesD = 2;
-constexpr int kWarpsDequant = 4, kWarpsEpilogue = 8;
-constexpr int kThreads = (2 + kWarpsDequant + kWarpsEpilogue) * 32;   // 448
+constexpr int kStagesW = 3, kStagesA = 4, kStagesB = 4, kStagesD = 2;
+constexpr int kWarpsDequant = 8, kWarpsEpilogue = 16;
+constexpr int kThreads = (2 + kWarpsDequant + kWarpsEpilogue) * 32;   // 832
 
 // meta words: [0] padded positions in use, [1] token blocks
 struct PfuLayout {
@@ -255,7 +260,7 @@ __host__ __device__ constexpr PfSmem pf_smem() {
     m.s = off;
     off += kStagesB * kStepBytesS;
     m.sw = off;
-    off += kStagesD * kTileRows * 4;
+    off += kStagesA * kTileRows * 4;
     m.bars = off;
     off += 32 * 8;
     m.tmem = off;
@@ -271,7 +276,7 @@ enum : int {
     kBarWFull = 0,                      // + stage: packed weights of a unit have landed
     kBarWFree = kBarWFull + kStagesW,   // dequant warps are done with them
     kBarAFull = kBarWFree + kStagesW,   // fp16 A tile written
-    kBarAFree = kBarAFull + kStagesA,   // the MMAs that read it have completed
+    kBarAFree = kBarAFull + kStagesA,   // the MMAs that read it have completed and the epilogue is done with its row scales
     kBarBFull = kBarAFree + kStagesA,   // fp16 B tile and activation scales have landed
     kBarBFree = kBarBFull + kStagesB,   // MMAs completed and epilogue done with the scales
     kBarDFull = kBarBFree + kStagesB,   // accumulators of a step are complete in tensor memory
@@ -280,14 +285,13 @@ enum : int {
 };
 static_assert(kBarCount <= 32, "barrier block too small");
 
-// 16 fp32 columns of tensor memory for this thread's lane, packed in pairs.
-__device__ __forceinline__ void tmem_ld16_pairs(uint32_t taddr, uint64_t (&v)[8]) {
+// 8 fp32 columns of tensor memory for this thread's lane, packed in pairs.
+__device__ __forceinline__ void tmem_ld8_pairs(uint32_t taddr, uint64_t (&v)[4]) {
     asm volatile(
-        "{\n\t.reg .b32 r<16>;\n\t"
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {r0,r1,r2,r3,r4,r5,r6,r7,r8,r9,r10,r11,r12,r13,r14,r15}, [%8];\n\t"
-        "mov.b64 %0, {r0,r1};\n\tmov.b64 %1, {r2,r3};\n\tmov.b64 %2, {r4,r5};\n\tmov.b64 %3, {r6,r7};\n\t"
-        "mov.b64 %4, {r8,r9};\n\tmov.b64 %5, {r10,r11};\n\tmov.b64 %6, {r12,r13};\n\tmov.b64 %7, {r14,r15};\n\t}"
-        : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]), "=l"(v[4]), "=l"(v[5]), "=l"(v[6]), "=l"(v[7])
+        "{\n\t.reg .b32 r<8>;\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {r0,r1,r2,r3,r4,r5,r6,r7}, [%4];\n\t"
+        "mov.b64 %0, {r0,r1};\n\tmov.b64 %1, {r2,r3};\n\tmov.b64 %2, {r4,r5};\n\tmov.b64 %3, {r6,r7};\n\t}"
+        : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3])
         : "r"(taddr));
 }
 
@@ -314,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         }
         for (int i = 0; i < kStagesA; ++i) {
             mbar_init(bars + kBarAFull + i, kWarpsDequant);
-            mbar_init(bars + kBarAFree + i, 1);
+            mbar_init(bars + kBarAFree + i, 1 + kWarpsEpilogue);
         }
         for (int i = 0; i < kStagesB; ++i) {
             mbar_init(bars + kBarBFull + i, 1);
@@ -381,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                     const uint32_t a_addr = smem_u32(smem + sm.a + as * kStepBytesA), b_addr = smem_u32(smem + sm.b + bs * kStepBytesB);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {   // four K = 16 instructions: two per 32-block
-                        const uint64_t da = umma_desc(a_addr + kk * 256, 128, 1024), db = umma_desc(b_addr + kk * 256, 128, 1024);
+                        const uint64_t da = umma_desc(a_addr + kk * 2 * kALbo, kALbo, kASbo), db = umma_desc(b_addr + kk * 256, 128, 1024);
                         umma_f16(tmem + ds * 256 + (kk >> 1) * kTileTok, da, db, idesc, kk & 1);
                     }
                     umma_commit(bars + kBarAFree + as);
@@ -392,25 +396,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         }
     } else if (warp < 2 + kWarpsDequant) {
         // ---------------- dequant: packed 2-bit codes -> fp16 (q - 1) in the A tile
-        const int dw = warp - 2;
+        const int dw = warp - 2;   // the group (16 rows) of the tile this warp unpacks
         const int g8 = lane >> 2, t4 = lane & 3;
         const __half2 k1025 = __floats2half2_rn(1025.0f, 1025.0f);
         uint32_t g = 0, gu = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             for (int b = 0; b < steps; ++b, ++g) {
                 const int j = b & 1;
-                const uint32_t ws = gu % kStagesW, as = g % kStagesA, ds = g % kStagesD;
+                const uint32_t ws = gu % kStagesW, as = g % kStagesA;
                 if (j == 0) wait_full(kBarWFull + ws, gu / kStagesW);
+                // an A stage (the fp16 tile and its row scales) is free once the MMAs that read the
+                // tile have completed and the epilogue warps have used the scales
                 wait_free(kBarAFree + as, g / kStagesA);
-                wait_free(kBarDFree + ds, g / kStagesD);   // the epilogue has read this stage's row scales
-                const uint8_t* wt = smem + sm.w + ws * kUnitTileBytes;
+                const uint8_t* wt = smem + sm.w + ws * kUnitTileBytes + dw * kUnitBytes;
                 uint8_t* at = smem + sm.a + as * kStepBytesA;
+                const uint4 wv = *reinterpret_cast<const uint4*>(wt + lane * 16);   // words [h][j] of this lane
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int gi = 2 * dw + (q >> 1), h = q & 1;
-                    const uint32_t w = *reinterpret_cast<const uint32_t*>(wt + gi * kUnitBytes + lane * 16 + (h * 2 + j) * 4);
-                    const int row = gi * 16 + g8 + 8 * h;
-                    uint8_t* dst = at + (row >> 3) * 1024 + (row & 7) * 16 + (t4 & 1) * 8;
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t w = h ? (j ? wv.w : wv.z) : (j ? wv.y : wv.x);
+                    const int row = dw * 16 + g8 + 8 * h;
+                    uint8_t* dst = at + (row >> 3) * kASbo + (row & 7) * 16 + (t4 & 1) * 8;
 #pragma unroll
                     for (int f = 0; f < 4; ++f) {   // field f: elements 16 f + 4 t4 .. + 3 of the block
                         const uint32_t x = (w >> (2 * f)) & 0x03030303u;
@@ -419,63 +424,66 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                         uint2 out;
                         out.x = *reinterpret_cast<const uint32_t*>(&l2);
                         out.y = *reinterpret_cast<const uint32_t*>(&h2);
-                        *reinterpret_cast<uint2*>(dst + (2 * f + (t4 >> 1)) * 128) = out;
+                        *reinterpret_cast<uint2*>(dst + (2 * f + (t4 >> 1)) * kALbo) = out;
                     }
                 }
-                {   // this step's weight scales, one row per thread
-                    const int gi = 2 * dw + (lane >> 4), m = lane & 15;
-                    const __half sc = *reinterpret_cast<const __half*>(wt + gi * kUnitBytes + kUnitCodeBytes + (m & 7) * 8 + ((m >> 3) * 2 + j) * 2);
-                    reinterpret_cast<float*>(smem + sm.sw)[ds * kTileRows + gi * 16 + m] = __half2float(sc);
+                if (lane < 16) {   // this step's weight scales of the warp's 16 rows
+                    const __half sc = *reinterpret_cast<const __half*>(wt + kUnitCodeBytes + (lane & 7) * 8 + ((lane >> 3) * 2 + j) * 2);
+                    reinterpret_cast<float*>(smem + sm.sw)[as * kTileRows + dw * 16 + lane] = __half2float(sc);
                 }
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bars + kBarAFull + as);
-                    if (j == 1 || b == steps - 1) mbar_arrive(bars + kBarWFree + ws);
+                    if (j == 1) mbar_arrive(bars + kBarWFree + ws);
                 }
-                if (j == 1 || b == steps - 1) ++gu;
+                if (j == 1) ++gu;
             }
         }
     } else {
         // ---------------- epilogue
         const int ew = warp - (2 + kWarpsDequant);
         const int quarter = warp & 3;             // the tensor-memory lanes this warp may read
-        const int half = ew >> 2;                 // which 64 columns
+        const int cq = ew >> 2;                   // which 32 token columns
         const int row = quarter * 32 + lane;      // M row of the tile
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
         uint32_t g = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int tb = tile / row_blocks, rb = tile % row_blocks;
             const int p0 = p.tb_p0[tb], ntok = p.tb_n[tb];
-            const int ncols = max(0, min(64, ntok - 64 * half));
-            uint64_t acc[32];
+            const int ncols = max(0, min(32, ntok - 32 * cq));
+            float acc[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
             for (int b = 0; b < steps; ++b, ++g) {
                 const uint32_t as = g % kStagesA, bs = g % kStagesB, ds = g % kStagesD;
                 wait_full(kBarDFull + ds, g / kStagesD);
-                // complete long ago (the MMAs needed them); waited on here so that this thread itself
-                // acquires what the dequant warps (row scales) and the TMA (activation scales) wrote
+                // complete long ago (the MMAs needed them) and not reusable before this warp releases
+                // the stages below; waited on here so that this thread itself acquires what the
+                // dequant warps (row scales) and the TMA (activation scales) wrote
                 wait_full(kBarAFull + as, g / kStagesA);
                 wait_full(kBarBFull + bs, g / kStagesB);
                 tc_fence_after_sync();
-                const float d = reinterpret_cast<const float*>(smem + sm.sw)[ds * kTileRows + row];
-                const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(smem + sm.s + bs * kStepBytesS) + half * 32;
-                const uint32_t t0 = tmem + lane_addr + ds * 256 + half * 64;
+                const float d = reinterpret_cast<const float*>(smem + sm.sw)[as * kTileRows + row];
+                const uint64_t dd = pack2(d, d);
+                const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(smem + sm.s + bs * kStepBytesS) + cq * 16;
+                const uint32_t t0 = tmem + lane_addr + ds * 256 + cq * 32;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    if (c * 16 < ncols) {
-                        uint64_t s0[8], s1[8];
-                        tmem_ld16_pairs(t0 + c * 16, s0);
-                        tmem_ld16_pairs(t0 + kTileTok + c * 16, s1);
+                    if (c * 8 < ncols) {
+                        uint64_t s0[4], s1[4];
+                        tmem_ld8_pairs(t0 + c * 8, s0);
+                        tmem_ld8_pairs(t0 + kTileTok + c * 8, s1);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const ulonglong2 a = sc[c * 8 + i];   // {a0 of the two tokens}, {a1 of the two tokens}
-                            const uint64_t sumi = fma2(a.y, s1[i], mul2(a.x, s0[i]));
+                        for (int i = 0; i < 4; ++i) {
+                            const ulonglong2 a = sc[c * 4 + i];   // {a0 of the two tokens}, {a1 of the two tokens}
+                            // packed multiply by the row scale, then *scalar* adds: a packed add
+                            // would be contracted with the multiply into one rounding
                             float u0, u1;
-                            unpack2(sumi, u0, u1);
-                            acc[c * 8 + i] = add2(acc[c * 8 + i], pack2(__fmul_rn(d, u0), __fmul_rn(d, u1)));
+                            unpack2(mul2(dd, fma2(a.y, s1[i], mul2(a.x, s0[i]))), u0, u1);
+                            acc[c * 8 + 2 * i] = __fadd_rn(acc[c * 8 + 2 * i], u0);
+                            acc[c * 8 + 2 * i + 1] = __fadd_rn(acc[c * 8 + 2 * i + 1], u1);
                         }
                     }
                 }
@@ -484,19 +492,19 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                 if (lane == 0) {
                     mbar_arrive(bars + kBarDFree + ds);
                     mbar_arrive(bars + kBarBFree + bs);
+                    mbar_arrive(bars + kBarAFree + as);
                 }
             }
-            // ---- tile done: acc[i] holds this row's sums for tokens 64 half + 2i, + 2i + 1
+            // ---- tile done: acc[i] holds this row's sum for token 32 cq + i
             if (GATE_UP) {
                 // rows m < 8 of a group are gate rows, m >= 8 the up rows of the same ff rows
                 const int m = row & 15, ffrow = rb * 64 + (row >> 4) * 8 + (m & 7);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v0, v1;
-                    unpack2(acc[i], v0, v1);
+                for (int i = 0; i < 16; ++i) {
+                    const float v0 = acc[2 * i], v1 = acc[2 * i + 1];
                     const float w0 = __shfl_down_sync(0xffffffffu, v0, 8), w1 = __shfl_down_sync(0xffffffffu, v1, 8);
                     if (m < 8 && 2 * i < ncols) {
-                        const size_t pos = size_t(p0 + 64 * half + 2 * i);
+                        const size_t pos = size_t(p0 + 32 * cq + 2 * i);
                         p.hf[pos * p.ff + ffrow] = swiglu_ref(v0, w0);
                         p.hf[(pos + 1) * p.ff + ffrow] = swiglu_ref(v1, w1);
                     }
@@ -504,11 +512,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
             } else {
                 const int orow = rb * kTileRows + row;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     if (2 * i < ncols) {
-                        float v0, v1;
-                        unpack2(acc[i], v0, v1);
-                        const int pos = p0 + 64 * half + 2 * i;
+                        const float v0 = acc[2 * i], v1 = acc[2 * i + 1];
+                        const int pos = p0 + 32 * cq + 2 * i;
                         const int sl0 = p.pslot[pos], sl1 = p.pslot[pos + 1];
                         if (sl0 >= 0) p.yd[size_t(sl0) * p.n + orow] = v0;
                         if (sl1 >= 0) p.yd[size_t(sl1) * p.n + orow] = v1;
@@ -620,10 +627,11 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     return FRX_OK;
 }
 
-// ---- the public entry: the tensor-memory form from kUmmaMinSlots (token, expert) slots on, where
-// its 128-row x up-to-128-token tiles fill; below that the streaming form, whose unit of work
-// is one expert and 8 tokens. Both compute the same bits.
-constexpr int kUmmaMinSlots = 2048;
+// ---- the public entry. Both forms compute the same bits; the choice is by measured speed: the
+// tensor-memory form pays per 128-row x 64-weight step whatever the number of tokens in the tile,
+// so it is taken only when experts get many tokens on average (256 or more, where it is on a par
+// with or ahead of the streaming form on B200), and the streaming form otherwise.
+constexpr int kUmmaMinTokensPerExpert = 256;
 
 size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E) {
     const size_t a = frx_moe_prefill_stream_workspace_bytes(T, K, n, ff, E), b = frx_moe_prefill_umma_workspace_bytes(T, K, n, ff, E);
@@ -633,7 +641,7 @@ size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E) {
 
 int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
                     float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
-    if (T > 0 && K > 0 && size_t(T) * K >= kUmmaMinSlots)
+    if (T > 0 && K > 0 && E > 0 && size_t(T) * K >= size_t(kUmmaMinTokensPerExpert) * E)
         return frx_moe_prefill_umma(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream);
     return frx_moe_prefill_stream(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream);
 }

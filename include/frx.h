@@ -219,10 +219,11 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
  * yd[t*K + k] [n] = down(silu(gate x_t) * up x_t) of expert ids[t*K + k], fp32.
  * Grouping by expert, the tile list and every launch size are computed on the device: no host
  * synchronisation. n % 128 == 0, ff % 128 == 0, E <= 4096.
- * From 2048 slots (T * K) on, the product runs on the tcgen05 tensor cores with accumulators in
- * tensor memory (frx_moe_prefill_umma); below, in the streaming form the decode path uses
- * (frx_moe_prefill_stream). Both give the same bits; the two are exported so each can be called
- * and measured on its own, with the same arguments and workspace size. */
+ * Two forms compute the same bits: frx_moe_prefill_umma runs the integer products on the tcgen05
+ * tensor cores with accumulators in tensor memory, frx_moe_prefill_stream is the form the decode
+ * path uses. frx_moe_prefill takes the tensor-memory form when experts receive 256 or more tokens
+ * on average (T * K >= 256 * E) and the streaming form otherwise; the two are exported so each can
+ * be called and measured on its own, with the same arguments and workspace size. */
 size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E);
 int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
                     int K, float* yd, void* ws, size_t ws_bytes, frx_stream_t stream);
