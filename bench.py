@@ -226,8 +226,11 @@ def run_frx(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- value: the 48 layer calls replayed from one CUDA graph (single GPU), inputs resident in HBM
+    # ---- value: inputs resident in HBM. Single GPU: the 48 layer calls replayed from one CUDA graph.
+    # Expert parallel: plain launches (capturing the NCCL all-reduces together with these kernels
+    # did not complete on the 2-GPU box, so it is not attempted).
     use_graph = world == 1 and not args.no_graph
+    run = step
     if use_graph:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -238,8 +241,6 @@ def run_frx(args):
         with torch.cuda.graph(graph):
             step()
         run = graph.replay
-    else:
-        run = step
     for _ in range(args.warmup):
         run()
     barrier()
@@ -257,7 +258,7 @@ def run_frx(args):
         ms = float(t.item())
     moe.workspace_status(ws)
     value = B * L / (ms * 1e-3)
-    launches_per_layer = 6 if world == 1 else 7
+    launches_per_layer = 7   # route, quantize x, group, gate/up, quantize hidden, down, combine (the all-reduce is NCCL's)
 
     # ---- per-kernel device time: CUDA events around every launch, the same K steps without the graph
     ncls = 7
@@ -333,6 +334,12 @@ def run_frx(args):
         else:
             cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
 
+    if world > 1:   # every rank must hold the same routing and the same reduced output
+        chk = torch.stack([out.double().sum(), ids.double().sum()])
+        lo_, hi_ = chk.clone(), chk.clone()
+        dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo_, hi_), "ranks disagree on the layer output"
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
