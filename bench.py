@@ -358,58 +358,83 @@ def run_frx(args):
 
 
 def run_prefill(args):
-    """BASELINE.json configs[2]: one MoE layer prefill, 4096 tokens x hidden 2048 (bf16-rounded N(0,1)),
-    512 experts top-10 with Zipf(1.1)-skewed routing; a step is route + grouped expert product + combine."""
+    """BASELINE.json configs[2] (one GPU) and configs[4] (expert parallel, --gpus N under
+    torch.distributed.run): one MoE layer prefill of --tokens tokens x hidden 2048 (bf16-rounded
+    N(0,1)), 512 experts top-10, Zipf(1.1) or uniform routing. A step is route + grouped expert
+    product + combine; expert parallel, tokens and experts are both sharded over the ranks and the
+    slots travel by NCCL all-to-all."""
     import torch
+    import torch.distributed as dist
 
-    from flashrt_b200 import moe, synth
+    from flashrt_b200 import ep, moe, synth
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     T = args.tokens
-    arena = moe.ExpertArena(1, E + 1, N_MODEL, FF)
+    Tl = T // world
+    e_lo, e_hi = ep.expert_range(rank, world, E)
+    arena = moe.ExpertArena(1, e_hi - e_lo, N_MODEL, FF)
     gen = torch.Generator(device=dev)
     gen.manual_seed(20260927)
     nb_gu, nb_dn = FF * (N_MODEL // 64), N_MODEL * (FF // 64)
-    pl = torch.randint(0, 256, (E + 1, EXPERT_BYTES), dtype=torch.uint8, device=dev, generator=gen)
+    pl = torch.randint(0, 256, (E, EXPERT_BYTES), dtype=torch.uint8, device=dev, generator=gen)
     off = 0
     for nblk in (nb_gu, nb_gu, nb_dn):
-        d = (torch.randn(E + 1, nblk, device=dev, generator=gen) * 0.02).abs().to(torch.float16)
+        d = (torch.randn(E, nblk, device=dev, generator=gen) * 0.02).abs().to(torch.float16)
         d[d == 0] = 6.103515625e-05
-        pl[:, off + nblk * 16:off + nblk * 18] = d.view(torch.uint8).view(E + 1, nblk * 2)
+        pl[:, off + nblk * 16:off + nblk * 18] = d.view(torch.uint8).view(E, nblk * 2)
         off += nblk * 18
-    arena.load_planar(0, 0, E + 1, pl.view(-1))
+    arena.load_planar(0, 0, e_hi - e_lo, pl[e_lo:e_hi].contiguous().view(-1))
     del pl
-    x = torch.from_numpy(synth.activations(T, N_MODEL, through_bf16=True)).to(dev)
-    logits = torch.from_numpy(synth.zipf_logits(T, E) if args.routing == "zipf" else synth.router_logits(T, E)).to(dev)
-    ws = moe.workspace(moe.moe_q2.workspace_bytes(T, K, N_MODEL, FF, E), dev)
-    yd = torch.empty(T * K, N_MODEL, device=dev)
-    out = torch.empty(T, N_MODEL, device=dev)
+    xa = synth.activations(T, N_MODEL, through_bf16=True)
+    la = synth.zipf_logits(T, E) if args.routing == "zipf" else synth.router_logits(T, E)
+    x = torch.from_numpy(xa[rank * Tl:(rank + 1) * Tl]).to(dev)
+    logits = torch.from_numpy(la[rank * Tl:(rank + 1) * Tl]).to(dev)
+    ws = moe.workspace(moe.moe_q2.workspace_bytes(Tl, K, N_MODEL, FF, E), dev)
+    yd = torch.empty(Tl * K, N_MODEL, device=dev)
+    out = torch.empty(Tl, N_MODEL, device=dev)
 
     def step():
-        ids, wts = moe.moe_route_topk(logits, K)
-        moe.moe_q2.run(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, ids, yd=yd, ws=ws, form=args.form)
-        moe.moe_combine(yd.view(T, K, N_MODEL), wts, None, None, None, out=out)
+        if world == 1:
+            ids, wts = moe.moe_route_topk(logits, K)
+            moe.moe_q2.run(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, ids, yd=yd, ws=ws, form=args.form)
+            moe.moe_combine(yd.view(Tl, K, N_MODEL), wts, None, None, None, out=out)
+        else:
+            ep.moe_prefill_ep(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, logits, K)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     for _ in range(args.warmup):
         step()
     moe.workspace_status(ws)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
-    torch.cuda.synchronize()
+    barrier()
     ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     ncls = 7
     pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
     moe.check(moe.lib.frx_profile_begin())
     for _ in range(args.steps):
         step()
     moe.check(moe.lib.frx_profile_end(pms, pn, ncls))
-    clocks = sampler.stop()
+    clocks = sampler.stop() if sampler else None
     names = [moe.lib.frx_profile_class_name(i).decode() for i in range(ncls)]
     kernels = {names[i]: {"launches": int(pn[i]), "us_per_step": round(1e3 * float(pms[i]) / args.steps, 2)} for i in range(ncls) if pn[i]}
     flops = T * K * 3 * 2 * N_MODEL * FF
@@ -418,17 +443,21 @@ def run_prefill(args):
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
         peak_tf = float(json.load(open(pk))["bf16_tflops"])
-    gemm_tf = flops / ((gu_ms + dn_ms) * 1e-3) / 1e12
-    print(json.dumps({
-        "metric": "q2_0_moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "fp16 operands holding exact integers, fp32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": f"configs[2]: one Q2_0 MoE layer prefill, {T} tokens, hidden 2048, 512 experts top-10, {'Zipf(1.1)' if args.routing == 'zipf' else 'uniform'} routing",
-                   "form": args.form, "l2": "453 MB of experts per step, larger than L2"},
-        "clocks": clocks, "kernels": kernels,
-        "roofline": {"bound": "tensor", "kernel": "k_pf_umma (gate/up + down)", "achieved": round(gemm_tf, 1), "peak": peak_tf,
-                     "unit": "TFLOP/s", "frac": round(gemm_tf / peak_tf, 4), "flops_per_step": flops,
-                     "ms_gate_up": gu_ms, "ms_down": dn_ms, "traffic": None}}))
+    gemm_tf = flops / world / ((gu_ms + dn_ms) * 1e-3) / 1e12
+    if rank == 0:
+        print(json.dumps({
+            "metric": "q2_0_moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "dtype": "exact integer products (int8 / fp16 operands), fp32 scale and accumulate", "data": "synthetic",
+            "config": {"workload": f"configs[{2 if world == 1 else 4}]: one Q2_0 MoE layer prefill, {T} tokens, hidden 2048, 512 experts top-10, "
+                                   f"{'Zipf(1.1)' if args.routing == 'zipf' else 'uniform'} routing",
+                       "form": args.form, "parallelism": f"ep{world}", "l2": "453 MB of experts per step, larger than L2"},
+            "clocks": clocks, "kernels": kernels,
+            "roofline": {"bound": "tensor", "kernel": "expert product (gate/up + down), rank 0", "achieved": round(gemm_tf, 1), "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": round(gemm_tf / peak_tf, 4), "flops_per_step": flops, "ms_gate_up": gu_ms,
+                         "ms_down": dn_ms, "traffic": None}}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():

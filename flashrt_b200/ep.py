@@ -44,3 +44,55 @@ def moe_layer_ep(experts_local: int, stride: int, E: int, e_lo: int, e_hi: int, 
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(out, group=group)
     return out
+
+
+def moe_prefill_ep(experts_local: int, stride: int, E: int, n: int, ff: int, x: torch.Tensor, logits: torch.Tensor, K: int,
+                   group=None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Prefill-sized expert-parallel layer. Tokens are sharded over the ranks (x, logits are this
+    rank's tokens), experts too (this rank holds expert_range(rank, world, E), E divisible by the
+    world size). Each rank routes its tokens, sends every (token, expert) slot's activations to the
+    rank that holds the expert (all-to-all), runs the grouped expert product on what it received,
+    returns the results (all-to-all) and sums them with the routing weights.
+
+    Returns (out [T_local][n], ids, wts). One host synchronisation (the split sizes), as the
+    reference's grouped path has one."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if E % world:
+        raise moe.FrxError(1, f"moe_prefill_ep: {E} experts do not divide over {world} ranks")
+    per = E // world
+    T = x.shape[0]
+    ids, wts = moe.moe_route_topk(logits, K)
+    flat = ids.reshape(-1).to(torch.int64)
+    dest = flat // per
+    order = torch.sort(dest, stable=True).indices                 # slots grouped by destination rank
+    send_counts = torch.bincount(dest, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts.copy_(send_counts)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()           # the one host synchronisation
+    tok = (order // K)
+    send_x = x.index_select(0, tok).contiguous()                  # [S][n]
+    send_e = (flat.index_select(0, order) - dest.index_select(0, order) * per).to(torch.int32).contiguous()
+    R = int(sum(rc))
+    recv_x = torch.empty(R, n, dtype=x.dtype, device=x.device)
+    recv_e = torch.empty(R, dtype=torch.int32, device=x.device)
+    if world > 1:
+        dist.all_to_all_single(recv_x, send_x, output_split_sizes=rc, input_split_sizes=sc, group=group)
+        dist.all_to_all_single(recv_e, send_e, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    else:
+        recv_x, recv_e = send_x, send_e
+    y = torch.empty(R, n, dtype=torch.float32, device=x.device)
+    if R:
+        moe.moe_q2.run(experts_local, stride, per, n, ff, recv_x, recv_e.view(R, 1), yd=y)
+    back = torch.empty(T * K, n, dtype=torch.float32, device=x.device)
+    if world > 1:
+        dist.all_to_all_single(back, y, output_split_sizes=sc, input_split_sizes=rc, group=group)
+    else:
+        back = y
+    yd = torch.empty_like(back)
+    yd.index_copy_(0, order, back)                                # slot order t * K + k again
+    out = moe.moe_combine(yd.view(T, K, n), wts, None, None, None)
+    return out, ids, wts

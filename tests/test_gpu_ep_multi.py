@@ -1,0 +1,71 @@
+"""Expert-parallel layers on two real GPUs (one process per GPU, NCCL): the decode form
+(replicated tokens, all-reduce) and the prefill form (sharded tokens, all-to-all) against the
+single-GPU result. Skipped on machines with fewer than two GPUs."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port_no, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port_no), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from flashrt_b200 import ep, moe, synth
+    from helpers import Experts, cuda, rel_max
+    from oracle import oracle
+    port = oracle.port()
+    n, ff, E, K, T = 512, 256, 16, 4, 64
+    ex = Experts(port, n, ff, E)                       # every rank builds all experts, uses its own range
+    lo, hi = ep.expert_range(rank, world, E)
+    x, lg = synth.activations(T, n), synth.router_logits(T, E)
+    ids, wts, _ = port.route(lg, K)
+    # decode form
+    out = torch.empty(T, n, device="cuda")
+    ids_o = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    wts_o = torch.empty(T, K, device="cuda")
+    ws = moe.workspace(moe.moe_layer_workspace_bytes(T, K, n, ff))
+    ep.moe_layer_ep(ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr if rank == 0 else None, n, ff, cuda(x), cuda(lg), None, K,
+                    out, ids_o, wts_o, ws)
+    full = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, cuda(x), cuda(ids), cuda(wts), None)
+    err_decode = rel_max(out.cpu().numpy(), full.cpu().numpy())
+    # prefill form: this rank's half of the tokens
+    Tl = T // world
+    xs, ls = x[rank * Tl:(rank + 1) * Tl], lg[rank * Tl:(rank + 1) * Tl]
+    o2, i2, w2 = ep.moe_prefill_ep(ex.base + lo * ex.stride, ex.stride, E, n, ff, cuda(xs), cuda(ls), K)
+    ref = port.moe_layer(ex.routed_planar(), ex.blob_bytes, None, n, ff, xs, ids[rank * Tl:(rank + 1) * Tl], wts[rank * Tl:(rank + 1) * Tl])
+    err_prefill = rel_max(o2.cpu().numpy(), ref)
+    ids_ok = bool(np.array_equal(i2.cpu().numpy(), ids[rank * Tl:(rank + 1) * Tl]))
+    ret[rank] = (err_decode, err_prefill, ids_ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_expert_parallel_layers():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as m:
+        ret = m.dict()
+        procs = [ctx.Process(target=_worker, args=(r, 2, 29533, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+            if p.is_alive():
+                p.kill()
+                pytest.fail("a rank did not finish in time")
+            assert p.exitcode == 0
+        for r in range(2):
+            err_decode, err_prefill, ids_ok = ret[r]
+            assert ids_ok
+            assert err_decode < 1e-5 and err_prefill < 1e-5
