@@ -57,6 +57,29 @@ void profile_mark(int cls, cudaStream_t stream, bool start);
         if (::frx::g_profile_on) ::frx::profile_mark(cls, stream, false); \
     } while (0)
 
+// Programmatic dependent launch: a kernel launched with launch_pdl may begin (be scheduled, run its
+// prologue) while the kernel before it in the stream is still running; it must call pdl_wait()
+// before it reads or writes anything the earlier kernels touch. pdl_wait() returns once those
+// kernels have completed and their writes are visible; without the launch attribute it is a no-op.
+// Every kernel of a chain calls it first thing, so completion is transitive along the chain.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Device-side error codes written to a workspace's status word.
 enum : int {
     kDevOk = 0,

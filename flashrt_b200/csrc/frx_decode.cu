@@ -109,6 +109,8 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  get sum((q - 1) * code) exactly.
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
                                                     float* __restrict__ a, float* __restrict__ c) {
+    pdl_wait();
+    pdl_trigger();
     const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= n_blocks) return;
@@ -135,9 +137,12 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
                                                 const uint8_t* __restrict__ experts, size_t stride,
                                                 const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                 int* __restrict__ status, int32_t* __restrict__ order, int max_items) {
-    extern __shared__ unsigned long long mask[];   // [E] tokens routed to each expert
+    extern __shared__ unsigned long long mask[];   // [E] tokens routed to each expert, then the ids [T * K]
     __shared__ int scan[1024];
+    pdl_wait();
+    pdl_trigger();
     const int tid = threadIdx.x;
+    int32_t* sid = reinterpret_cast<int32_t*>(mask + E);   // the ids, read many times below
     if (tid == 0 && status[3] != kCookie) {   // first use of this workspace
         status[0] = kDevOk;
         status[2] = 0;
@@ -147,6 +152,7 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
     __syncthreads();
     for (int s = tid; s < T * K; s += 1024) {
         const int e = ids[s];
+        sid[s] = e;
         if (e < 0 || e >= E) {
             status[0] = kDevBadExpertId;
             status[2] = s;
@@ -187,7 +193,7 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
                 const int t = __ffsll((long long)bits) - 1;
                 bits &= bits - 1;
                 int k = 0;
-                while (k < K - 1 && ids[t * K + k] != e) ++k;
+                while (k < K - 1 && sid[t * K + k] != e) ++k;
                 it.slot[m] = t * K + k;
                 ++m;
             }
@@ -207,19 +213,19 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
     }
     if (tid == 0) status[1] = routed_items + shared_items;
     if (tid < T) {   // slots of token tid by ascending expert id (insertion sort, K <= 32)
-        int32_t* o = order + tid * K;
+        int o[32];
         for (int k = 0; k < K; ++k) {
-            const int e = ids[tid * K + k];
+            const int e = sid[tid * K + k];
             int j = k;
-            while (j > 0 && ids[o[j - 1]] > e) {
+            while (j > 0 && sid[o[j - 1]] > e) {
                 o[j] = o[j - 1];
                 --j;
             }
             o[j] = tid * K + k;
         }
         for (int k = 0; k < K; ++k) {   // slots of experts held elsewhere take no part in this rank's sum
-            const int e = ids[o[k]];
-            if (e < e_lo || e >= e_hi) o[k] = -1 - o[k];
+            const int e = sid[o[k]];
+            order[tid * K + k] = (e < e_lo || e >= e_hi) ? -1 - o[k] : o[k];
         }
     }
 }
@@ -351,6 +357,8 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int
 template <bool GATE_UP, int NW, int UPC>
 __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_wait();
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
@@ -549,6 +557,8 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
 __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out, const float* __restrict__ y,
                                                          const float* __restrict__ wts, const int32_t* __restrict__ order,
                                                          const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (i >= n) return;
     float acc = 0.0f;
@@ -693,9 +703,9 @@ void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_
     const int sms = sm_count();
     constexpr int kFixed = GATE_UP ? 8 : 4;   // the benchmark shapes: n = 2048 in two chunks, ff = 512
     if (upc == kFixed)
-        k_stream<GATE_UP, NW, kFixed><<<sms, NW * 32, smem, stream>>>(p);
+        launch_pdl(k_stream<GATE_UP, NW, kFixed>, dim3(sms), dim3(NW * 32), smem, stream, p);
     else
-        k_stream<GATE_UP, NW, 0><<<sms, NW * 32, smem, stream>>>(p);
+        launch_pdl(k_stream<GATE_UP, NW, 0>, dim3(sms), dim3(NW * 32), smem, stream, p);
 }
 
 template <bool GATE_UP>
@@ -740,7 +750,7 @@ struct ActBufs {
 // (The grouping kernel that fills p.items may be enqueued before or after the first quantizer.)
 void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaStream_t stream) {
     const size_t nblk = size_t(x_rows) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_quant_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, n, nblk, xb.q, xb.a, xb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c));
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
@@ -751,7 +761,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_quant_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(p.h, p.ff, nblk, hb.q, hb.a, hb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, (const float*)p.h, p.ff, nblk, hb.q, hb.a, hb.c));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.aq = hb.q;
@@ -830,8 +840,9 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
         const float* xc = x + size_t(t0) * n;
         const int32_t* idc = ids + size_t(t0) * K;
         launch_quant_x(xc, Tc, n, act_x(base, L), stream);
-        FRX_LAUNCH(kKGroup, stream, k_group<<<1, 1024, size_t(E) * 8, stream>>>(idc, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
-                                                    static_cast<const uint8_t*>(shared), items, status, order, L.max_items));
+        FRX_LAUNCH(kKGroup, stream, launch_pdl(k_group, dim3(1), dim3(1024), size_t(E) * 8 + size_t(Tc) * K * 4, stream, idc, Tc, K, E, e_lo, e_hi,
+                                                       static_cast<const uint8_t*>(experts), stride, static_cast<const uint8_t*>(shared), items, status, order,
+                                                       L.max_items));
         StreamParams p{};
         p.items = items;
         p.status = status;
@@ -843,9 +854,9 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
         p.K = K;
         p.TK = Tc * K;
         launch_ffn(p, act_x(base, L), act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
-        FRX_LAUNCH(kKCombine, stream, k_combine_ordered<<<dim3((n + 255) / 256, Tc), 256, 0, stream>>>(out + size_t(t0) * n, p.y, wts + size_t(t0) * K, order,
-                                                                        shared ? p.ysh : nullptr,
-                                                                        gate_logit ? gate_logit + t0 : nullptr, n, K));
+        FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
+                                                        wts + size_t(t0) * K, (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
+                                                        gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
     }
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;

@@ -21,6 +21,8 @@ __device__ __forceinline__ float key_value(uint32_t k) { return __uint_as_float(
 template <int V>   // logits per lane: E <= 32 * V
 __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ logits, int T, int E, int K, int32_t* __restrict__ ids,
                                                     float* __restrict__ wts, uint32_t* counts, uint32_t* tail, int tail_from) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float* l = logits + size_t(t) * E;
@@ -46,12 +48,12 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     const double sum = part;
 
-    float wsum = 0.0f, my_p = 0.0f;
+    // selection: K rounds on the integer keys only; lane k remembers the k-th winner
+    uint32_t my_key = 0;
     int my_id = 0;
     for (int k = 0; k < K; ++k) {
         const uint32_t top = __reduce_max_sync(0xffffffffu, best);
         const int sel = __reduce_min_sync(0xffffffffu, best == top ? best_i : 0x7fffffff);
-        const float p = float(double(expf(key_value(top) - m)) / sum);
         if ((sel & 31) == lane) {   // the owner retires it and finds its next best
             best = 0;
             best_i = 0x7fffffff;
@@ -65,11 +67,14 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
             }
         }
         if (lane == k) {
-            my_p = p;
+            my_key = top;
             my_id = sel;
         }
-        wsum += p;
     }
+    // probabilities of the winners, all lanes at once; their sum in selection order (lane order)
+    const float my_p = lane < K ? float(double(expf(key_value(my_key) - m)) / sum) : 0.0f;
+    float wsum = 0.0f;
+    for (int k = 0; k < K; ++k) wsum += __shfl_sync(0xffffffffu, my_p, k);
     wsum = fmaxf(wsum, 6.103515625e-5f);
     if (lane < K) {
         ids[size_t(t) * K + lane] = my_id;
@@ -92,11 +97,11 @@ extern "C" int frx_route_topk(frx_stream_t stream, const float* logits, int T, i
     if (T == 0) return FRX_OK;
     const unsigned grid = unsigned((T + 7) / 8);
     if (E <= 128)
-        FRX_LAUNCH(kKRoute, stream, k_route_topk<4><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
+        FRX_LAUNCH(kKRoute, stream, launch_pdl(k_route_topk<4>, dim3(grid), dim3(256), 0, stream, logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     else if (E <= 512)
-        FRX_LAUNCH(kKRoute, stream, k_route_topk<16><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
+        FRX_LAUNCH(kKRoute, stream, launch_pdl(k_route_topk<16>, dim3(grid), dim3(256), 0, stream, logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     else
-        FRX_LAUNCH(kKRoute, stream, k_route_topk<32><<<grid, 256, 0, stream>>>(logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
+        FRX_LAUNCH(kKRoute, stream, launch_pdl(k_route_topk<32>, dim3(grid), dim3(256), 0, stream, logits, T, E, k, ids, wts, counts, tail_counts, tail_from));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }
