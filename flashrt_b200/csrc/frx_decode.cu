@@ -104,8 +104,8 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  block b for its token in one 16-byte load;
 //   a [row][k/32]  the block scale d (through fp16), divided by 16 for the second half of a
 //                  64-block (see group_mma);
-//   c [row][k/32]  kMagic + sum(codes) as a float (the sum times 16 for the second half): what is
-//                  subtracted from an accumulator that started at kMagicBits, read as a float, to
+//   c [row][k/32]  -(kMagic + sum(codes)) as a float (the sum times 16 for the second half): what is
+//                  added to an accumulator that started at kMagicBits, read as a float, to
 //                  get sum((q - 1) * code) exactly.
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
                                                     float* __restrict__ a, float* __restrict__ c) {
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
     q[row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
     if (lane == 0) {
         a[blk] = s ? d * 0.0625f : d;
-        c[blk] = kMagic + float(s ? 16 * sum : sum);
+        c[blk] = -(kMagic + float(s ? 16 * sum : sum));
     }
 }
 
@@ -232,12 +232,14 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
 
 // ---------------------------------------------------------------------------------------------
 // The streaming expert kernel, used for both halves of the FFN.
-//   GATE_UP: a task is one gate/up group (8 gate + 8 up rows over K = n); the activations are the
+//   GATE_UP: a task is two gate/up groups (each 8 gate + 8 up rows over K = n); the activations are the
 //            Q8 form of x; the epilogue is SwiGLU and a float store of the hidden value.
 //   else   : a task is kDownGroups down groups (16 rows each over K = ff); the activations are
 //            the Q8 form of the hidden rows; the epilogue stores the expert's output rows.
-// A task is one contiguous byte range of an expert blob. It is fetched as `cpt` equal chunks
-// (two when the task splits evenly, else one), each by one TMA bulk copy into a ring slot.
+// A task is one contiguous byte range of an expert blob, fetched as `cpt` chunks into ring slots:
+// a down chunk is a run of whole groups (one TMA bulk copy); a gate/up chunk is the same K range
+// of the task's two groups (two bulk copies on one barrier). A warp walks K once for a pair of
+// groups, so the activation fragments, scales and biases of a block are read once per 32 rows.
 // Task i of a block belongs to warp i % NW. Every warp owns `rpw` ring slots and is its own
 // producer: it issues the copy of a later chunk into a slot as soon as it has finished with the
 // chunk that was there, so slots are filled and drained strictly in order (a warp never waits on
@@ -256,39 +258,35 @@ struct StreamParams {
     float* y;          // [T*K][n]      routed slots (down)
     float* ysh;        // [T][n]        shared-expert slots (down)
     int n, ff, K, TK;
-    int cpt;           // chunks per task (1 or 2)
+    int cpt;           // chunks per task
     int rpw;           // ring slots per consumer warp
+    int nbuf;          // item buffers (2 or 3)
 };
 
-// Shared-memory plan of k_stream.
+// Shared-memory plan of k_stream. The activation operand of an item (fragments, scales, biases,
+// the item header) lives in one of `nbuf` buffers.
+constexpr int kMaxItemBufs = 3;
 struct SmemPlan {
-    uint32_t ring, bfrag[2], da[2], ci[2], item[2], bars, abort, total;
+    uint32_t ring, bfrag, da, ci, item, bars, abort, total;   // bfrag, da, ci, item: buffer 0; buffer b follows at b * its size
 };
-__host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, int slots) {
+__host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, int slots, int nbuf) {
     const uint32_t nb = uint32_t(kdim / kQK);
     SmemPlan s{};
     uint32_t off = 0;
     s.ring = off;
     off += uint32_t(slots) * chunk_bytes;
     off = (off + 127u) & ~127u;
-    for (int i = 0; i < 2; ++i) {
-        s.bfrag[i] = off;
-        off += nb * 512;   // [block][lane] uint4
-    }
-    for (int i = 0; i < 2; ++i) {
-        s.da[i] = off;
-        off += nb * 64;    // [block][t4] float4
-    }
-    for (int i = 0; i < 2; ++i) {
-        s.ci[i] = off;
-        off += nb * 64;    // [block][t4] int4
-    }
-    for (int i = 0; i < 2; ++i) {
-        s.item[i] = off;
-        off += 64;
-    }
-    s.bars = off;
-    off += uint32_t(slots) * 16;
+    s.bfrag = off;
+    off += uint32_t(nbuf) * nb * 512;   // [buffer][block][lane] uint4
+    s.da = off;
+    off += uint32_t(nbuf) * nb * 64;    // [buffer][block][t4] float4
+    s.ci = off;
+    off += uint32_t(nbuf) * nb * 64;    // [buffer][block][t4] float4
+    s.item = off;
+    off += uint32_t(nbuf) * 64;
+    s.bars = off;          // `slots` ring barriers, then kMaxItemBufs "ready" and kMaxItemBufs "done" barriers
+    off += uint32_t(slots + 2 * kMaxItemBufs) * 8;
+    off = (off + 15u) & ~15u;
     s.abort = off;
     off += 16;
     s.total = off;
@@ -304,12 +302,14 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, in
 // masked with 0x03), the second takes fields 2 and 3 *in place* (masked with 0x30, i.e. the
 // codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
 // scale table, which holds d / 16 for the second half. Every accumulator starts at kMagicBits;
-// read as a float it is kMagic + sum(q * a), and subtracting the bias table's kMagic + sum(a)
+// read as a float it is kMagic + sum(q * a), and adding the bias table's -(kMagic + sum(a))
 // (times 16 for the second half) leaves sum((q - 1) * a), exactly.
+// Two groups of 16 M rows (group 1 at units + gstride) share the activation fragments, scales and
+// biases of each block, which are read once for both.
 template <int UPC>   // units per call when known at compile time, else 0
-__device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int count, int b0, const uint4* __restrict__ bfrag,
-                                          const ulonglong2* __restrict__ da, const ulonglong2* __restrict__ ci, int lane, uint64_t& acc_lo,
-                                          uint64_t& acc_hi) {
+__device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
+                                          const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
+                                          const ulonglong2* __restrict__ ci, int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
     const int g = lane >> 2, t4 = lane & 3;
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint8_t* codes = units + lane * 16;
@@ -318,36 +318,44 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, int
     const ulonglong2* ci_p = ci + b0 * 4 + t4;
     const ulonglong2* da_p = da + b0 * 4 + t4;
     const int n_units = UPC ? UPC : count;
-#pragma unroll(UPC ? UPC : 2)
+#pragma unroll(2)
     for (int u = 0; u < n_units; ++u) {
-        const uint4 c = *reinterpret_cast<const uint4*>(codes + u * kUnitBytes);
-        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
-        const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
+        uint4 c[2];
+        uint2 sc[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            c[r] = *reinterpret_cast<const uint4*>(codes + r * gstride + u * kUnitBytes);
+            sc[r] = *reinterpret_cast<const uint2*>(scales + r * gstride + u * kUnitBytes);
+        }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const uint32_t w0 = j ? c.y : c.x, w1 = j ? c.w : c.z;
-            const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
             const int b = 2 * u + j;
             const uint4 bf = bf_p[b * 32];
             const ulonglong2 cb = ci_p[b * 4];  // {bias0[c0], bias0[c1]}, {bias1[c0], bias1[c1]}
             const ulonglong2 a = da_p[b * 4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
-            uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, kMagicBits);
-            mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, kMagicBits);
-            const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
-            const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
-            // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
-            // multiply-add rounds exactly where the reference's two statements round once.
-            const uint64_t sumi_lo = fma2(a.y, sub2(lo1, cb.y), mul2(a.x, sub2(lo0, cb.x)));
-            const uint64_t sumi_hi = fma2(a.y, sub2(hi1, cb.y), mul2(a.x, sub2(hi0, cb.x)));
-            // The weight scale is applied with scalar multiplies: a packed multiply followed by a
-            // packed add is contracted into one fused multiply-add by the assembler, which would
-            // round once where the reference rounds twice.
-            float s0, s1, s2, s3;
-            unpack2(sumi_lo, s0, s1);
-            unpack2(sumi_hi, s2, s3);
-            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
-            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint32_t w0 = j ? c[r].y : c[r].x, w1 = j ? c[r].w : c[r].z;
+                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
+                uint64_t lo0, hi0, lo1, hi1;
+                mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, kMagicBits);
+                mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, kMagicBits);
+                const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[r].x), s_hi = *reinterpret_cast<const __half2*>(&sc[r].y);
+                const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
+                const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
+                // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
+                // multiply-add rounds exactly where the reference's two statements round once.
+                const uint64_t sumi_lo = fma2(a.y, add2(lo1, cb.y), mul2(a.x, add2(lo0, cb.x)));
+                const uint64_t sumi_hi = fma2(a.y, add2(hi1, cb.y), mul2(a.x, add2(hi0, cb.x)));
+                // The weight scale is applied with scalar multiplies: a packed multiply followed by a
+                // packed add is contracted into one fused multiply-add by the assembler, which would
+                // round once where the reference rounds twice.
+                float s0, s1, s2, s3;
+                unpack2(sumi_lo, s0, s1);
+                unpack2(sumi_hi, s2, s3);
+                acc_lo[r] = add2(acc_lo[r], pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
+                acc_hi[r] = add2(acc_hi[r], pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+            }
         }
     }
 }
@@ -363,13 +371,17 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
     const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
-    const uint32_t task_bytes = GATE_UP ? group_bytes : group_bytes * kDownGroups;
+    const uint32_t task_bytes = GATE_UP ? group_bytes * 2 : group_bytes * kDownGroups;
     const int cpt = p.cpt, rpw = p.rpw;
     const uint32_t chunk_bytes = task_bytes / uint32_t(cpt);
-    const int tasks_per_expert = GATE_UP ? p.ff / 8 : p.n / 16 / kDownGroups;
+    const uint32_t half_bytes = chunk_bytes / 2;   // gate/up: one group's share of a chunk
+    const int tasks_per_expert = GATE_UP ? p.ff / 16 : p.n / 16 / kDownGroups;
     const size_t section = GATE_UP ? 0 : size_t(p.ff / 8) * (size_t(p.n / kUnitK) * kUnitBytes);
     const int slots = NW * rpw;
-    const SmemPlan sp = smem_plan(kdim, chunk_bytes, slots);
+    const int nbuf = p.nbuf;
+    const SmemPlan sp = smem_plan(kdim, chunk_bytes, slots, nbuf);
+    uint64_t* ready = reinterpret_cast<uint64_t*>(smem + sp.bars) + slots;   // ready[b]: item buffer b is built
+    uint64_t* done = ready + kMaxItemBufs;                                   // done[b]: every warp has finished with it
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + sp.bars) + warp * rpw;   // this warp's barriers
     uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;            // this warp's slots
     volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
@@ -382,6 +394,10 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
+        for (int b = 0; b < kMaxItemBufs; ++b) {
+            mbar_init(ready + b, NW);
+            mbar_init(done + b, NW);
+        }
         *abort = 0;
         mbar_fence_init();
     }
@@ -402,8 +418,14 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     auto issue_next = [&]() {   // lane 0 only
         if (is_i >= ntasks) return;
         mbar_expect_tx(full + is_slot, chunk_bytes);
-        bulk_g2s(ring + size_t(is_slot) * chunk_bytes, is_blob + size_t(is_task) * task_bytes + size_t(is_c) * chunk_bytes, chunk_bytes,
-                 full + is_slot);
+        uint8_t* dst = ring + size_t(is_slot) * chunk_bytes;
+        if (GATE_UP) {   // the same K range of the task's two groups, one after the other
+            const uint8_t* src = is_blob + size_t(is_task) * task_bytes + size_t(is_c) * half_bytes;
+            bulk_g2s(dst, src, half_bytes, full + is_slot);
+            bulk_g2s(dst + half_bytes, src + group_bytes, half_bytes, full + is_slot);
+        } else {
+            bulk_g2s(dst, is_blob + size_t(is_task) * task_bytes + size_t(is_c) * chunk_bytes, chunk_bytes, full + is_slot);
+        }
         if (++is_slot == rpw) is_slot = 0;
         if (++is_c == cpt) {
             is_c = 0;
@@ -441,11 +463,11 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
 
     auto build = [&](int q) {
         const Item* it = p.items + first_item + q;
-        const int buf = q & 1;
-        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag[buf]);
-        float* daw = reinterpret_cast<float*>(smem + sp.da[buf]);
-        float* ciw = reinterpret_cast<float*>(smem + sp.ci[buf]);
-        if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item[buf])[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
+        const int buf = q % nbuf;
+        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag + buf * (nb * 512));
+        float* daw = reinterpret_cast<float*>(smem + sp.da + buf * (nb * 64));
+        float* ciw = reinterpret_cast<float*>(smem + sp.ci + buf * (nb * 64));
+        if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
         const int m = it->n_tok;
         // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
         constexpr int NT = NW * 32;
@@ -481,16 +503,25 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         }
     };
 
-    build(0);
-    __syncthreads();
+    // Items are pipelined through the buffers without block-wide barriers: a warp that has finished
+    // its tasks of item q builds its share of item q + nbuf - 1 (into the buffer item q - 1 used, once
+    // every warp has left that item) and goes on to item q + 1 as soon as all shares of it are in.
+    // With three buffers a warp can run one item ahead of the slowest warp.
+    const int ahead = nbuf - 1;
+    for (int q = 0; q < ahead && q < nseg; ++q) {
+        build(q);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready + q % nbuf);
+    }
     for (int q = 0; q < nseg; ++q) {
-        const int item = first_item + q, buf = q & 1;
+        const int item = first_item + q, buf = q % nbuf;
+        mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort);
         const long long seg_lo = max(lo, (long long)item * tasks_per_expert);
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
-        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag[buf]);
-        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da[buf]);
-        const ulonglong2* ci = reinterpret_cast<const ulonglong2*>(smem + sp.ci[buf]);
-        const Item* its = reinterpret_cast<const Item*>(smem + sp.item[buf]);
+        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
+        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da + buf * (nb * 64));
+        const ulonglong2* ci = reinterpret_cast<const ulonglong2*>(smem + sp.ci + buf * (nb * 64));
+        const Item* its = reinterpret_cast<const Item*>(smem + sp.item + buf * 64);
         const int m = its->n_tok;
         const int g = lane >> 2, t4 = lane & 3;
         const int c0 = 2 * t4, c1 = 2 * t4 + 1;
@@ -498,51 +529,71 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         for (long long tau = lo + first; tau < seg_hi; tau += NW) {
             const int task = int(tau % tasks_per_expert);
             if (GATE_UP) {
-                uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
+                uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};   // {0.0f, 0.0f}
                 const int upc = units / cpt;
                 for (int c = 0; c < cpt; ++c) {
                     const uint8_t* cp = chunk_wait();
-                    units_mma<UPC>(cp, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
+                    units_mma<UPC>(cp, half_bytes, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
                     chunk_done();
                 }
-                float sum[4];
-                unpack2(acc_lo, sum[0], sum[1]);
-                unpack2(acc_hi, sum[2], sum[3]);
-                const int row = task * 8 + g;
-                if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
-                if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float sum[4];
+                    unpack2(acc_lo[r], sum[0], sum[1]);
+                    unpack2(acc_hi[r], sum[2], sum[3]);
+                    const int row = (task * 2 + r) * 8 + g;
+                    if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
+                    if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
+                }
             } else {
                 const int gpc = kDownGroups / cpt;   // groups per chunk
                 for (int c = 0; c < cpt; ++c) {
                     const uint8_t* cp = chunk_wait();
 #pragma unroll 1
-                    for (int gd = 0; gd < gpc; ++gd) {
-                        uint64_t acc_lo = 0ull, acc_hi = 0ull;
-                        units_mma<UPC>(cp + size_t(gd) * group_bytes, units, 0, bfrag, da, ci, lane, acc_lo, acc_hi);
-                        float sum[4];
-                        unpack2(acc_lo, sum[0], sum[1]);
-                        unpack2(acc_hi, sum[2], sum[3]);
-                        const int row = ((task * cpt + c) * gpc + gd) * 16 + g;
+                    for (int gd = 0; gd < gpc; gd += 2) {   // gpc is even
+                        uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};
+                        units_mma<UPC>(cp + size_t(gd) * group_bytes, group_bytes, units, 0, bfrag, da, ci, lane, acc_lo, acc_hi);
+                        float* o0 = nullptr;
+                        float* o1 = nullptr;
                         if (c0 < m) {
                             const int sl = its->slot[c0];
-                            float* o = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                            o[row] = sum[0];
-                            o[row + 8] = sum[2];
+                            o0 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
                         }
                         if (c1 < m) {
                             const int sl = its->slot[c1];
-                            float* o = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                            o[row] = sum[1];
-                            o[row + 8] = sum[3];
+                            o1 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            float sum[4];
+                            unpack2(acc_lo[r], sum[0], sum[1]);
+                            unpack2(acc_hi[r], sum[2], sum[3]);
+                            const int row = ((task * cpt + c) * gpc + gd + r) * 16 + g;
+                            if (o0) {
+                                o0[row] = sum[0];
+                                o0[row + 8] = sum[2];
+                            }
+                            if (o1) {
+                                o1[row] = sum[1];
+                                o1[row + 8] = sum[3];
+                            }
                         }
                     }
                     chunk_done();
                 }
             }
         }
-        if (q + 1 < nseg) build(q + 1);
-        __syncthreads();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(done + buf);
+        if (q + ahead < nseg) {
+            const int nxt = (q + ahead) % nbuf;   // the buffer of item q - 1
+            if (q >= 1) mbar_wait_bounded(done + nxt, uint32_t((q - 1) / nbuf) & 1u, abort);
+            build(q + ahead);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready + nxt);
+        }
     }
+    __syncthreads();
     if (*abort) {
         // A wait ran out: report it, and give copies still in flight time to land before the
         // block's shared memory is released.
@@ -670,30 +721,35 @@ struct StreamCfg {
     int nw_gu = 8, nw_dn = 8;     // warps per block
     int cpt_gu = 1, cpt_dn = 1;   // chunks per task
     int rpw_gu = 2, rpw_dn = 2;   // ring slots per warp
+    int nbuf_gu = 2, nbuf_dn = 2; // item buffers
     uint32_t smem_gu = 0, smem_dn = 0;
 };
 
 int stream_cfg(int n, int ff, StreamCfg& c) {
     const int budget = max_smem_optin() - 1024;
     if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
-    // a task is fetched as two chunks when it splits evenly; the preferred warp count is kept if
+    // a task is fetched as `chunks` chunks; the preferred warp count is kept if
     // every warp can have at least two ring slots (up to four), else fewer warps are used
-    auto fit = [&](int kdim, uint32_t task_bytes, bool even, int& nw, int& cpt, int& rpw, uint32_t& bytes) {
-        cpt = even ? 2 : 1;
+    // and, first of all, three item buffers rather than two
+    auto fit = [&](int kdim, uint32_t task_bytes, int chunks, int& nw, int& cpt, int& rpw, int& nbuf, uint32_t& bytes) {
+        cpt = chunks;
         const uint32_t chunk = task_bytes / uint32_t(cpt);
         const int prefs[3] = {g_nw, g_nw > 12 ? 12 : 8, 8};
         for (int k = 0; k < 3; ++k) {
             nw = prefs[k];
-            for (rpw = 4; rpw >= 2; --rpw) {
-                bytes = smem_plan(kdim, chunk, nw * rpw).total;
-                if (int(bytes) <= budget) return true;
-            }
+            for (nbuf = kMaxItemBufs; nbuf >= 2; --nbuf)
+                for (rpw = 4; rpw >= 2; --rpw) {
+                    bytes = smem_plan(kdim, chunk, nw * rpw, nbuf).total;
+                    if (int(bytes) <= budget) return true;
+                }
         }
         return false;
     };
     const int gu_units = n / kUnitK, dn_units = ff / kUnitK;
-    if (!fit(n, uint32_t(gu_units) * kUnitBytes, gu_units % 2 == 0, c.nw_gu, c.cpt_gu, c.rpw_gu, c.smem_gu) ||
-        !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, true, c.nw_dn, c.cpt_dn, c.rpw_dn, c.smem_dn))
+    // gate/up: a task is two groups, fetched in K slices; down: kDownGroups groups in two chunks of whole groups
+    const int gu_chunks = gu_units % 4 == 0 ? 4 : gu_units % 2 == 0 ? 2 : 1;
+    if (!fit(n, uint32_t(gu_units) * kUnitBytes * 2, gu_chunks, c.nw_gu, c.cpt_gu, c.rpw_gu, c.nbuf_gu, c.smem_gu) ||
+        !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, 2, c.nw_dn, c.cpt_dn, c.rpw_dn, c.nbuf_dn, c.smem_dn))
         return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
     return FRX_OK;
 }
@@ -701,7 +757,7 @@ int stream_cfg(int n, int ff, StreamCfg& c) {
 template <bool GATE_UP, int NW>
 void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_t stream) {
     const int sms = sm_count();
-    constexpr int kFixed = GATE_UP ? 8 : 4;   // the benchmark shapes: n = 2048 in two chunks, ff = 512
+    constexpr int kFixed = 4;   // the benchmark shapes: n = 2048 in four chunks, ff = 512
     if (upc == kFixed)
         launch_pdl(k_stream<GATE_UP, NW, kFixed>, dim3(sms), dim3(NW * 32), smem, stream, p);
     else
@@ -728,11 +784,11 @@ int set_smem_attr() {
     if (dev >= 0 && dev < 64 && done[dev]) return FRX_OK;
     const int lim = max_smem_optin();
     const void* fns[] = {
-        reinterpret_cast<const void*>(k_stream<true, 8, 8>),   reinterpret_cast<const void*>(k_stream<true, 8, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 8, 4>),   reinterpret_cast<const void*>(k_stream<true, 8, 0>),
         reinterpret_cast<const void*>(k_stream<false, 8, 4>),  reinterpret_cast<const void*>(k_stream<false, 8, 0>),
-        reinterpret_cast<const void*>(k_stream<true, 12, 8>),  reinterpret_cast<const void*>(k_stream<true, 12, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 12, 4>),  reinterpret_cast<const void*>(k_stream<true, 12, 0>),
         reinterpret_cast<const void*>(k_stream<false, 12, 4>), reinterpret_cast<const void*>(k_stream<false, 12, 0>),
-        reinterpret_cast<const void*>(k_stream<true, 16, 8>),  reinterpret_cast<const void*>(k_stream<true, 16, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 16, 4>),  reinterpret_cast<const void*>(k_stream<true, 16, 0>),
         reinterpret_cast<const void*>(k_stream<false, 16, 4>), reinterpret_cast<const void*>(k_stream<false, 16, 0>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (dev >= 0 && dev < 64) done[dev] = true;
@@ -756,6 +812,7 @@ void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaSt
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
     p.cpt = cfg.cpt_gu;
     p.rpw = cfg.rpw_gu;
+    p.nbuf = cfg.nbuf_gu;
     p.aq = xb.q;
     p.aa = xb.a;
     p.ac = xb.c;
@@ -764,6 +821,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, (const float*)p.h, p.ff, nblk, hb.q, hb.a, hb.c));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
+    p.nbuf = cfg.nbuf_dn;
     p.aq = hb.q;
     p.aa = hb.a;
     p.ac = hb.c;
