@@ -258,10 +258,9 @@ def run_frx(args):
         ms = float(t.item())
     moe.workspace_status(ws)
     value = B * L / (ms * 1e-3)
-    launches_per_layer = 7   # route, quantize x, group, gate/up, quantize hidden, down, combine (the all-reduce is NCCL's)
 
     # ---- per-kernel device time: CUDA events around every launch, the same K steps without the graph
-    ncls = 7
+    ncls = 8
     pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
     moe.check(moe.lib.frx_profile_begin())
     for _ in range(args.steps):
@@ -349,7 +348,7 @@ def run_frx(args):
                        "batch": B, "layers_per_step": L, "l2": "inputs larger than L2: 48 distinct layers, 21.8 GB of experts",
                        "distinct_experts_per_layer_mean": float(np.mean(distinct)), "parallelism": f"ep{world}",
                        "cuda_graph": use_graph},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_layer * L * args.steps, "kernels": kernels,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": sum(v["launches"] for v in kernels.values()), "kernels": kernels,
             "roofline": roofline, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
@@ -428,7 +427,7 @@ def run_prefill(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ncls = 7
+    ncls = 8
     pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
     moe.check(moe.lib.frx_profile_begin())
     for _ in range(args.steps):

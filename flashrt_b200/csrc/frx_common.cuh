@@ -47,7 +47,7 @@ int max_smem_optin();
 
 // Optional per-kernel timing (frx_profile_begin / frx_profile_end): when switched on, every
 // launch made through FRX_LAUNCH is bracketed by two CUDA events on its own stream.
-enum KernelClass : int { kKRoute = 0, kKQuant, kKGroup, kKGateUp, kKDown, kKCombine, kKLayout, kNumKernelClasses };
+enum KernelClass : int { kKRoute = 0, kKQuant, kKGroup, kKGateUp, kKDown, kKCombine, kKLayout, kKPrologue, kNumKernelClasses };
 extern bool g_profile_on;
 void profile_mark(int cls, cudaStream_t stream, bool start);
 #define FRX_LAUNCH(cls, stream, ...)                                   \
@@ -78,6 +78,42 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The same with thread-block clusters of `cluster` blocks along x (grid.x a multiple of it).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster,
+                                      Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2]{};
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+// Hardware barrier over all threads of the cluster; writes made before it (global memory
+// included) are visible to the cluster's threads after it.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // Device-side error codes written to a workspace's status word.

@@ -6,6 +6,7 @@
 // the blocks of a row run in one lane, in block order, with the roundings of the reference's
 // scalar matvec (quant/q2_0/q2_0.cpp:119-140), so results match it bit for bit.
 #include "frx_common.cuh"
+#include "frx_route.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -107,13 +108,8 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //   c [row][k/32]  -(kMagic + sum(codes)) as a float (the sum times 16 for the second half): what is
 //                  added to an accumulator that started at kMagicBits, read as a float, to
 //                  get sum((q - 1) * code) exactly.
-__global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
-                                                    float* __restrict__ a, float* __restrict__ c) {
-    pdl_wait();
-    pdl_trigger();
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (blk >= n_blocks) return;
+__device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
+                                                 float* __restrict__ a, float* __restrict__ c) {
     float d;
     int sum;
     const int code = q8_block(x[blk * kQ8 + lane], d, sum);
@@ -126,22 +122,28 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
         c[blk] = -(kMagic + float(s ? 16 * sum : sum));
     }
 }
+__global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
+                                                    float* __restrict__ a, float* __restrict__ c) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (blk < n_blocks) quant_frag_block(x, k, blk, threadIdx.x & 31, q, a, c);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Grouping: the distinct experts of up to 64 tokens in ascending id, each with its tokens in
 // token order, cut into items of at most 8 tokens; then the shared expert's items; and per token
 // the order in which its slots are summed (ascending expert id, the order in which the
-// reference's CPU path adds them, quant/q2_0/moe_cpu.cpp:70-79). One block, no atomics on data:
-// the result does not depend on thread timing.
-__global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids, int T, int K, int E, int e_lo, int e_hi,
-                                                const uint8_t* __restrict__ experts, size_t stride,
-                                                const uint8_t* __restrict__ shared, Item* __restrict__ items,
-                                                int* __restrict__ status, int32_t* __restrict__ order, int max_items) {
-    extern __shared__ unsigned long long mask[];   // [E] tokens routed to each expert, then the ids [T * K]
-    __shared__ int scan[1024];
-    pdl_wait();
-    pdl_trigger();
-    const int tid = threadIdx.x;
+// reference's CPU path adds them, quant/q2_0/moe_cpu.cpp:70-79). One block of 1024 threads, no
+// atomics on data: the result does not depend on thread timing.
+// dyn: dynamic shared memory of E * 8 + T * K * 4 bytes.
+__device__ __forceinline__ void group_block(unsigned long long* dyn, const int32_t* __restrict__ ids, int T, int K, int E, int e_lo,
+                                            int e_hi, const uint8_t* __restrict__ experts, size_t stride,
+                                            const uint8_t* __restrict__ shared, Item* __restrict__ items, int* __restrict__ status,
+                                            int32_t* __restrict__ order, int max_items) {
+    unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K]
+    __shared__ int warp_tot[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int32_t* sid = reinterpret_cast<int32_t*>(mask + E);   // the ids, read many times below
     if (tid == 0 && status[3] != kCookie) {   // first use of this workspace
         status[0] = kDevOk;
@@ -164,16 +166,26 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
     const int per = (E + 1023) / 1024, e0 = tid * per, e1 = min(E, e0 + per);
     int cnt = 0;
     for (int e = e0; e < e1; ++e) cnt += (__popcll(mask[e]) + kTokPerItem - 1) / kTokPerItem;
-    scan[tid] = cnt;
-    __syncthreads();
-    for (int o = 1; o < 1024; o <<= 1) {   // inclusive scan
-        const int v = tid >= o ? scan[tid - o] : 0;
-        __syncthreads();
-        scan[tid] += v;
-        __syncthreads();
+    int inc = cnt;   // inclusive scan over the block: within the warp, then over the warp totals
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
     }
-    int at = scan[tid] - cnt;
-    const int routed_items = scan[1023];
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_tot[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        warp_tot[lane] = w;
+    }
+    __syncthreads();
+    int at = inc - cnt + (warp ? warp_tot[warp - 1] : 0);
+    const int routed_items = warp_tot[31];
     const int shared_items = shared ? (T + kTokPerItem - 1) / kTokPerItem : 0;
     if (routed_items + shared_items > max_items) {
         if (tid == 0) {
@@ -212,22 +224,48 @@ __global__ void __launch_bounds__(1024) k_group(const int32_t* __restrict__ ids,
         items[routed_items + tid] = it;
     }
     if (tid == 0) status[1] = routed_items + shared_items;
-    if (tid < T) {   // slots of token tid by ascending expert id (insertion sort, K <= 32)
-        int o[32];
-        for (int k = 0; k < K; ++k) {
-            const int e = sid[tid * K + k];
-            int j = k;
-            while (j > 0 && sid[o[j - 1]] > e) {
-                o[j] = o[j - 1];
-                --j;
-            }
-            o[j] = tid * K + k;
+    // Slots of a token by ascending expert id: slot s takes the place given by the number of the
+    // token's slots that come before it (smaller id, or the same id and a smaller k).
+    for (int s = tid; s < T * K; s += 1024) {
+        const int t = s / K, k = s - t * K, e = sid[s];
+        int rank = 0;
+        for (int j = 0; j < K; ++j) {
+            const int ej = sid[t * K + j];
+            rank += (ej < e || (ej == e && j < k)) ? 1 : 0;
         }
-        for (int k = 0; k < K; ++k) {   // slots of experts held elsewhere take no part in this rank's sum
-            const int e = sid[o[k]];
-            order[tid * K + k] = (e < e_lo || e >= e_hi) ? -1 - o[k] : o[k];
-        }
+        order[t * K + rank] = (e < e_lo || e >= e_hi) ? -1 - s : s;   // slots of experts held elsewhere take no part in this rank's sum
     }
+}
+
+// The head of a decode step, one launch of clusters of kHeadCluster blocks. Cluster 0 routes the
+// tokens (when given the router's logits; token t by warp t / kHeadCluster of block
+// t % kHeadCluster), meets at the cluster's hardware barrier, and its block 0 groups the tokens
+// into work items. All other blocks quantize x into the expert kernel's activation form; the two
+// halves do not depend on each other.
+constexpr int kHeadCluster = 8;
+template <int V>   // router: logits per lane, E <= 32 * V; 0: no router
+__global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ wts,
+                                                   int T, int K, int E, int e_lo, int e_hi, const uint8_t* __restrict__ experts,
+                                                   size_t stride, const uint8_t* __restrict__ shared, Item* __restrict__ items,
+                                                   int* __restrict__ status, int32_t* __restrict__ order, int max_items,
+                                                   const float* __restrict__ x, int n, size_t n_blocks, int8_t* __restrict__ xq,
+                                                   float* __restrict__ xa, float* __restrict__ xc) {
+    extern __shared__ unsigned long long dyn[];
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (blockIdx.x >= kHeadCluster) {
+        const size_t qb = blockIdx.x - kHeadCluster, nqb = gridDim.x - kHeadCluster;
+        for (size_t blk = qb * 32 + warp; blk < n_blocks; blk += nqb * 32) quant_frag_block(x, n, blk, lane, xq, xa, xc);
+        return;
+    }
+    const int rank = int(cluster_ctarank());   // cluster 0 is blocks 0 .. kHeadCluster - 1
+    if constexpr (V > 0) {
+        for (int t = warp * kHeadCluster + rank; t < T; t += 32 * kHeadCluster)
+            route_warp<V>(logits + size_t(t) * E, E, K, lane, ids + size_t(t) * K, wts + size_t(t) * K, nullptr, nullptr);
+    }
+    cluster_sync_all();   // every block's ids are visible to block 0
+    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -844,6 +882,72 @@ int check_moe_shape(const char* who, int n, int ff, int K) {
     return FRX_OK;
 }
 
+// The decode layer over T tokens, 64 at a time: head (route when `logits` is given, group,
+// quantize x), gate/up + SwiGLU, quantize the hidden rows, down, combine. With `logits` the ids
+// and weights are outputs, else inputs.
+int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff, const float* x,
+                 const float* logits, int32_t* ids, float* wts, const float* gate_logit, int T, int K, float* out, float* yslot, void* ws,
+                 size_t ws_bytes, cudaStream_t stream) {
+    if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
+    if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
+    if (e_lo < 0 || e_hi > E || e_lo > e_hi) return fail(FRX_ERR_ARG, "frx_moe_decode: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
+    if (int rc = check_moe_shape("frx_moe_decode", n, ff, K)) return rc;
+    if (logits && (E > 1024 || K > E)) return fail(FRX_ERR_SHAPE, "frx_moe_layer: unsupported router shape E %d, k %d", E, K);
+    if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
+        return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
+    if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_decode: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
+    if (T == 0) return FRX_OK;
+    const Layout L = make_layout(T, K, n, ff);
+    if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_decode: workspace %zu < %zu", ws_bytes, L.total);
+    StreamCfg cfg;
+    if (int rc = stream_cfg(n, ff, cfg)) return rc;
+    if (int rc = set_smem_attr()) return rc;
+    auto* base = static_cast<uint8_t*>(ws);
+    int* status = reinterpret_cast<int*>(base + L.status);
+    Item* items = reinterpret_cast<Item*>(base + L.items);
+    int32_t* order = reinterpret_cast<int32_t*>(base + L.order);
+    const int sms = sm_count();
+
+    for (int t0 = 0; t0 < T; t0 += kMaxChunkTokens) {
+        const int Tc = T - t0 < kMaxChunkTokens ? T - t0 : kMaxChunkTokens;
+        const ActBufs xb = act_x(base, L);
+        const size_t nblk = size_t(Tc) * (n / kQ8);
+        const unsigned want = unsigned(std::min<size_t>((nblk + 31) / 32, size_t(sms)));
+        const unsigned qblocks = (want + kHeadCluster - 1) / kHeadCluster * kHeadCluster;
+        const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4;
+        auto head = [&](auto kernel) {
+            return launch_pdl_cluster(kernel, dim3(kHeadCluster + qblocks), dim3(1024), dyn, stream, kHeadCluster, logits ? logits + size_t(t0) * E : (const float*)nullptr,
+                              ids + size_t(t0) * K, wts + size_t(t0) * K, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
+                              static_cast<const uint8_t*>(shared), items, status, order, L.max_items, x + size_t(t0) * n, n, nblk, xb.q, xb.a,
+                              xb.c);
+        };
+        if (!logits)
+            FRX_LAUNCH(kKPrologue, stream, head(k_prologue<0>));
+        else if (E <= 128)
+            FRX_LAUNCH(kKPrologue, stream, head(k_prologue<4>));
+        else if (E <= 512)
+            FRX_LAUNCH(kKPrologue, stream, head(k_prologue<16>));
+        else
+            FRX_LAUNCH(kKPrologue, stream, head(k_prologue<32>));
+        StreamParams p{};
+        p.items = items;
+        p.status = status;
+        p.h = reinterpret_cast<float*>(base + L.h);
+        p.y = yslot ? yslot + size_t(t0) * K * n : reinterpret_cast<float*>(base + L.y);
+        p.ysh = reinterpret_cast<float*>(base + L.ysh);
+        p.n = n;
+        p.ff = ff;
+        p.K = K;
+        p.TK = Tc * K;
+        launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
+        FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
+                                                        (const float*)(wts + size_t(t0) * K), (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
+                                                        gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
+    }
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
 }  // namespace
 }  // namespace frx
 
@@ -875,49 +979,9 @@ int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared
 int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
                       const float* x, const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
                       float* yslot, void* ws, size_t ws_bytes, frx_stream_t stream) {
-    if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
-    if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
-    if (e_lo < 0 || e_hi > E || e_lo > e_hi) return fail(FRX_ERR_ARG, "frx_moe_decode: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
-    if (int rc = check_moe_shape("frx_moe_decode", n, ff, K)) return rc;
-    if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
-        return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
-    if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_decode: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
-    if (T == 0) return FRX_OK;
-    const Layout L = make_layout(T, K, n, ff);
-    if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_decode: workspace %zu < %zu", ws_bytes, L.total);
-    StreamCfg cfg;
-    if (int rc = stream_cfg(n, ff, cfg)) return rc;
-    if (int rc = set_smem_attr()) return rc;
-    auto* base = static_cast<uint8_t*>(ws);
-    int* status = reinterpret_cast<int*>(base + L.status);
-    Item* items = reinterpret_cast<Item*>(base + L.items);
-    int32_t* order = reinterpret_cast<int32_t*>(base + L.order);
-
-    for (int t0 = 0; t0 < T; t0 += kMaxChunkTokens) {
-        const int Tc = T - t0 < kMaxChunkTokens ? T - t0 : kMaxChunkTokens;
-        const float* xc = x + size_t(t0) * n;
-        const int32_t* idc = ids + size_t(t0) * K;
-        launch_quant_x(xc, Tc, n, act_x(base, L), stream);
-        FRX_LAUNCH(kKGroup, stream, launch_pdl(k_group, dim3(1), dim3(1024), size_t(E) * 8 + size_t(Tc) * K * 4, stream, idc, Tc, K, E, e_lo, e_hi,
-                                                       static_cast<const uint8_t*>(experts), stride, static_cast<const uint8_t*>(shared), items, status, order,
-                                                       L.max_items));
-        StreamParams p{};
-        p.items = items;
-        p.status = status;
-        p.h = reinterpret_cast<float*>(base + L.h);
-        p.y = yslot ? yslot + size_t(t0) * K * n : reinterpret_cast<float*>(base + L.y);
-        p.ysh = reinterpret_cast<float*>(base + L.ysh);
-        p.n = n;
-        p.ff = ff;
-        p.K = K;
-        p.TK = Tc * K;
-        launch_ffn(p, act_x(base, L), act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
-        FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
-                                                        wts + size_t(t0) * K, (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
-                                                        gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
-    }
-    FRX_CUDA(cudaGetLastError());
-    return FRX_OK;
+    if (!ids || !wts) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
+    return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, nullptr, const_cast<int32_t*>(ids), const_cast<float*>(wts),
+                        gate_logit, T, K, out, yslot, ws, ws_bytes, stream);
 }
 
 size_t frx_moe_layer_workspace_bytes(int T, int K, int n, int ff) {
@@ -938,8 +1002,7 @@ int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared,
     auto* base = static_cast<uint8_t*>(ws);
     int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
     float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
-    if (int rc = frx_route_topk(stream, logits, T, E, K, ids, wts, nullptr, nullptr, 1 << 30)) return rc;
-    return frx_moe_decode(experts, stride, E, shared, n, ff, x, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
+    return decode_steps(experts, stride, E, 0, E, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
 }
 
 size_t frx_moe_layer_host_workspace_bytes(int T, int K, int n, int ff, int E) {
