@@ -34,7 +34,7 @@ __host__ __device__ inline int slot_token(int slot, int K, int TK) { return slot
 
 // Workspace status words: [0] device error, [1] items of the current chunk, [2] detail, [3] cookie.
 struct Layout {
-    size_t status, items, order, xq, xa, xc, h, hq, ha, hc, y, ysh, total;
+    size_t status, items, order, xq, xa, xc, gu, h, hq, ha, hc, y, ysh, total;
     int max_items;
 };
 
@@ -54,6 +54,7 @@ Layout make_layout(int T, int K, int n, int ff) {
     L.xq = take(size_t(Tc) * n);
     L.xa = take(size_t(Tc) * (n / kQ8) * 4);
     L.xc = take(size_t(Tc) * (n / kQ8) * 4);
+    L.gu = take(size_t(Tc) * (K + 1) * ff * 8);
     L.h = take(size_t(Tc) * (K + 1) * ff * 4);
     L.hq = take(size_t(Tc) * (K + 1) * ff);
     L.ha = take(size_t(Tc) * (K + 1) * (ff / kQ8) * 4);
@@ -108,11 +109,11 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //   c [row][k/32]  -(kMagic + sum(codes)) as a float (the sum times 16 for the second half): what is
 //                  added to an accumulator that started at kMagicBits, read as a float, to
 //                  get sum((q - 1) * code) exactly.
-__device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
-                                                 float* __restrict__ a, float* __restrict__ c) {
+__device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int lane, int8_t* __restrict__ q, float* __restrict__ a,
+                                                 float* __restrict__ c) {
     float d;
     int sum;
-    const int code = q8_block(x[blk * kQ8 + lane], d, sum);
+    const int code = q8_block(v, d, sum);
     const int bpr = k / kQ8;
     const size_t row = blk / bpr;
     const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
@@ -121,6 +122,25 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
         a[blk] = s ? d * 0.0625f : d;
         c[blk] = -(kMagic + float(s ? 16 * sum : sum));
     }
+}
+__device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
+                                                 float* __restrict__ a, float* __restrict__ c) {
+    quant_frag_value(x[blk * kQ8 + lane], k, blk, lane, q, a, c);
+}
+// The hidden rows: gu holds (gate x, up x) pairs; h = silu(gate x) * up x is formed here, where
+// there are thousands of independent warps to hide the latency of the exponential, stored, and
+// quantized like x.
+__global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
+                                                      int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= n_blocks) return;
+    const float2 v = gu[blk * kQ8 + lane];
+    const float hv = swiglu_ref(v.x, v.y);
+    h[blk * kQ8 + lane] = hv;
+    quant_frag_value(hv, k, blk, lane, q, a, c);
 }
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
                                                     float* __restrict__ a, float* __restrict__ c) {
@@ -292,7 +312,8 @@ struct StreamParams {
     const int8_t* aq;
     const float* aa;
     const float* ac;
-    float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by GATE_UP
+    float2* gu;        // [slots][ff]   (gate x, up x) per hidden element, written by GATE_UP
+    float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by the quantizer of the hidden rows
     float* y;          // [T*K][n]      routed slots (down)
     float* ysh;        // [T][n]        shared-expert slots (down)
     int n, ff, K, TK;
@@ -580,8 +601,8 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                     unpack2(acc_lo[r], sum[0], sum[1]);
                     unpack2(acc_hi[r], sum[2], sum[3]);
                     const int row = (task * 2 + r) * 8 + g;
-                    if (c0 < m) p.h[size_t(its->slot[c0]) * p.ff + row] = swiglu_ref(sum[0], sum[2]);
-                    if (c1 < m) p.h[size_t(its->slot[c1]) * p.ff + row] = swiglu_ref(sum[1], sum[3]);
+                    if (c0 < m) p.gu[size_t(its->slot[c0]) * p.ff + row] = make_float2(sum[0], sum[2]);
+                    if (c1 < m) p.gu[size_t(its->slot[c1]) * p.ff + row] = make_float2(sum[1], sum[3]);
                 }
             } else {
                 const int gpc = kDownGroups / cpt;   // groups per chunk
@@ -856,7 +877,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, (const float*)p.h, p.ff, nblk, hb.q, hb.a, hb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -932,6 +953,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         StreamParams p{};
         p.items = items;
         p.status = status;
+        p.gu = reinterpret_cast<float2*>(base + L.gu);
         p.h = reinterpret_cast<float*>(base + L.h);
         p.y = yslot ? yslot + size_t(t0) * K * n : reinterpret_cast<float*>(base + L.y);
         p.ysh = reinterpret_cast<float*>(base + L.ysh);
@@ -1081,7 +1103,7 @@ size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* 
 // ---- moe_hits
 namespace {
 struct HitsLayout {
-    size_t status, items, xq, xa, xc, h, hq, ha, hc, total;
+    size_t status, items, xq, xa, xc, gu, h, hq, ha, hc, total;
 };
 HitsLayout hits_layout(int K, int n, int ff, int T) {
     HitsLayout L{};
@@ -1096,6 +1118,7 @@ HitsLayout hits_layout(int K, int n, int ff, int T) {
     L.xq = take(size_t(T) * n);
     L.xa = take(size_t(T) * (n / kQ8) * 4);
     L.xc = take(size_t(T) * (n / kQ8) * 4);
+    L.gu = take(size_t(T) * K * ff * 8);
     L.h = take(size_t(T) * K * ff * 4);
     L.hq = take(size_t(T) * K * ff);
     L.ha = take(size_t(T) * K * (ff / kQ8) * 4);
@@ -1127,6 +1150,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     StreamParams p{};
     p.items = reinterpret_cast<const Item*>(base + L.items);
     p.status = reinterpret_cast<int*>(base + L.status);
+    p.gu = reinterpret_cast<float2*>(base + L.gu);
     p.h = reinterpret_cast<float*>(base + L.h);
     p.y = yh;
     p.ysh = nullptr;
@@ -1142,7 +1166,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
 // ---- prefill-sized entry, streaming form: the general grouping feeding the same expert kernel
 namespace {
 struct PfLayout {
-    size_t status, chunk_cnt, bounds, item_off, perm, items, xq, xa, xc, h, hq, ha, hc, total;
+    size_t status, chunk_cnt, bounds, item_off, perm, items, xq, xa, xc, gu, h, hq, ha, hc, total;
     int n_chunks, max_items;
 };
 PfLayout pf_layout(int T, int K, int n, int ff, int E) {
@@ -1165,6 +1189,7 @@ PfLayout pf_layout(int T, int K, int n, int ff, int E) {
     L.xq = take(size_t(T) * n);
     L.xa = take(size_t(T) * (n / kQ8) * 4);
     L.xc = take(size_t(T) * (n / kQ8) * 4);
+    L.gu = take(S * ff * 8);
     L.h = take(S * ff * 4);
     L.hq = take(S * ff);
     L.ha = take(S * (ff / kQ8) * 4);
@@ -1210,6 +1235,7 @@ int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int
     StreamParams p{};
     p.items = items;
     p.status = status;
+    p.gu = reinterpret_cast<float2*>(base + L.gu);
     p.h = reinterpret_cast<float*>(base + L.h);
     p.y = yd;
     p.ysh = nullptr;
