@@ -148,6 +148,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a barrier phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -158,16 +170,28 @@ __device__ __forceinline__ uint64_t global_ns() {
 // `*abort` was already set; it then sets `*abort` so every later wait of the block returns at
 // once, and the caller's block finishes its control flow without trusting the data.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// SLEEP: back off with nanosleep after a few polls (right for waits on data from global memory,
+// where a waiting warp should leave the issue slots to working warps); without it the wait polls
+// try_wait, which itself suspends the thread for a short hardware-defined time (right for the
+// short hand-offs of a warp-specialised pipeline, where a sleep that overshoots delays every step).
+template <bool SLEEP = true>
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
-    const uint64_t t0 = global_ns();
+    uint64_t t0 = 0;   // the clock is only read once the wait has lasted a while: reading it is slow
     for (uint32_t polls = 1;; ++polls) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (polls > 4) __nanosleep(polls > 64 ? 256 : 32);   // a long wait must not take issue slots from working warps
+        if (SLEEP ? mbar_try_wait(bar, parity) : mbar_test_wait(bar, parity)) return true;
+        if (SLEEP) {
+            if (polls > 4) __nanosleep(polls > 64 ? 256 : 32);   // a long wait must not take issue slots from working warps
+        } else if (polls > 65536) {
+            __nanosleep(64);
+        }
         if ((polls & 63u) == 0) {
             if (*abort) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
                 *abort = 1;
                 return false;
             }
@@ -183,6 +207,10 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 
+// Non-blocking arrival at a hardware barrier that other threads bar.sync on.
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -249,8 +277,35 @@ __device__ __forceinline__ float round_half_away(float v) {
     return fabsf(f) >= 0.5f ? t + copysignf(1.0f, v) : t;
 }
 
-// Correctly rounded expf for all but a vanishing fraction of inputs: exp in double, one rounding.
-__device__ __forceinline__ float expf_cr(float x) { return float(exp(double(x))); }
+// Correctly rounded expf for all but a vanishing fraction of inputs: exp in double to about 2^-51,
+// then one rounding to float. e^x = 2^k * e^r with k = round(x / ln 2) and r = x - k ln 2
+// (ln 2 as a 32-bit head, so that k * head is exact, and a tail), |r| <= 0.347, e^r by its Taylor
+// series to r^13 / 13! (the next term is below 2^-57). Half the double-precision work of the
+// library's exp, which matters where this sits at the end of a tile. Identical to
+// float(exp(double(x))) on 5e7 random inputs checked on the host.
+__device__ __forceinline__ float expf_cr(float x) {
+    if (!(x == x)) return x;
+    const double xd = double(fminf(fmaxf(x, -110.0f), 90.0f));   // beyond: 0 or inf as a float either way
+    const double kd = rint(xd * 1.4426950408889634);
+    double r = fma(-kd, 0x1.62e42fee00000p-1, xd);
+    r = fma(-kd, 0x1.a39ef35793c76p-33, r);
+    double p = 1.0 / 6227020800.0;
+    p = fma(p, r, 1.0 / 479001600.0);
+    p = fma(p, r, 1.0 / 39916800.0);
+    p = fma(p, r, 1.0 / 3628800.0);
+    p = fma(p, r, 1.0 / 362880.0);
+    p = fma(p, r, 1.0 / 40320.0);
+    p = fma(p, r, 1.0 / 5040.0);
+    p = fma(p, r, 1.0 / 720.0);
+    p = fma(p, r, 1.0 / 120.0);
+    p = fma(p, r, 1.0 / 24.0);
+    p = fma(p, r, 1.0 / 6.0);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);
+    const double scale = __hiloint2double((__double2int_rn(kd) + 1023) << 20, 0);   // 2^k, k in [-159, 130]
+    return __double2float_rn(p * scale);
+}
 
 // silu(g) * u as the reference's CPU path writes it: g / (1 + exp(-g)) * u
 __device__ __forceinline__ float swiglu_ref(float g, float u) {

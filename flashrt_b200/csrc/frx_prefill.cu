@@ -11,9 +11,14 @@
 // sums held in registers, block after block.
 //
 // Per CTA (one per SM), warp roles: 0 = TMA producer, 1 = MMA issuer and tensor-memory owner,
-// 2-9 = dequant (2-bit codes of 128 rows x 64 weights -> fp16 core-matrix layout in shared
-// memory), 10-25 = epilogue (tensor memory -> registers, scaling, SwiGLU / output stores): each
-// epilogue warp owns 32 rows (its quarter of the tensor-memory lanes) x 32 token columns.
+// 2-3 = dequant (2-bit codes of 128 rows x 64 weights -> fp16 core-matrix layout in shared
+// memory), 4-19 = epilogue (tensor memory -> registers, scaling, stores of the (gate, up) sums or
+// the output rows): each epilogue warp owns 32 rows (its quarter of the tensor-memory lanes) x 32
+// token columns. 640 threads leave 96 registers per thread, which lets an epilogue thread fetch
+// 16 columns of both sums per round trip to tensor memory (a round trip costs several hundred
+// cycles whatever its size). Hand-offs are shared-memory barriers; a barrier operation has about a
+// hundred cycles of latency and a thread's steps are serial, so each role tests the next step's
+// barriers while it still works on the current one.
 // All waits are bounded; a wait that runs out sets the workspace status word and the block drains.
 #include "frx_umma.cuh"
 
@@ -35,9 +40,13 @@ constexpr int kStepBytesA = (kTileRows / 8) * kASbo;   // 24 KB
 constexpr int kStepBytesB = kTileTok * 64 * 2;    // fp16 B tile of one 64-block: 16 KB
 constexpr int kStepBytesS = kTileTok * 8;         // activation scales of one 64-block: 1 KB
 constexpr int kUnitTileBytes = 8 * kUnitBytes;    // packed weights of 8 groups x one unit: 4608 B
-constexpr int kStagesW = 3, kStagesA = 4, kStagesB = 4, kStagesD = 2;
-constexpr int kWarpsDequant = 8, kWarpsEpilogue = 16;
-constexpr int kThreads = (2 + kWarpsDequant + kWarpsEpilogue) * 32;   // 832
+constexpr int kStagesW = 8, kStagesA = 4, kStagesB = 4, kStagesD = 2;
+static_assert(kStagesA == kStagesB, "one barrier frees an A and a B stage together");
+constexpr int kStageColsD = 2 * kTileTok;   // tensor-memory columns of one step: the two 32-value sums of every token
+static_assert(kStagesD * kStageColsD <= 512, "tensor memory has 512 columns");
+constexpr int kWarpsDequant = 2, kWarpsEpilogue = 16;
+constexpr int kThreads = (2 + kWarpsDequant + kWarpsEpilogue) * 32;   // 640: 96 registers per thread
+constexpr int kGroupsPerDequantWarp = 8 / kWarpsDequant;             // 16-row groups of the tile per dequant warp
 
 // meta words: [0] padded positions in use, [1] token blocks
 struct PfuLayout {
@@ -74,7 +83,7 @@ PfuLayout pfu_layout(int T, int K, int n, int ff, int E) {
     L.xd = take(size_t(T) * (n / kQ8) * 4);
     L.xg = take(L.pmax * n * 2);
     L.xa = take(L.pmax * (n / kQK) * 8);
-    L.hf = take(L.pmax * ff * 4);
+    L.hf = take(L.pmax * ff * 8);   // (gate x, up x) pairs
     L.hg = take(L.pmax * ff * 2);
     L.ha = take(L.pmax * (ff / kQK) * 8);
     L.total = off;
@@ -209,21 +218,48 @@ __global__ void __launch_bounds__(256) k_pfu_quant_x(const float* __restrict__ x
 }
 
 // Q8 of the hidden rows (one row of ff per padded position) straight into the grouped fp16
-// operand layout and scale table of the down product. Warp per 32-block.
-__global__ void __launch_bounds__(256) k_pfu_quant_h(const float* __restrict__ hf, int ff, size_t pmax, const int* __restrict__ meta,
+// operand layout and scale table of the down product. A thread owns 8 consecutive hidden values
+// (one 16-byte chunk of the operand), four neighbouring lanes one 32-block: silu(gate x) * up x is
+// formed here (eight independent exponentials per thread hide their latency), the block maximum
+// comes from two shuffles, and each thread stores its chunk whole.
+__global__ void __launch_bounds__(256) k_pfu_quant_h(const float2* __restrict__ hf, int ff, size_t pmax, const int* __restrict__ meta,
                                                      const int32_t* __restrict__ pslot, uint8_t* __restrict__ hg, float* __restrict__ ha) {
-    const int bpr = ff / kQ8;
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    const size_t p = blk / bpr;
-    if (p >= size_t(meta[0])) return;
-    const int rb = int(blk % bpr), b64 = rb >> 1, s = rb & 1;
-    const bool live = pslot[p] >= 0;
-    float d = 0.0f;
-    const int code = q8_block_pf(live ? hf[p * ff + size_t(rb) * kQ8 + lane] : 0.0f, d);
-    const int k = 32 * s + lane;   // position inside the 64-block
-    *reinterpret_cast<__half*>(hg + grouped_chunk_off(pmax, b64, int(p), k >> 3) + size_t(k & 7) * 2) = __int2half_rn(code);
-    if (lane == 0) ha[grouped_scale_idx(pmax, b64, int(p), s)] = d;
+    const int cpr = ff / 8;   // chunks per row
+    const size_t chunk = size_t(blockIdx.x) * 256 + threadIdx.x;
+    const size_t p = chunk / cpr;
+    const bool in_range = p < size_t(meta[0]);   // no early exit: the shuffles below need the whole warp
+    const int c = int(chunk % cpr);              // chunk of the row: values 8 c .. 8 c + 7
+    const bool live = in_range && pslot[p] >= 0;
+    float hv[8];
+    float am = 0.0f;
+    if (live) {
+        const float4* src = reinterpret_cast<const float4*>(hf + p * ff + size_t(c) * 8);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 gu = src[i];   // (gate, up) of two hidden values
+            hv[2 * i] = swiglu_ref(gu.x, gu.y);
+            hv[2 * i + 1] = swiglu_ref(gu.z, gu.w);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(hv[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hv[i] = 0.0f;
+    }
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16
+    const float d = __fdiv_rn(am, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        h[i] = __halves2half2(__int2half_rn(int(round_half_away(__fmul_rn(hv[2 * i], id)))),
+                              __int2half_rn(int(round_half_away(__fmul_rn(hv[2 * i + 1], id)))));
+    const int b64 = c >> 3, k8 = c & 7;   // the 64-block and the chunk inside it
+    if (!in_range) return;
+    *reinterpret_cast<uint4*>(hg + grouped_chunk_off(pmax, b64, int(p), k8)) = *reinterpret_cast<const uint4*>(h);
+    if ((c & 3) == 0) ha[grouped_scale_idx(pmax, b64, int(p), k8 >> 2)] = __half2float(__float2half_rn(d));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -237,7 +273,7 @@ struct UmmaParams {
     const uint8_t* act;       // grouped fp16 codes (xg or hg)
     const float* act_scale;   // grouped block scales (xa or ha)
     const int32_t* pslot;
-    float* hf;                // gate/up: hidden values [pmax][ff]
+    float2* hf;               // gate/up: (gate x, up x) of every hidden element [pmax][ff]
     float* yd;                // down: [slots][n]
     int* status;
     size_t pmax;
@@ -262,7 +298,7 @@ __host__ __device__ constexpr PfSmem pf_smem() {
     m.sw = off;
     off += kStagesA * kTileRows * 4;
     m.bars = off;
-    off += 32 * 8;
+    off += 48 * 8;
     m.tmem = off;
     off += 16;
     m.abort = off;
@@ -276,14 +312,14 @@ enum : int {
     kBarWFull = 0,                      // + stage: packed weights of a unit have landed
     kBarWFree = kBarWFull + kStagesW,   // dequant warps are done with them
     kBarAFull = kBarWFree + kStagesW,   // fp16 A tile written
-    kBarAFree = kBarAFull + kStagesA,   // the MMAs that read it have completed and the epilogue is done with its row scales
+    kBarAFree = kBarAFull + kStagesA,   // the epilogue is done with a step's row and activation scales (and so the MMAs that
+                                        // read its A and B tiles have completed): frees the A stage and the B stage of the step
     kBarBFull = kBarAFree + kStagesA,   // fp16 B tile and activation scales have landed
-    kBarBFree = kBarBFull + kStagesB,   // MMAs completed and epilogue done with the scales
-    kBarDFull = kBarBFree + kStagesB,   // accumulators of a step are complete in tensor memory
+    kBarDFull = kBarBFull + kStagesB,   // accumulators of a step are complete in tensor memory
     kBarDFree = kBarDFull + kStagesD,   // epilogue warps have read them
     kBarCount = kBarDFree + kStagesD
 };
-static_assert(kBarCount <= 32, "barrier block too small");
+static_assert(kBarCount <= 48, "barrier block too small");
 
 // 8 fp32 columns of tensor memory for this thread's lane, packed in pairs.
 __device__ __forceinline__ void tmem_ld8_pairs(uint32_t taddr, uint64_t (&v)[4]) {
@@ -318,11 +354,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         }
         for (int i = 0; i < kStagesA; ++i) {
             mbar_init(bars + kBarAFull + i, kWarpsDequant);
-            mbar_init(bars + kBarAFree + i, 1 + kWarpsEpilogue);
+            mbar_init(bars + kBarAFree + i, kWarpsEpilogue);
         }
         for (int i = 0; i < kStagesB; ++i) {
             mbar_init(bars + kBarBFull + i, 1);
-            mbar_init(bars + kBarBFree + i, 1 + kWarpsEpilogue);
         }
         for (int i = 0; i < kStagesD; ++i) {
             mbar_init(bars + kBarDFull + i, 1);
@@ -339,8 +374,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
 
     // "free" barriers are waited on with the parity of the phase before the one about to be used,
     // which a fresh barrier reports as complete
-    auto wait_full = [&](int bar, uint32_t use) { return mbar_wait_bounded(bars + bar, use & 1u, abort); };
-    auto wait_free = [&](int bar, uint32_t use) { return mbar_wait_bounded(bars + bar, (use & 1u) ^ 1u, abort); };
+    auto wait_full = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, use & 1u, abort); };
+    auto wait_free = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, (use & 1u) ^ 1u, abort); };
 
     if (warp == 0) {
         // ---------------- producer
@@ -361,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                         ++gu;
                     }
                     const uint32_t bs = g % kStagesB;
-                    wait_free(kBarBFree + bs, g / kStagesB);
+                    wait_free(kBarAFree + bs, g / kStagesB);
                     const uint32_t bbytes = uint32_t(ntok) * 128u, sbytes = uint32_t(ntok) * 8u;
                     mbar_expect_tx(bars + kBarBFull + bs, bbytes + sbytes);
                     bulk_g2s(smem + sm.b + bs * kStepBytesB, p.act + (size_t(b) * (p.pmax / 8) + size_t(p0 >> 3)) * 1024, bbytes, bars + kBarBFull + bs);
@@ -373,23 +408,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         // ---------------- MMA issuer
         if (lane == 0) {
             uint32_t g = 0;
+            bool a_ok = false, b_ok = false, d_ok = false;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
                 const int ntok = p.tb_n[tile / row_blocks];
                 const uint32_t idesc = umma_idesc_f16(kTileRows, ntok);
                 for (int b = 0; b < steps; ++b, ++g) {
                     const uint32_t as = g % kStagesA, bs = g % kStagesB, ds = g % kStagesD;
-                    wait_full(kBarAFull + as, g / kStagesA);
-                    wait_full(kBarBFull + bs, g / kStagesB);
-                    wait_free(kBarDFree + ds, g / kStagesD);
+                    if (!a_ok) wait_full(kBarAFull + as, g / kStagesA);
+                    if (!b_ok) wait_full(kBarBFull + bs, g / kStagesB);
+                    if (!d_ok) wait_free(kBarDFree + ds, g / kStagesD);
+                    // the next step's tests, answered while this step's MMAs are being issued
+                    a_ok = mbar_try_wait(bars + kBarAFull + (g + 1) % kStagesA, ((g + 1) / kStagesA) & 1u);
+                    b_ok = mbar_try_wait(bars + kBarBFull + (g + 1) % kStagesB, ((g + 1) / kStagesB) & 1u);
+                    d_ok = mbar_try_wait(bars + kBarDFree + (g + 1) % kStagesD, (((g + 1) / kStagesD) & 1u) ^ 1u);
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(smem + sm.a + as * kStepBytesA), b_addr = smem_u32(smem + sm.b + bs * kStepBytesB);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {   // four K = 16 instructions: two per 32-block
                         const uint64_t da = umma_desc(a_addr + kk * 2 * kALbo, kALbo, kASbo), db = umma_desc(b_addr + kk * 256, 128, 1024);
-                        umma_f16(tmem + ds * 256 + (kk >> 1) * kTileTok, da, db, idesc, kk & 1);
+                        umma_f16(tmem + ds * kStageColsD + (kk >> 1) * kTileTok, da, db, idesc, kk & 1);
                     }
-                    umma_commit(bars + kBarAFree + as);
-                    umma_commit(bars + kBarBFree + bs);
+                    // one commit per step: the epilogue warps release the A and B stages after they
+                    // have seen it, which also tells that the MMAs are done reading those stages
                     umma_commit(bars + kBarDFull + ds);
                 }
             }
@@ -400,21 +440,29 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         const int g8 = lane >> 2, t4 = lane & 3;
         const __half2 k1025 = __floats2half2_rn(1025.0f, 1025.0f);
         uint32_t g = 0, gu = 0;
+        bool a_free = false, w_ready = false;   // the next step's A stage / weights were already seen free / landed
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             for (int b = 0; b < steps; ++b, ++g) {
                 const int j = b & 1;
                 const uint32_t ws = gu % kStagesW, as = g % kStagesA;
-                if (j == 0) wait_full(kBarWFull + ws, gu / kStagesW);
+                // (the tests were issued during the previous step's work, see the epilogue)
+                if (j == 0 && !w_ready) wait_full(kBarWFull + ws, gu / kStagesW);
                 // an A stage (the fp16 tile and its row scales) is free once the MMAs that read the
                 // tile have completed and the epilogue warps have used the scales
-                wait_free(kBarAFree + as, g / kStagesA);
-                const uint8_t* wt = smem + sm.w + ws * kUnitTileBytes + dw * kUnitBytes;
+                if (!a_free) wait_free(kBarAFree + as, g / kStagesA);
                 uint8_t* at = smem + sm.a + as * kStepBytesA;
-                const uint4 wv = *reinterpret_cast<const uint4*>(wt + lane * 16);   // words [h][j] of this lane
+                uint4 wvs[kGroupsPerDequantWarp];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int gi = 0; gi < kGroupsPerDequantWarp; ++gi)   // words [h][j] of this lane, per group
+                    wvs[gi] = *reinterpret_cast<const uint4*>(smem + sm.w + ws * kUnitTileBytes + (dw * kGroupsPerDequantWarp + gi) * kUnitBytes + lane * 16);
+                a_free = mbar_try_wait(bars + kBarAFree + (g + 1) % kStagesA, (((g + 1) / kStagesA) & 1u) ^ 1u);
+                if (j == 1) w_ready = mbar_try_wait(bars + kBarWFull + (gu + 1) % kStagesW, ((gu + 1) / kStagesW) & 1u);
+#pragma unroll
+                for (int gh = 0; gh < 2 * kGroupsPerDequantWarp; ++gh) {
+                    const int gi = gh >> 1, h = gh & 1;
+                    const uint4 wv = wvs[gi];
                     const uint32_t w = h ? (j ? wv.w : wv.z) : (j ? wv.y : wv.x);
-                    const int row = dw * 16 + g8 + 8 * h;
+                    const int row = (dw * kGroupsPerDequantWarp + gi) * 16 + g8 + 8 * h;
                     uint8_t* dst = at + (row >> 3) * kASbo + (row & 7) * 16 + (t4 & 1) * 8;
 #pragma unroll
                     for (int f = 0; f < 4; ++f) {   // field f: elements 16 f + 4 t4 .. + 3 of the block
@@ -427,9 +475,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                         *reinterpret_cast<uint2*>(dst + (2 * f + (t4 >> 1)) * kALbo) = out;
                     }
                 }
-                if (lane < 16) {   // this step's weight scales of the warp's 16 rows
-                    const __half sc = *reinterpret_cast<const __half*>(wt + kUnitCodeBytes + (lane & 7) * 8 + ((lane >> 3) * 2 + j) * 2);
-                    reinterpret_cast<float*>(smem + sm.sw)[as * kTileRows + dw * 16 + lane] = __half2float(sc);
+#pragma unroll
+                for (int r = lane; r < 16 * kGroupsPerDequantWarp; r += 32) {   // this step's weight scales of the warp's rows
+                    const int gi = r >> 4, l16 = r & 15;
+                    const uint8_t* wt = smem + sm.w + ws * kUnitTileBytes + (dw * kGroupsPerDequantWarp + gi) * kUnitBytes;
+                    const __half sc = *reinterpret_cast<const __half*>(wt + kUnitCodeBytes + (l16 & 7) * 8 + ((l16 >> 3) * 2 + j) * 2);
+                    reinterpret_cast<float*>(smem + sm.sw)[as * kTileRows + (dw * kGroupsPerDequantWarp + gi) * 16 + l16] = __half2float(sc);
                 }
                 fence_async_smem();
                 __syncwarp();
@@ -448,67 +499,83 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
         const int row = quarter * 32 + lane;      // M row of the tile
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
         uint32_t g = 0;
+        bool d_ready = false;   // this step's accumulators were already seen complete
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int tb = tile / row_blocks, rb = tile % row_blocks;
             const int p0 = p.tb_p0[tb], ntok = p.tb_n[tb];
             const int ncols = max(0, min(32, ntok - 32 * cq));
+            const int last_chunk = ncols > 0 ? (ncols - 1) >> 4 : 0;   // the last 16-column chunk this thread reads
             float acc[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
             for (int b = 0; b < steps; ++b, ++g) {
                 const uint32_t as = g % kStagesA, bs = g % kStagesB, ds = g % kStagesD;
-                wait_full(kBarDFull + ds, g / kStagesD);
-                // complete long ago (the MMAs needed them) and not reusable before this warp releases
-                // the stages below; waited on here so that this thread itself acquires what the
-                // dequant warps (row scales) and the TMA (activation scales) wrote
-                wait_full(kBarAFull + as, g / kStagesA);
-                wait_full(kBarBFull + bs, g / kStagesB);
+                // Every barrier operation costs on the order of a hundred cycles of latency, and a
+                // thread's steps are serial (its sums are added block after block), so the tests
+                // are issued ahead of where their answer is needed: the one for this step's
+                // accumulators was issued during the previous step's arithmetic.
+                if (!d_ready) wait_full(kBarDFull + ds, g / kStagesD);
                 tc_fence_after_sync();
-                const float d = reinterpret_cast<const float*>(smem + sm.sw)[as * kTileRows + row];
-                const uint64_t dd = pack2(d, d);
+                // complete long ago (the MMAs needed them); tested so that what the dequant warps
+                // (row scales) and the TMA (activation scales) wrote is acquired by this thread
+                bool a_ready = mbar_try_wait(bars + kBarAFull + as, (g / kStagesA) & 1u);
+                bool b_ready = mbar_try_wait(bars + kBarBFull + bs, (g / kStagesB) & 1u);
+                const uint32_t t0 = tmem + lane_addr + ds * kStageColsD + cq * 32;
                 const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(smem + sm.s + bs * kStepBytesS) + cq * 16;
-                const uint32_t t0 = tmem + lane_addr + ds * 256 + cq * 32;
+                uint64_t dd = 0ull;
+                // two chunks of 16 columns: a round trip to tensor memory costs several hundred cycles
+                // whatever its size, so few, large loads (as large as the registers allow)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    if (c * 8 < ncols) {
-                        uint64_t s0[4], s1[4];
-                        tmem_ld8_pairs(t0 + c * 8, s0);
-                        tmem_ld8_pairs(t0 + kTileTok + c * 8, s1);
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v0[16], v1[16];
+                    if (c * 16 < ncols) {
+                        tmem_ld16(t0 + c * 16, v0);
+                        tmem_ld16(t0 + kTileTok + c * 16, v1);
                         tmem_ld_wait();
+                    }
+                    if (c == last_chunk) {
+                        // all of this thread's sums are in registers: the tensor-memory stage goes back
+                        // before the arithmetic on the last chunk; the stages limit the MMAs in flight
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bars + kBarDFree + ds);
+                        d_ready = mbar_try_wait(bars + kBarDFull + (g + 1) % kStagesD, ((g + 1) / kStagesD) & 1u);
+                    }
+                    if (c == 0) {
+                        if (!a_ready) a_ready = wait_full(kBarAFull + as, g / kStagesA);
+                        if (!b_ready) b_ready = wait_full(kBarBFull + bs, g / kStagesB);
+                        const float d = reinterpret_cast<const float*>(smem + sm.sw)[as * kTileRows + row];
+                        dd = pack2(d, d);
+                    }
+                    if (c * 16 < ncols) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const ulonglong2 a = sc[c * 4 + i];   // {a0 of the two tokens}, {a1 of the two tokens}
-                            // packed multiply by the row scale, then *scalar* adds: a packed add
-                            // would be contracted with the multiply into one rounding
+                        for (int i = 0; i < 8; ++i) {
+                            const ulonglong2 a = sc[c * 8 + i];   // {a0 of the two tokens}, {a1 of the two tokens}
+                            const uint64_t s0 = pack2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+                            const uint64_t s1 = pack2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+                            // packed multiply by the row scale, then *scalar* adds: a packed add (or a
+                            // packed t * 1 + acc) would be contracted with the multiply into one rounding
                             float u0, u1;
-                            unpack2(mul2(dd, fma2(a.y, s1[i], mul2(a.x, s0[i]))), u0, u1);
-                            acc[c * 8 + 2 * i] = __fadd_rn(acc[c * 8 + 2 * i], u0);
-                            acc[c * 8 + 2 * i + 1] = __fadd_rn(acc[c * 8 + 2 * i + 1], u1);
+                            unpack2(mul2(dd, fma2(a.y, s1, mul2(a.x, s0))), u0, u1);
+                            acc[c * 16 + 2 * i] = __fadd_rn(acc[c * 16 + 2 * i], u0);
+                            acc[c * 16 + 2 * i + 1] = __fadd_rn(acc[c * 16 + 2 * i + 1], u1);
                         }
                     }
                 }
-                tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(bars + kBarDFree + ds);
-                    mbar_arrive(bars + kBarBFree + bs);
                     mbar_arrive(bars + kBarAFree + as);
                 }
             }
             // ---- tile done: acc[i] holds this row's sum for token 32 cq + i
             if (GATE_UP) {
-                // rows m < 8 of a group are gate rows, m >= 8 the up rows of the same ff rows
+                // rows m < 8 of a group are gate rows, m >= 8 the up rows of the same ff rows: a
+                // warp's 32 rows are 16 (gate, up) pairs, 128 contiguous bytes per token
                 const int m = row & 15, ffrow = rb * 64 + (row >> 4) * 8 + (m & 7);
+                float* dst = reinterpret_cast<float*>(p.hf) + size_t(ffrow) * 2 + (m >> 3);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float v0 = acc[2 * i], v1 = acc[2 * i + 1];
-                    const float w0 = __shfl_down_sync(0xffffffffu, v0, 8), w1 = __shfl_down_sync(0xffffffffu, v1, 8);
-                    if (m < 8 && 2 * i < ncols) {
-                        const size_t pos = size_t(p0 + 32 * cq + 2 * i);
-                        p.hf[pos * p.ff + ffrow] = swiglu_ref(v0, w0);
-                        p.hf[(pos + 1) * p.ff + ffrow] = swiglu_ref(v1, w1);
-                    }
-                }
+                for (int i = 0; i < 32; ++i)
+                    if (i < ncols) dst[size_t(p0 + 32 * cq + i) * p.ff * 2] = acc[i];
             } else {
                 const int orow = rb * kTileRows + row;
 #pragma unroll
@@ -607,7 +674,7 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     p.tb_p0 = tb_p0;
     p.tb_n = tb_n;
     p.pslot = pslot;
-    p.hf = reinterpret_cast<float*>(base + L.hf);
+    p.hf = reinterpret_cast<float2*>(base + L.hf);
     p.yd = yd;
     p.status = status;
     p.pmax = L.pmax;
@@ -617,8 +684,8 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     p.act = base + L.xg;
     p.act_scale = reinterpret_cast<const float*>(base + L.xa);
     FRX_LAUNCH(kKGateUp, stream, k_pf_umma<true><<<sms, kThreads, pf_smem().total, stream>>>(p));
-    const size_t hblk = L.pmax * size_t(ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_pfu_quant_h<<<unsigned((hblk + 7) / 8), 256, 0, stream>>>(p.hf, ff, L.pmax, meta, pslot, base + L.hg,
+    const size_t hchunks = L.pmax * size_t(ff / 8);
+    FRX_LAUNCH(kKQuant, stream, k_pfu_quant_h<<<unsigned((hchunks + 255) / 256), 256, 0, stream>>>((const float2*)p.hf, ff, L.pmax, meta, pslot, base + L.hg,
                                                                                     reinterpret_cast<float*>(base + L.ha)));
     p.act = base + L.hg;
     p.act_scale = reinterpret_cast<const float*>(base + L.ha);
