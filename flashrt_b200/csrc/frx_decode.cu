@@ -128,19 +128,52 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
     quant_frag_value(x[blk * kQ8 + lane], k, blk, lane, q, a, c);
 }
 // The hidden rows: gu holds (gate x, up x) pairs; h = silu(gate x) * up x is formed here, where
-// there are thousands of independent warps to hide the latency of the exponential, stored, and
-// quantized like x.
+// there are thousands of independent threads to hide the latency of the exponential, stored, and
+// quantized like x. A thread owns four consecutive values (one word of codes in fragment order),
+// eight neighbouring lanes one 32-block.
 __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
                                                       int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
     pdl_wait();
     pdl_trigger();
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (blk >= n_blocks) return;
-    const float2 v = gu[blk * kQ8 + lane];
-    const float hv = swiglu_ref(v.x, v.y);
-    h[blk * kQ8 + lane] = hv;
-    quant_frag_value(hv, k, blk, lane, q, a, c);
+    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
+    const size_t blk = quad >> 3;
+    const bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
+    const int j = int(quad & 7);        // values 4 j .. 4 j + 3 of the block
+    float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+        const float4* src = reinterpret_cast<const float4*>(gu + quad * 4);
+        const float4 g0 = src[0], g1 = src[1];
+        hv[0] = swiglu_ref(g0.x, g0.y);
+        hv[1] = swiglu_ref(g0.z, g0.w);
+        hv[2] = swiglu_ref(g1.x, g1.y);
+        hv[3] = swiglu_ref(g1.z, g1.w);
+        *reinterpret_cast<float4*>(h + quad * 4) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+    }
+    // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16
+    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float d = __fdiv_rn(am, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int code[4], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
+        sum += code[i];
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (!live) return;
+    const int bpr = k / kQ8;
+    const size_t row = blk / bpr;
+    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = j >> 2, t = j & 3;
+    const uint32_t word = uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
+    *reinterpret_cast<uint32_t*>(q + row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4) = word;
+    if (j == 0) {
+        const float ds = __half2float(__float2half_rn(d));
+        a[blk] = s ? ds * 0.0625f : ds;
+        c[blk] = -(kMagic + float(s ? 16 * sum : sum));
+    }
 }
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
                                                     float* __restrict__ a, float* __restrict__ c) {
@@ -877,7 +910,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
