@@ -20,30 +20,53 @@ __device__ __forceinline__ uint32_t order_key(float v) {
 __device__ __forceinline__ float key_value(uint32_t k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
 // Routes token t (all 32 lanes of a warp call it). l: the token's E logits; ids_t, wts_t: its K outputs.
+//
+// Which logits a lane holds: when the row fills the warp exactly and is 16-byte aligned, lane L
+// holds experts 128 q + 4 L .. + 3 for q = 0 .. V / 4 - 1 (V / 4 vector loads, all in flight at
+// once); otherwise experts 32 i + L. Either way a lane's slots are in ascending expert order, which
+// the tie rule (lowest index wins) relies on.
 template <int V>   // logits per lane: E <= 32 * V
 __device__ __forceinline__ void route_warp(const float* __restrict__ l, int E, int K, int lane, int32_t* __restrict__ ids_t,
                                            float* __restrict__ wts_t, uint32_t* counts, uint32_t* tail) {
+    const bool vec = (V % 4 == 0) && E == 32 * V && (reinterpret_cast<uintptr_t>(l) & 15) == 0;
+    auto slot_expert = [&](int i) { return vec ? 128 * (i >> 2) + 4 * lane + (i & 3) : 32 * i + lane; };
     uint32_t key[V];
+    if (vec) {
+        float4 v[V / 4 > 0 ? V / 4 : 1];
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q) v[q] = reinterpret_cast<const float4*>(l)[32 * q + lane];
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q) {   // + 0.0f: -0.0 and +0.0 tie, as they do when compared as floats
+            key[4 * q] = order_key(v[q].x + 0.0f);
+            key[4 * q + 1] = order_key(v[q].y + 0.0f);
+            key[4 * q + 2] = order_key(v[q].z + 0.0f);
+            key[4 * q + 3] = order_key(v[q].w + 0.0f);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int e = 32 * i + lane;
+            key[i] = e < E ? order_key(l[e] + 0.0f) : 0u;
+        }
+    }
     uint32_t best = 0;
     int best_i = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-        const int e = 32 * i + lane;
-        key[i] = e < E ? order_key(l[e] + 0.0f) : 0u;   // + 0.0f: -0.0 and +0.0 tie, as they do when compared as floats
         if (key[i] > best) {   // ascending index within a lane: the first maximum wins
             best = key[i];
-            best_i = e;
+            best_i = slot_expert(i);
         }
     }
     const uint32_t kmax = __reduce_max_sync(0xffffffffu, best);
     const float m = key_value(kmax);
-    double part = 0.0;
+    double part[4] = {0.0, 0.0, 0.0, 0.0};   // four running sums: the additions are slow and would otherwise form one chain
 #pragma unroll
     for (int i = 0; i < V; ++i)
-        if (32 * i + lane < E) part += double(expf(key_value(key[i]) - m));
+        if (key[i] != 0u) part[i & 3] += double(expf(key_value(key[i]) - m));
+    double sum = (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    const double sum = part;
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 
     // selection: K rounds on the integer keys only; lane k remembers the k-th winner
     uint32_t my_key = 0;
@@ -51,15 +74,15 @@ __device__ __forceinline__ void route_warp(const float* __restrict__ l, int E, i
     for (int k = 0; k < K; ++k) {
         const uint32_t top = __reduce_max_sync(0xffffffffu, best);
         const int sel = __reduce_min_sync(0xffffffffu, best == top ? best_i : 0x7fffffff);
-        if ((sel & 31) == lane) {   // the owner retires it and finds its next best
+        if ((vec ? (sel >> 2) & 31 : sel & 31) == lane) {   // the owner retires it and finds its next best
             best = 0;
             best_i = 0x7fffffff;
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                if (32 * i + lane == sel) key[i] = 0u;
+                if (slot_expert(i) == sel) key[i] = 0u;
                 if (key[i] > best) {
                     best = key[i];
-                    best_i = 32 * i + lane;
+                    best_i = slot_expert(i);
                 }
             }
         }
