@@ -41,6 +41,7 @@ sys.path.insert(0, ROOT)
 N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
+NCU_GU_TRAFFIC_PER_BLOB = 224.17e6 / 367   # DRAM bytes per distinct expert blob of one gate/up launch (ncu, profiles/)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
 UNIT = "layer-tokens/s"
@@ -277,7 +278,11 @@ def run_frx(args):
     achieved = gu_alg_bytes / (gu_us * 1e-6) / 1e9
     layer_bytes = float(np.mean([(d + 1) * EXPERT_BYTES for d in distinct])) + B * (E * 4 + N_MODEL * 8) + B * K * 8
     roofline = {"bound": "hbm", "kernel": "k_stream<gate_up>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "peak_source": peak_src, "traffic": None,
+                "frac": round(achieved / peak, 4), "peak_source": peak_src,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch: 224.17 MB for 367 distinct
+                # expert blobs in the ncu capture summarised in profiles/k_stream_decode_b64.md (a 2-layer
+                # case of the same kernel), scaled to this run by the distinct blobs a launch reads
+                "traffic": int(mean_local * NCU_GU_TRAFFIC_PER_BLOB), "traffic_source": "ncu capture of a 2-layer case, scaled by distinct expert blobs",
                 "algorithmic_bytes_per_launch": int(gu_alg_bytes), "us_per_launch": gu_us,
                 "timing": "CUDA events around each launch, a separate pass of the same steps without the CUDA graph",
                 "layer": {"algorithmic_bytes": int(layer_bytes), "us": round(ms * 1e3 / L, 3),

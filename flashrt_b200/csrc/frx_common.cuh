@@ -171,16 +171,16 @@ __device__ __forceinline__ uint64_t global_ns() {
 // once, and the caller's block finishes its control flow without trusting the data.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // SLEEP: back off with nanosleep after a few polls (right for waits on data from global memory,
-// where a waiting warp should leave the issue slots to working warps); without it the wait polls
-// try_wait, which itself suspends the thread for a short hardware-defined time (right for the
-// short hand-offs of a warp-specialised pipeline, where a sleep that overshoots delays every step).
+// where a waiting warp should leave the issue slots to working warps); without it the wait only
+// repeats try_wait, which itself suspends the thread for a short hardware-defined time (right for
+// the short hand-offs of a warp-specialised pipeline, where a sleep that overshoots delays every step).
 template <bool SLEEP = true>
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
     uint64_t t0 = 0;   // the clock is only read once the wait has lasted a while: reading it is slow
     for (uint32_t polls = 1;; ++polls) {
-        if (SLEEP ? mbar_try_wait(bar, parity) : mbar_test_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) return true;   // suspends the thread for a short, hardware-defined time when not complete
         if (SLEEP) {
             if (polls > 4) __nanosleep(polls > 64 ? 256 : 32);   // a long wait must not take issue slots from working warps
         } else if (polls > 65536) {
