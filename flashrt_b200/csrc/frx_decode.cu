@@ -1091,6 +1091,102 @@ int frx_moe_layer_host(const void* experts, size_t stride, int E, const void* sh
     return FRX_OK;
 }
 
+namespace {
+constexpr int kHostSlots = 4;   // staging slots of frx_moe_layers_host
+struct HostPipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, copied[kHostSlots] = {}, computed[kHostSlots] = {}, returned[kHostSlots] = {};
+};
+// The copy streams and events of the current device, created at the first call.
+int host_pipe(HostPipe** pipe) {
+    static std::mutex mu;
+    static HostPipe pipes[64];
+    int dev = 0;
+    FRX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FRX_ERR_ARG, "frx_moe_layers_host: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    HostPipe& hp = pipes[dev];
+    if (!hp.in) {
+        FRX_CUDA(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+        FRX_CUDA(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+        FRX_CUDA(cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming));
+        for (int i = 0; i < kHostSlots; ++i) {
+            FRX_CUDA(cudaEventCreateWithFlags(&hp.copied[i], cudaEventDisableTiming));
+            FRX_CUDA(cudaEventCreateWithFlags(&hp.computed[i], cudaEventDisableTiming));
+            FRX_CUDA(cudaEventCreateWithFlags(&hp.returned[i], cudaEventDisableTiming));
+        }
+    }
+    *pipe = &hp;
+    return FRX_OK;
+}
+struct HostSlotBytes {
+    size_t x, out, logits, gate, slot;
+};
+HostSlotBytes host_slot_bytes(int T, int n, int E) {
+    HostSlotBytes b{};
+    b.x = align_up(size_t(T) * n * 4);
+    b.out = b.x;
+    b.logits = align_up(size_t(T) * E * 4);
+    b.gate = align_up(size_t(T) * 4);
+    b.slot = b.x + b.out + b.logits + b.gate;
+    return b;
+}
+}  // namespace
+
+size_t frx_moe_layers_host_workspace_bytes(int T, int K, int n, int ff, int E) {
+    const size_t l = frx_moe_layer_workspace_bytes(T, K, n, ff);
+    if (!l || E < 1) return 0;
+    return l + kHostSlots * host_slot_bytes(T, n, E).slot;
+}
+
+int frx_moe_layers_host(const void* const* experts, size_t stride, int E, const void* const* shared, int n, int ff,
+                        const float* const* x_host, const float* const* logits_host, const float* const* gate_logit_host,
+                        int L, int T, int K, float* const* out_host, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    if (!experts || !x_host || !logits_host || !out_host || !ws) return fail(FRX_ERR_ARG, "frx_moe_layers_host: null pointer");
+    if (int rc = check_moe_shape("frx_moe_layers_host", n, ff, K)) return rc;
+    if (L < 0 || T < 1 || E < 1) return fail(FRX_ERR_ARG, "frx_moe_layers_host: L %d, T %d, E %d", L, T, E);
+    const size_t need = frx_moe_layers_host_workspace_bytes(T, K, n, ff, E);
+    if (ws_bytes < need) return fail(FRX_ERR_WORKSPACE, "frx_moe_layers_host: workspace %zu < %zu", ws_bytes, need);
+    for (int l = 0; l < L; ++l)
+        if (!experts[l] || !x_host[l] || !logits_host[l] || !out_host[l]) return fail(FRX_ERR_ARG, "frx_moe_layers_host: null pointer for layer %d", l);
+    if (L == 0) return FRX_OK;
+    HostPipe* hp = nullptr;
+    if (int rc = host_pipe(&hp)) return rc;
+    const size_t lw = frx_moe_layer_workspace_bytes(T, K, n, ff);
+    const HostSlotBytes sb = host_slot_bytes(T, n, E);
+    auto* base = static_cast<uint8_t*>(ws);
+    // what is already queued on the caller's stream may still use the workspace
+    FRX_CUDA(cudaEventRecord(hp->start, stream));
+    FRX_CUDA(cudaStreamWaitEvent(hp->in, hp->start, 0));
+    for (int l = 0; l < L; ++l) {
+        const int s = l % kHostSlots;
+        uint8_t* slot = base + lw + size_t(s) * sb.slot;
+        float* dx = reinterpret_cast<float*>(slot);
+        float* dout = reinterpret_cast<float*>(slot + sb.x);
+        float* dlog = reinterpret_cast<float*>(slot + sb.x + sb.out);
+        float* dgate = reinterpret_cast<float*>(slot + sb.x + sb.out + sb.logits);
+        const float* gh = gate_logit_host ? gate_logit_host[l] : nullptr;
+        // the slot is free once the output of the layer that used it last has been copied out
+        if (l >= kHostSlots) FRX_CUDA(cudaStreamWaitEvent(hp->in, hp->returned[s], 0));
+        FRX_CUDA(cudaMemcpyAsync(dx, x_host[l], size_t(T) * n * 4, cudaMemcpyHostToDevice, hp->in));
+        FRX_CUDA(cudaMemcpyAsync(dlog, logits_host[l], size_t(T) * E * 4, cudaMemcpyHostToDevice, hp->in));
+        if (gh) FRX_CUDA(cudaMemcpyAsync(dgate, gh, size_t(T) * 4, cudaMemcpyHostToDevice, hp->in));
+        FRX_CUDA(cudaEventRecord(hp->copied[s], hp->in));
+        FRX_CUDA(cudaStreamWaitEvent(stream, hp->copied[s], 0));
+        if (int rc = frx_moe_layer(experts[l], stride, E, shared ? shared[l] : nullptr, n, ff, dx, dlog, gh ? dgate : nullptr, T, K, dout, nullptr,
+                                   nullptr, ws, lw, stream))
+            return rc;
+        FRX_CUDA(cudaEventRecord(hp->computed[s], stream));
+        FRX_CUDA(cudaStreamWaitEvent(hp->out, hp->computed[s], 0));
+        FRX_CUDA(cudaMemcpyAsync(out_host[l], dout, size_t(T) * n * 4, cudaMemcpyDeviceToHost, hp->out));
+        FRX_CUDA(cudaEventRecord(hp->returned[s], hp->out));
+    }
+    FRX_CUDA(cudaStreamSynchronize(hp->out));
+    FRX_CUDA(cudaStreamSynchronize(hp->in));
+    FRX_CUDA(cudaStreamSynchronize(stream));
+    return FRX_OK;
+}
+
 int frx_workspace_status(const void* ws, frx_stream_t stream) {
     if (!ws) return fail(FRX_ERR_ARG, "frx_workspace_status: null workspace");
     int st[4] = {0, 0, 0, 0};

@@ -62,6 +62,8 @@ SIGNATURES = {
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "frx_moe_layer_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_moe_layers_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "frx_moe_layers_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "frx_workspace_status": (_i, [_vp, _vp]),
     "frx_moe_hits_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_hits": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _sz, _vp, _vp, _i]),

@@ -246,6 +246,36 @@ def moe_layer_host(experts: int, stride: int, E: int, shared: int | None, n: int
     return out_host
 
 
+def moe_layers_host_workspace_bytes(T: int, K: int, n: int, ff: int, E: int) -> int:
+    return int(lib.frx_moe_layers_host_workspace_bytes(T, K, n, ff, E))
+
+
+def moe_layers_host(experts: list[int], stride: int, E: int, shared: list[int | None] | None, n: int, ff: int,
+                    x_host: list[torch.Tensor], logits_host: list[torch.Tensor], gate_logit_host: list[torch.Tensor | None] | None,
+                    K: int, out_host: list[torch.Tensor], ws: torch.Tensor, stream=None) -> list[torch.Tensor]:
+    """L independent layer calls from host tensors in one call (frx_moe_layers_host): the copies of
+    neighbouring layers overlap a layer's compute when the host tensors are pinned. Entry l of every
+    list belongs to layer l; results are identical to L calls of moe_layer_host."""
+    L = len(experts)
+    for ts in (x_host, logits_host, out_host):
+        if len(ts) != L:
+            raise FrxError(_l.ERR_ARG, "moe_layers_host: one entry per layer in every list")
+        for t in ts:
+            if t.is_cuda or not t.is_contiguous() or t.dtype != torch.float32:
+                raise FrxError(_l.ERR_ARG, "moe_layers_host takes contiguous float32 host tensors")
+    T = x_host[0].shape[0] if L else 1
+    arr = C.c_void_p * max(L, 1)
+    ex = arr(*[C.c_void_p(e) for e in experts])
+    sh = arr(*[C.c_void_p(e) if e else None for e in shared]) if shared is not None else None
+    xs = arr(*[C.c_void_p(t.data_ptr()) for t in x_host])
+    ls = arr(*[C.c_void_p(t.data_ptr()) for t in logits_host])
+    gs = arr(*[C.c_void_p(t.data_ptr()) if t is not None else None for t in gate_logit_host]) if gate_logit_host is not None else None
+    os_ = arr(*[C.c_void_p(t.data_ptr()) for t in out_host])
+    wp, wb = _ws_ptr(ws)
+    check(lib.frx_moe_layers_host(ex, stride, E, sh, n, ff, xs, ls, gs, L, T, K, os_, wp, wb, _stream(stream)))
+    return out_host
+
+
 def _raw_view(ws: torch.Tensor, off: int, dt, shape):
     wp, _ = _ws_ptr(ws)
     start = wp.value - ws.data_ptr() + off

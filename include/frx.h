@@ -194,6 +194,21 @@ int frx_moe_layer_host(const void* experts, size_t stride, int E, const void* sh
                        const float* x_host, const float* logits_host, const float* gate_logit_host, int T, int K,
                        float* out_host, void* ws, size_t ws_bytes, frx_stream_t stream);
 
+/* L independent layer calls from host buffers in one call, pipelined: while layer l computes on
+ * `stream`, the inputs of the following layers are copied in and the outputs of the preceding ones
+ * copied out on two copy streams the library creates once per device (at the first call; call it
+ * once outside any stream capture). experts[l], shared[l] (shared may be null, or shared[l] null):
+ * device blobs of layer l; x_host[l] [T][n], logits_host[l] [T][E], gate_logit_host[l] [T] (the
+ * array or an entry may be null), out_host[l] [T][n]: host buffers, pinned if the copies are to
+ * overlap. Results are bit-identical to L calls of frx_moe_layer_host. Returns after everything
+ * has drained. `ws`: device workspace of frx_moe_layers_host_workspace_bytes (independent of L:
+ * inputs and outputs pass through a ring of four staging slots). The reference has no counterpart:
+ * its engine keeps activations on the device between layers. */
+size_t frx_moe_layers_host_workspace_bytes(int T, int K, int n, int ff, int E);
+int frx_moe_layers_host(const void* const* experts, size_t stride, int E, const void* const* shared, int n, int ff,
+                        const float* const* x_host, const float* const* logits_host, const float* const* gate_logit_host,
+                        int L, int T, int K, float* const* out_host, void* ws, size_t ws_bytes, frx_stream_t stream);
+
 /* After the stream has drained: FRX_OK, or FRX_ERR_DEVICE if a kernel of a call that used this
  * workspace reported an error (then frx_last_error() says which). */
 int frx_workspace_status(const void* ws, frx_stream_t stream);

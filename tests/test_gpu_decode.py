@@ -165,6 +165,20 @@ def test_layer_with_router_and_host_entry(port):
     moe.moe_layer_host(ex.base, ex.stride, E, ex.shared_ptr, n, ff, torch.from_numpy(x).pin_memory(), torch.from_numpy(lg).pin_memory(),
                        torch.from_numpy(gate).pin_memory(), K, out_h, ws)
     assert np.array_equal(out_h.numpy(), out.cpu().numpy())
+    # the pipelined many-layer form: 9 "layers" (more than its four staging slots) over the same
+    # experts with different activations, identical to one call per layer
+    L = 9
+    xs = [torch.from_numpy(synth.activations(T, n, seed=100 + l)).pin_memory() for l in range(L)]
+    ls = [torch.from_numpy(synth.router_logits(T, E, seed=200 + l)).pin_memory() for l in range(L)]
+    gs = [torch.from_numpy(gate + 0.1 * l).pin_memory() if l % 2 == 0 else None for l in range(L)]
+    outs = [torch.empty(T, n).pin_memory() for _ in range(L)]
+    wsl = moe.workspace(moe.moe_layers_host_workspace_bytes(T, K, n, ff, E))
+    moe.moe_layers_host([ex.base] * L, ex.stride, E, [ex.shared_ptr] * L, n, ff, xs, ls, gs, K, outs, wsl)
+    for l in range(L):
+        want = torch.empty(T, n).pin_memory()
+        moe.moe_layer_host(ex.base, ex.stride, E, ex.shared_ptr, n, ff, xs[l], ls[l], gs[l], K, want, ws)
+        assert np.array_equal(outs[l].numpy(), want.numpy()), l
+    moe.workspace_status(wsl)
 
 
 def test_combine_in_hit_order(port):
