@@ -55,15 +55,18 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms from before the warm-up on; the
+    samples that fall inside the timed region (between begin() and stop()) are reported, or, when the
+    region was shorter than the sampling period allows, the ones nearest to it (taken under the same
+    load, during warm-up)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.t_begin = [], None, None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
         except OSError:
@@ -71,22 +74,33 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def begin(self):
+        self.t_begin = time.time()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t_end = time.time()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        ok = [(t, r) for t, r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        t0 = self.t_begin if self.t_begin is not None else 0.0
+        inside = [r for t, r in ok if t0 <= t <= t_end + 0.05]
+        window = "timed region"
+        if not inside and ok:
+            inside = [r for _, r in sorted(ok, key=lambda tr: min(abs(tr[0] - t0), abs(tr[0] - t_end)))[:3]]
+            window = "nearest samples (region shorter than the sampling period)"
+        sm = [float(r[0]) for r in inside]
+        mx = [float(r[1]) for r in inside if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in inside)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 def cpu_moe_setup(oracle, n_layers: int, B: int, seed: int):
@@ -203,14 +217,36 @@ def run_frx(args):
     wts = torch.empty(L, B, K, device=dev)
     ws = moe.workspace(moe.moe_layer_workspace_bytes(B, K, N_MODEL, FF), dev)
 
+    # Expert parallel: the all-reduce is fused into each layer's last kernel over peer memory (CUDA
+    # IPC); if the peer mapping cannot be set up, NCCL's all-reduce is used instead.
+    comm = None
+    if world > 1:
+        from flashrt_b200 import ep
+        try:
+            comm = ep.EpComm(B, N_MODEL)
+        except Exception as exc:   # noqa: BLE001 - any failure of the set-up means the NCCL form
+            if rank == 0:
+                print(f"peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+        ok = torch.tensor([1 if comm is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0 and comm is not None:
+            comm.close()
+            comm = None
+
+    def ep_layer(l: int, xin, lin, gin, o):
+        shared_blob = arena.blob(l, e_local) if rank == 0 else None
+        if comm is not None:
+            ep.moe_layer_ep_fused(comm, arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o,
+                                  ids[l], wts[l], ws)
+        else:
+            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o, ids[l], wts[l], ws)
+
     def layer_call(l: int):
         if world == 1:
             moe.moe_layer(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, x[l], logits[l], gate[l], K,
                           out=out[l], ids_out=ids[l], wts_out=wts[l], ws=ws)
         else:
-            from flashrt_b200 import ep
-            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, arena.blob(l, e_local) if rank == 0 else None, N_MODEL, FF,
-                            x[l], logits[l], gate[l], K, out[l], ids[l], wts[l], ws)
+            ep_layer(l, x[l], logits[l], gate[l], out[l])
 
     def step():
         for l in range(L):
@@ -227,10 +263,10 @@ def run_frx(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- value: inputs resident in HBM. Single GPU: the 48 layer calls replayed from one CUDA graph.
-    # Expert parallel: plain launches (capturing the NCCL all-reduces together with these kernels
-    # did not complete on the 2-GPU box, so it is not attempted).
-    use_graph = world == 1 and not args.no_graph
+    # ---- value: inputs resident in HBM; the 48 layer calls replayed from one CUDA graph. With
+    # NCCL all-reduces on the path the launches stay plain (capturing them together with these
+    # kernels did not complete on the 2-GPU box, so it is not attempted).
+    use_graph = (world == 1 or comm is not None) and not args.no_graph
     run = step
     if use_graph:
         side = torch.cuda.Stream()
@@ -242,10 +278,12 @@ def run_frx(args):
         with torch.cuda.graph(graph):
             step()
         run = graph.replay
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         run()
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -290,7 +328,7 @@ def run_frx(args):
                           "frac_of_peak": round(layer_bytes / world / (ms * 1e-3 / L) / 1e9 / peak, 4)}}
 
     # ---- e2e: host buffers through frx_moe_layers_host (one call per step, copies pipelined with
-    # compute), every copy inside the timed region (single GPU)
+    # compute), every copy inside the timed region
     e2e = None
     if world == 1:
         xh, lh, gh = x.cpu().pin_memory(), logits.cpu().pin_memory(), gate.cpu().pin_memory()
@@ -313,6 +351,37 @@ def run_frx(args):
         assert torch.equal(oh.to(dev), out), "host entry and device entry disagree"
         e2e = {"value": B * L / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
                "h2d_bytes_per_step": L * B * (N_MODEL + E + 1) * 4, "d2h_bytes_per_step": L * B * N_MODEL * 4}
+    else:
+        # Expert parallel: the activations and logits are replicated, so every rank copies its own
+        # from pinned host memory; the all-reduced result goes back to host memory on every rank.
+        # Copies, layer calls and all-reduces are stream-ordered; one synchronisation per step.
+        xh, lh, gh = x.cpu().pin_memory(), logits.cpu().pin_memory(), gate.cpu().pin_memory()
+        oh = torch.empty(L, B, N_MODEL).pin_memory()
+        xd, ld, gd, od = torch.empty_like(x[0]), torch.empty_like(logits[0]), torch.empty_like(gate[0]), torch.empty_like(out[0])
+
+        def host_step():
+            for l in range(L):
+                xd.copy_(xh[l], non_blocking=True)
+                ld.copy_(lh[l], non_blocking=True)
+                gd.copy_(gh[l], non_blocking=True)
+                ep_layer(l, xd, ld, gd, od)
+                oh[l].copy_(od, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(max(1, args.warmup // 2)):
+            host_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            host_step()
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+        assert torch.allclose(oh.to(dev), out, rtol=1e-5, atol=1e-6), "host-buffer step and device-resident step disagree"
+        e2e = {"value": B * L / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
+               "h2d_bytes_per_step": world * L * B * (N_MODEL + E + 1) * 4, "d2h_bytes_per_step": world * L * B * N_MODEL * 4}
 
     # ---- CPU baseline: the reference's CPU path on a bounded sample (rank 0, single GPU runs only)
     cpu = None
@@ -354,7 +423,8 @@ def run_frx(args):
             "config": {"workload": f"configs[1]: one Q2_0 MoE layer decode, batch {B}, hidden 2048, 512 experts + shared, top-10",
                        "batch": B, "layers_per_step": L, "l2": "inputs larger than L2: 48 distinct layers, 21.8 GB of experts",
                        "distinct_experts_per_layer_mean": float(np.mean(distinct)), "parallelism": f"ep{world}",
-                       "cuda_graph": use_graph},
+                       "cuda_graph": use_graph,
+                       "all_reduce": "none" if world == 1 else ("fused into the combine kernel, peer memory over NVLink" if comm is not None else "NCCL")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": sum(v["launches"] for v in kernels.values()), "kernels": kernels,
             "roofline": roofline, "cpu_baseline": cpu,
         }
@@ -418,11 +488,13 @@ def run_prefill(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     moe.workspace_status(ws)
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):

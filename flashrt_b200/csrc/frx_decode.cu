@@ -131,13 +131,23 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
 // there are thousands of independent threads to hide the latency of the exponential, stored, and
 // quantized like x. A thread owns four consecutive values (one word of codes in fragment order),
 // eight neighbouring lanes one 32-block.
+// With `slot_ids` (expert parallel), routed rows whose expert lies outside [e_lo, e_hi) are skipped:
+// another rank computes them, and nothing here reads their hidden values.
 __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
-                                                      int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
+                                                      int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c,
+                                                      const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi) {
     pdl_wait();
     pdl_trigger();
     const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
     const size_t blk = quad >> 3;
-    const bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
+    bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
+    if (live && slot_ids) {
+        const size_t r = blk / size_t(k / kQ8);
+        if (r < size_t(routed_rows)) {
+            const int e = slot_ids[r];
+            live = e >= e_lo && e < e_hi;
+        }
+    }
     const int j = int(quad & 7);        // values 4 j .. 4 j + 3 of the block
     float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (live) {
@@ -345,6 +355,8 @@ struct StreamParams {
     const int8_t* aq;
     const float* aa;
     const float* ac;
+    const int32_t* slot_ids;   // expert parallel: the expert of every routed slot (else null), and the range held here
+    int e_lo, e_hi;
     float2* gu;        // [slots][ff]   (gate x, up x) per hidden element, written by GATE_UP
     float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by the quantizer of the hidden rows
     float* y;          // [T*K][n]      routed slots (down)
@@ -716,6 +728,141 @@ __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out
     out[size_t(t) * n + i] = acc;
 }
 
+// ---- combine fused with the expert-parallel all-reduce over peer memory
+// Layout of a rank's communication buffer: two slots of partial sums [max_T][n] fp32, then
+// (256-byte aligned) flag words [FRX_EP_MAX_RANKS] (word q is written by rank q: the number of the
+// last call whose partial sums rank q has published), then three local words: the number of calls
+// completed and two ticket counters.
+struct EpLayout {
+    size_t slot_floats, flags, state, total;
+};
+__host__ __device__ inline EpLayout ep_layout(int max_T, int n) {
+    EpLayout L{};
+    L.slot_floats = size_t(max_T) * n;
+    L.flags = align_up(2 * L.slot_floats * 4);
+    L.state = L.flags + 256;
+    L.total = L.state + 256;
+    return L;
+}
+struct EpParams {
+    int world, rank;
+    float* partial[FRX_EP_MAX_RANKS];      // slot 0 of every rank's buffer
+    uint32_t* flags[FRX_EP_MAX_RANKS];     // every rank's flag words
+    uint32_t* state;                       // local: [0] calls completed so far, [1], [2] tickets
+    size_t slot_floats;
+};
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// out[t] = sum over ranks (in rank order) of that rank's partial sum; this rank's partial sum is
+// what k_combine_ordered computes. A thread owns up to kEpElems output elements of one token, and
+// their partial sums never leave its registers, so no barrier inside the GPU is needed: a block
+// publishes its part, the last block to do so raises this rank's flag at the peers, and every
+// block then waits for the peers' flags (not for its own rank's). Blocks of different GPUs wait
+// on one another, so all blocks of a launch must be resident at once: the host keeps the grid
+// below the number of SMs times four.
+constexpr int kEpElems = 4;   // consecutive elements per thread: one 16-byte access
+__device__ __forceinline__ float4 ld_peer4(const float* p) {   // never from a cache of this GPU: the buffer is rewritten every other call
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ out, const float* __restrict__ y,
+                                                           const float* __restrict__ wts, const int32_t* __restrict__ order,
+                                                           const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
+                                                           const EpParams ep, int* __restrict__ status) {
+    __shared__ int s_fail;
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.y;
+    const int i = (blockIdx.x * 256 + threadIdx.x) * kEpElems;   // n is a multiple of 128: a thread's four elements are all inside or all outside
+    const uint32_t call = ep.state[0] + 1;   // the same in every block: state[0] only changes after all blocks have read it
+    const size_t slot = size_t(call & 1u) * ep.slot_floats;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (i < n) {
+        for (int k = 0; k < K; ++k) {
+            const int s = order[t * K + k];
+            if (s >= 0) {
+                const float w = wts[s];
+                const float4 v = *reinterpret_cast<const float4*>(y + size_t(s) * n + i);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+            }
+        }
+        if (ysh) {
+            const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
+            const float4 v = *reinterpret_cast<const float4*>(ysh + size_t(t) * n + i);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, g));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, g));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, g));
+        }
+        *reinterpret_cast<float4*>(ep.partial[ep.rank] + slot + size_t(t) * n + i) = acc;
+    }
+    // publish: the block's stores are ordered before thread 0 by the block barrier; thread 0 makes
+    // them visible to the system and takes a ticket; the last block raises this rank's flag at every peer
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int fail_flag = 0;
+        const uint32_t blocks = gridDim.x * gridDim.y;
+        __threadfence_system();
+        if (atomicAdd(&ep.state[1], 1u) == blocks - 1) {
+            ep.state[1] = 0;
+            __threadfence_system();
+            for (int q = 0; q < ep.world; ++q)
+                if (q != ep.rank) st_release_sys(ep.flags[q] + ep.rank, call);
+        }
+        // wait for every peer's flag of this call (flags only grow; the signed distance makes wrap-around harmless)
+        const uint64_t t0 = global_ns();
+        for (int q = 0; q < ep.world && !fail_flag; ++q) {
+            if (q == ep.rank) continue;
+            uint32_t polls = 0;
+            while (int32_t(ld_acquire_sys(ep.flags[ep.rank] + q) - call) < 0) {
+                if ((++polls & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) {
+                    fail_flag = 1;
+                    break;
+                }
+            }
+        }
+        s_fail = fail_flag;
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (threadIdx.x == 0) status[0] = kDevWaitTimeout;
+    } else if (i < n) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int q = 0; q < ep.world; ++q) {
+            const float4 v = q == ep.rank ? acc : ld_peer4(ep.partial[q] + slot + size_t(t) * n + i);
+            if (q == 0) {
+                sum = v;
+            } else {
+                sum.x = __fadd_rn(sum.x, v.x);
+                sum.y = __fadd_rn(sum.y, v.y);
+                sum.z = __fadd_rn(sum.z, v.z);
+                sum.w = __fadd_rn(sum.w, v.w);
+            }
+        }
+        *reinterpret_cast<float4*>(out + size_t(t) * n + i) = sum;
+    }
+    // the call is complete on this rank once every block has passed its wait: a second ticket
+    // counts them and the last one advances the call number
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t blocks = gridDim.x * gridDim.y;
+        if (atomicAdd(&ep.state[2], 1u) == blocks - 1) {
+            ep.state[2] = 0;
+            __threadfence();
+            ep.state[0] = call;
+        }
+    }
+}
+
 // k_moe_combine / k_stream_combine semantics: k order, as the hit list gives it
 __global__ void __launch_bounds__(256) k_combine_hits(float* __restrict__ out, const float* __restrict__ yh,
                                                       const float* __restrict__ w, const int32_t* __restrict__ hit_n,
@@ -910,7 +1057,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -941,7 +1088,7 @@ int check_moe_shape(const char* who, int n, int ff, int K) {
 // and weights are outputs, else inputs.
 int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff, const float* x,
                  const float* logits, int32_t* ids, float* wts, const float* gate_logit, int T, int K, float* out, float* yslot, void* ws,
-                 size_t ws_bytes, cudaStream_t stream) {
+                 size_t ws_bytes, cudaStream_t stream, const EpParams* ep = nullptr) {
     if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
     if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
     if (e_lo < 0 || e_hi > E || e_lo > e_hi) return fail(FRX_ERR_ARG, "frx_moe_decode: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
@@ -994,10 +1141,20 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         p.ff = ff;
         p.K = K;
         p.TK = Tc * K;
+        if (e_lo > 0 || e_hi < E) {
+            p.slot_ids = ids + size_t(t0) * K;
+            p.e_lo = e_lo;
+            p.e_hi = e_hi;
+        }
         launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
-        FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
-                                                        (const float*)(wts + size_t(t0) * K), (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
-                                                        gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
+        if (ep)   // one chunk only (the caller checked T <= 64)
+            FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_allreduce, dim3((n + 256 * kEpElems - 1) / (256 * kEpElems), Tc), dim3(256), 0, stream, out,
+                                                            (const float*)p.y, (const float*)wts, (const int32_t*)order,
+                                                            (const float*)(shared ? p.ysh : nullptr), gate_logit, n, K, *ep, status));
+        else
+            FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
+                                                            (const float*)(wts + size_t(t0) * K), (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
+                                                            gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
     }
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
@@ -1048,6 +1205,12 @@ size_t frx_moe_layer_workspace_bytes(int T, int K, int n, int ff) {
 int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
                   const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out, float* wts_out,
                   void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_layer_ep(experts, stride, E, 0, E, shared, n, ff, x, logits, gate_logit, T, K, out, ids_out, wts_out, ws, ws_bytes, stream);
+}
+
+int frx_moe_layer_ep(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff, const float* x,
+                     const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out, float* wts_out,
+                     void* ws, size_t ws_bytes, frx_stream_t stream) {
     if (!logits || !ws) return fail(FRX_ERR_ARG, "frx_moe_layer: null pointer");
     if (int rc = check_moe_shape("frx_moe_layer", n, ff, K)) return rc;
     if (T < 0) return fail(FRX_ERR_ARG, "frx_moe_layer: T %d", T);
@@ -1057,7 +1220,88 @@ int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared,
     auto* base = static_cast<uint8_t*>(ws);
     int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
     float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
-    return decode_steps(experts, stride, E, 0, E, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
+    return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
+}
+
+size_t frx_ep_buffer_bytes(int max_T, int n) {
+    if (max_T < 1 || n < 1) return 0;
+    return ep_layout(max_T, n).total;
+}
+
+int frx_ep_buffer_create(void** buffer, int max_T, int n) {
+    if (!buffer || max_T < 1 || n < 1) return fail(FRX_ERR_ARG, "frx_ep_buffer_create: bad argument");
+    const size_t bytes = ep_layout(max_T, n).total;
+    void* p = nullptr;
+    FRX_CUDA(cudaMalloc(&p, bytes));   // its own allocation: CUDA IPC exports whole allocations
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(e, "frx_ep_buffer_create: cudaMemset");
+    }
+    *buffer = p;
+    return FRX_OK;
+}
+
+int frx_ep_buffer_destroy(void* buffer) {
+    if (buffer) FRX_CUDA(cudaFree(buffer));
+    return FRX_OK;
+}
+
+int frx_ipc_export(const void* buffer, void* handle) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == FRX_IPC_HANDLE_BYTES, "handle size");
+    if (!buffer || !handle) return fail(FRX_ERR_ARG, "frx_ipc_export: null pointer");
+    cudaIpcMemHandle_t h;
+    FRX_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(buffer)));
+    std::memcpy(handle, &h, sizeof h);
+    return FRX_OK;
+}
+
+int frx_ipc_open(const void* handle, void** mapped) {
+    if (!handle || !mapped) return fail(FRX_ERR_ARG, "frx_ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof h);
+    FRX_CUDA(cudaIpcOpenMemHandle(mapped, h, cudaIpcMemLazyEnablePeerAccess));
+    return FRX_OK;
+}
+
+int frx_ipc_close(void* mapped) {
+    if (mapped) FRX_CUDA(cudaIpcCloseMemHandle(mapped));
+    return FRX_OK;
+}
+
+int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
+                               const float* x, const float* logits, const float* gate_logit, int T, int K, float* out,
+                               int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
+                               frx_stream_t stream) {
+    if (!logits || !ws || !comm) return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: null pointer");
+    if (comm->world < 1 || comm->world > FRX_EP_MAX_RANKS || comm->rank < 0 || comm->rank >= comm->world)
+        return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: rank %d of %d", comm->rank, comm->world);
+    if (T < 0 || T > kMaxChunkTokens || T > comm->max_T || n != comm->n)
+        return fail(FRX_ERR_SHAPE, "frx_moe_layer_ep_allreduce: T %d (at most %d and the buffers' %d), n %d (buffers' %d)", T, kMaxChunkTokens,
+                    comm->max_T, n, comm->n);
+    if (int rc = check_moe_shape("frx_moe_layer_ep_allreduce", n, ff, K)) return rc;
+    if (T == 0) return FRX_OK;   // every rank skips the call alike
+    // blocks of different GPUs wait on one another: all of a launch must be resident at once
+    const long long blocks = (long long)((n + 256 * kEpElems - 1) / (256 * kEpElems)) * T;
+    if (blocks > 4LL * sm_count()) return fail(FRX_ERR_SHAPE, "frx_moe_layer_ep_allreduce: %lld blocks would not be resident together", blocks);
+    const EpLayout L = ep_layout(comm->max_T, comm->n);
+    EpParams ep{};
+    ep.world = comm->world;
+    ep.rank = comm->rank;
+    for (int q = 0; q < comm->world; ++q) {
+        if (!comm->buffer[q]) return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: buffer of rank %d is null", q);
+        ep.partial[q] = static_cast<float*>(comm->buffer[q]);
+        ep.flags[q] = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(comm->buffer[q]) + L.flags);
+    }
+    ep.state = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(comm->buffer[comm->rank]) + L.state);
+    ep.slot_floats = L.slot_floats;
+    const size_t d = frx_moe_decode_workspace_bytes(T, K, n, ff), r = align_up(size_t(T) * K * 4);
+    if (ws_bytes < d + 2 * r) return fail(FRX_ERR_WORKSPACE, "frx_moe_layer_ep_allreduce: workspace %zu < %zu", ws_bytes, d + 2 * r);
+    auto* base = static_cast<uint8_t*>(ws);
+    int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
+    float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
+    return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream, &ep);
 }
 
 size_t frx_moe_layer_host_workspace_bytes(int T, int K, int n, int ff, int E) {

@@ -4,6 +4,9 @@
 Decode-sized batches: activations and router logits are replicated, every rank routes (the router
 is deterministic, so all ranks agree bit for bit), each rank runs the experts it holds and forms
 the weighted partial sum of its slots, and one all-reduce of [T][n] fp32 gives the layer output.
+The all-reduce is either NCCL's (moe_layer_ep) or fused into the layer's last kernel over peer
+memory (EpComm + moe_layer_ep_fused: no NCCL call on the data path, so steps can be captured in a
+CUDA graph).
 """
 from __future__ import annotations
 
@@ -39,10 +42,70 @@ def moe_layer_ep(experts_local: int, stride: int, E: int, e_lo: int, e_hi: int, 
     """Router on every rank, local experts, all-reduce of the partial sums. `shared` is the shared
     expert's blob on the one rank that computes it and None elsewhere."""
     T = x.shape[0]
-    check(lib.frx_route_topk(moe._stream(), moe._ptr(logits), T, E, K, moe._ptr(ids_out), moe._ptr(wts_out), None, None, 1 << 30))
-    moe_decode_ep(experts_local, stride, E, e_lo, e_hi, shared, n, ff, x, ids_out, wts_out, gate_logit if shared else None, out, ws)
+    wp, wb = moe._ws_ptr(ws)
+    check(lib.frx_moe_layer_ep(C.c_void_p(experts_local), stride, E, e_lo, e_hi, C.c_void_p(shared) if shared else None, n, ff, moe._ptr(x),
+                               moe._ptr(logits), moe._ptr(gate_logit) if shared else None, T, K, moe._ptr(out), moe._ptr(ids_out),
+                               moe._ptr(wts_out), wp, wb, moe._stream()))
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(out, group=group)
+    return out
+
+
+class _CommStruct(C.Structure):
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("max_T", C.c_int), ("n", C.c_int), ("buffer", C.c_void_p * 8)]
+
+
+class EpComm:
+    """The peer-memory communication state of frx_moe_layer_ep_allreduce: one device buffer per
+    rank (two slots of partial sums [max_T][n], flag words, counters), every rank's buffer mapped
+    into every other rank's address space through CUDA IPC. Collective: every rank of `group`
+    constructs it at the same time. The handles travel through torch.distributed (set-up only)."""
+
+    def __init__(self, max_T: int, n: int, group=None):
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise moe.FrxError(1, "EpComm: at most 8 ranks")
+        self.max_T, self.n = max_T, n
+        self._own = C.c_void_p()
+        check(lib.frx_ep_buffer_create(C.byref(self._own), max_T, n))
+        handle = C.create_string_buffer(64)
+        check(lib.frx_ipc_export(self._own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._mapped = []
+        ptrs = []
+        for q in range(self.world):
+            if q == self.rank:
+                ptrs.append(self._own.value)
+                continue
+            m = C.c_void_p()
+            check(lib.frx_ipc_open(C.create_string_buffer(handles[q], 64), C.byref(m)))
+            self._mapped.append(m)
+            ptrs.append(m.value)
+        self.struct = _CommStruct(self.world, self.rank, max_T, n, (C.c_void_p * 8)(*ptrs))
+        dist.barrier(group=group)   # every rank has mapped every buffer before anyone uses them
+
+    def close(self) -> None:
+        for m in self._mapped:
+            lib.frx_ipc_close(m)
+        self._mapped = []
+        if self._own:
+            lib.frx_ep_buffer_destroy(self._own)
+            self._own = C.c_void_p()
+
+
+def moe_layer_ep_fused(comm: EpComm, experts_local: int, stride: int, E: int, e_lo: int, e_hi: int, shared: int | None, n: int, ff: int,
+                       x: torch.Tensor, logits: torch.Tensor, gate_logit: torch.Tensor | None, K: int, out: torch.Tensor,
+                       ids_out: torch.Tensor, wts_out: torch.Tensor, ws: torch.Tensor, stream=None) -> torch.Tensor:
+    """Router on every rank, local experts, and the all-reduce inside the layer's last kernel (peer
+    loads over NVLink, partial sums added in rank order on every rank). `out` is the complete layer
+    output on every rank. Every rank must make the same sequence of calls."""
+    T = x.shape[0]
+    wp, wb = moe._ws_ptr(ws)
+    check(lib.frx_moe_layer_ep_allreduce(C.c_void_p(experts_local), stride, E, e_lo, e_hi, C.c_void_p(shared) if shared else None, n, ff,
+                                         moe._ptr(x), moe._ptr(logits), moe._ptr(gate_logit) if shared else None, T, K, moe._ptr(out),
+                                         moe._ptr(ids_out), moe._ptr(wts_out), C.byref(comm.struct), wp, wb, moe._stream(stream)))
     return out
 
 

@@ -60,6 +60,14 @@ SIGNATURES = {
     "frx_moe_decode_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_layer_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_ep_buffer_bytes": (_sz, [_i, _i]),
+    "frx_ep_buffer_create": (_i, [_vp, _i, _i]),
+    "frx_ep_buffer_destroy": (_i, [_vp]),
+    "frx_ipc_export": (_i, [_vp, _vp]),
+    "frx_ipc_open": (_i, [_vp, _vp]),
+    "frx_ipc_close": (_i, [_vp]),
+    "frx_moe_layer_ep_allreduce": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "frx_moe_layer_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "frx_moe_layers_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

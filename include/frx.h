@@ -186,6 +186,47 @@ int frx_moe_layer(const void* experts, size_t stride, int E, const void* shared,
                   const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out,
                   float* wts_out, void* ws, size_t ws_bytes, frx_stream_t stream);
 
+/* Expert-parallel form of frx_moe_layer: every rank routes (the logits are replicated, so ids and
+ * weights are identical everywhere), this rank computes the experts [e_lo, e_hi) it holds
+ * (`experts_local` points at the blob of expert e_lo) and `out` receives its partial sums, as
+ * frx_moe_decode_ep. */
+int frx_moe_layer_ep(const void* experts_local, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
+                     const float* x, const float* logits, const float* gate_logit, int T, int K, float* out, int32_t* ids_out,
+                     float* wts_out, void* ws, size_t ws_bytes, frx_stream_t stream);
+
+/* ---- Expert parallel with the all-reduce fused into the combine (peer memory over NVLink) ------
+ *
+ * Every rank owns one communication buffer (frx_ep_buffer_create; device memory that other
+ * processes of the node map through CUDA IPC: frx_ipc_export / frx_ipc_open). It holds two slots of
+ * partial sums [max_T][n] fp32, one flag word per peer and two local counters. frx_ep_comm lists
+ * every rank's buffer as mapped on this device (entry `rank` is the local one).
+ *
+ * frx_moe_layer_ep_allreduce = frx_moe_layer_ep, but its last kernel, after forming this rank's
+ * weighted partial sums, stores them into the rank's own buffer, tells every peer (one flag word
+ * each, release at system scope), waits until every peer has told it (bounded: after 2 s the
+ * workspace status reports a time-out and the kernel finishes), and adds the peers' partial sums
+ * to its own, in rank order on every rank, so all ranks get the same bits. `out` then holds the
+ * complete layer output on every rank. No NCCL call is involved, so a step can be captured in a
+ * CUDA graph. All ranks must make the same sequence of calls with the same comm; T <= 64 and
+ * T <= max_T. The reference is single-GPU and has no counterpart. */
+#define FRX_EP_MAX_RANKS 8
+typedef struct frx_ep_comm {
+    int world, rank;
+    int max_T, n;
+    void* buffer[FRX_EP_MAX_RANKS]; /* every rank's communication buffer, as mapped on this device */
+} frx_ep_comm;
+size_t frx_ep_buffer_bytes(int max_T, int n);
+int frx_ep_buffer_create(void** buffer, int max_T, int n);   /* allocated and zeroed; once, at set-up */
+int frx_ep_buffer_destroy(void* buffer);
+#define FRX_IPC_HANDLE_BYTES 64
+int frx_ipc_export(const void* buffer, void* handle);        /* handle: FRX_IPC_HANDLE_BYTES bytes to send to the peers */
+int frx_ipc_open(const void* handle, void** mapped);         /* a peer's buffer on this device */
+int frx_ipc_close(void* mapped);
+int frx_moe_layer_ep_allreduce(const void* experts_local, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
+                               const float* x, const float* logits, const float* gate_logit, int T, int K, float* out,
+                               int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
+                               frx_stream_t stream);
+
 /* The same with host buffers: x_host [T][n], logits_host [T][E], gate_logit_host [T] or null are
  * copied to the device, the layer runs, out_host [T][n] is copied back, and the call returns after
  * the stream has drained. `ws` is a device workspace of frx_moe_layer_host_workspace_bytes. */

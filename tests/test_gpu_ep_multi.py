@@ -38,6 +38,23 @@ def _worker(rank, world, port_no, ret):
                     out, ids_o, wts_o, ws)
     full = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, cuda(x), cuda(ids), cuda(wts), None)
     err_decode = rel_max(out.cpu().numpy(), full.cpu().numpy())
+    # decode form with the all-reduce fused into the combine over peer memory: three calls in a row
+    # (both buffer slots and a reuse), every rank must end with the same bits
+    comm = ep.EpComm(T, n)
+    err_fused, same_bits = 0.0, True
+    for it in range(3):
+        xi = synth.activations(T, n, seed=50 + it)
+        want = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, cuda(xi), cuda(ids), cuda(wts), None)
+        got = torch.empty(T, n, device="cuda")
+        ep.moe_layer_ep_fused(comm, ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr if rank == 0 else None, n, ff, cuda(xi),
+                              cuda(lg), None, K, got, ids_o, wts_o, ws)
+        torch.cuda.synchronize()
+        moe.workspace_status(ws)
+        err_fused = max(err_fused, rel_max(got.cpu().numpy(), want.cpu().numpy()))
+        gathered = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got)
+        same_bits = same_bits and all(torch.equal(g, gathered[0]) for g in gathered)
+    comm.close()
     # prefill form: this rank's half of the tokens
     Tl = T // world
     xs, ls = x[rank * Tl:(rank + 1) * Tl], lg[rank * Tl:(rank + 1) * Tl]
@@ -45,7 +62,7 @@ def _worker(rank, world, port_no, ret):
     ref = port.moe_layer(ex.routed_planar(), ex.blob_bytes, None, n, ff, xs, ids[rank * Tl:(rank + 1) * Tl], wts[rank * Tl:(rank + 1) * Tl])
     err_prefill = rel_max(o2.cpu().numpy(), ref)
     ids_ok = bool(np.array_equal(i2.cpu().numpy(), ids[rank * Tl:(rank + 1) * Tl]))
-    ret[rank] = (err_decode, err_prefill, ids_ok)
+    ret[rank] = (err_decode, err_prefill, ids_ok, err_fused, same_bits)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -66,6 +83,7 @@ def test_two_gpu_expert_parallel_layers():
                 pytest.fail("a rank did not finish in time")
             assert p.exitcode == 0
         for r in range(2):
-            err_decode, err_prefill, ids_ok = ret[r]
+            err_decode, err_prefill, ids_ok, err_fused, same_bits = ret[r]
             assert ids_ok
             assert err_decode < 1e-5 and err_prefill < 1e-5
+            assert err_fused < 1e-5 and same_bits
