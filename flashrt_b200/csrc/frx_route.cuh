@@ -49,15 +49,31 @@ __device__ __forceinline__ void route_warp(const float* __restrict__ l, int E, i
             key[i] = e < E ? order_key(l[e] + 0.0f) : 0u;
         }
     }
-    uint32_t best = 0;
-    int best_i = 0x7fffffff;
+    // every lane keeps its best and its second best key (with their experts): when its best is
+    // taken, the second moves up without a rescan; the lane rescans only when it is hit again
+    uint32_t best = 0, next = 0;
+    int best_i = 0x7fffffff, next_i = 0x7fffffff;
+    auto rescan = [&]() {
+        best = 0;
+        next = 0;
+        best_i = 0x7fffffff;
+        next_i = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        if (key[i] > best) {   // ascending index within a lane: the first maximum wins
-            best = key[i];
-            best_i = slot_expert(i);
+        for (int i = 0; i < V; ++i) {
+            const uint32_t kv = key[i];
+            if (kv > best) {   // ascending index within a lane: the first maximum wins
+                next = best;
+                next_i = best_i;
+                best = kv;
+                best_i = slot_expert(i);
+            } else if (kv > next) {
+                next = kv;
+                next_i = slot_expert(i);
+            }
         }
-    }
+    };
+    rescan();
+    bool next_valid = true;
     const uint32_t kmax = __reduce_max_sync(0xffffffffu, best);
     const float m = key_value(kmax);
     double part[4] = {0.0, 0.0, 0.0, 0.0};   // four running sums: the additions are slow and would otherwise form one chain
@@ -74,16 +90,17 @@ __device__ __forceinline__ void route_warp(const float* __restrict__ l, int E, i
     for (int k = 0; k < K; ++k) {
         const uint32_t top = __reduce_max_sync(0xffffffffu, best);
         const int sel = __reduce_min_sync(0xffffffffu, best == top ? best_i : 0x7fffffff);
-        if ((vec ? (sel >> 2) & 31 : sel & 31) == lane) {   // the owner retires it and finds its next best
-            best = 0;
-            best_i = 0x7fffffff;
+        if ((vec ? (sel >> 2) & 31 : sel & 31) == lane) {   // the owner retires it and moves its next best up
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
+            for (int i = 0; i < V; ++i)
                 if (slot_expert(i) == sel) key[i] = 0u;
-                if (key[i] > best) {
-                    best = key[i];
-                    best_i = slot_expert(i);
-                }
+            if (next_valid) {
+                best = next;
+                best_i = next_i;
+                next_valid = false;
+            } else {
+                rescan();
+                next_valid = true;
             }
         }
         if (lane == k) {
