@@ -964,20 +964,28 @@ struct StreamCfg {
     uint32_t smem_gu = 0, smem_dn = 0;
 };
 
-int stream_cfg(int n, int ff, StreamCfg& c) {
+// max_items: an upper bound of the work items of a launch when the caller knows one (decode), else
+// 0. With few items most warps of a 16-warp block would have no task at all while the busy ones
+// are limited by their two ring slots (a warp streams its task with only that much in flight):
+// blocks of 4 or 8 warps with deeper rings serve small batches better.
+int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
     const int budget = max_smem_optin() - 1024;
     if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
     // a task is fetched as `chunks` chunks; the preferred warp count is kept if
     // every warp can have at least two ring slots (up to four), else fewer warps are used
     // and, first of all, three item buffers rather than two
-    auto fit = [&](int kdim, uint32_t task_bytes, int chunks, int& nw, int& cpt, int& rpw, int& nbuf, uint32_t& bytes) {
+    const int sms = sm_count();
+    auto fit = [&](int kdim, uint32_t task_bytes, int chunks, long long max_tasks, int& nw, int& cpt, int& rpw, int& nbuf, uint32_t& bytes) {
         cpt = chunks;
         const uint32_t chunk = task_bytes / uint32_t(cpt);
-        const int prefs[3] = {g_nw, g_nw > 12 ? 12 : 8, 8};
+        int first = g_nw;
+        if (max_tasks > 0 && max_tasks <= 4LL * sms) first = 4;
+        else if (max_tasks > 0 && max_tasks <= 8LL * sms) first = 8;
+        const int prefs[3] = {first, first > 12 ? 12 : 8, 8};
         for (int k = 0; k < 3; ++k) {
             nw = prefs[k];
             for (nbuf = kMaxItemBufs; nbuf >= 2; --nbuf)
-                for (rpw = 4; rpw >= 2; --rpw) {
+                for (rpw = nw <= 4 ? 8 : 4; rpw >= 2; --rpw) {
                     bytes = smem_plan(kdim, chunk, nw * rpw, nbuf).total;
                     if (int(bytes) <= budget) return true;
                 }
@@ -987,8 +995,9 @@ int stream_cfg(int n, int ff, StreamCfg& c) {
     const int gu_units = n / kUnitK, dn_units = ff / kUnitK;
     // gate/up: a task is two groups, fetched in K slices; down: kDownGroups groups in two chunks of whole groups
     const int gu_chunks = gu_units % 4 == 0 ? 4 : gu_units % 2 == 0 ? 2 : 1;
-    if (!fit(n, uint32_t(gu_units) * kUnitBytes * 2, gu_chunks, c.nw_gu, c.cpt_gu, c.rpw_gu, c.nbuf_gu, c.smem_gu) ||
-        !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, 2, c.nw_dn, c.cpt_dn, c.rpw_dn, c.nbuf_dn, c.smem_dn))
+    if (!fit(n, uint32_t(gu_units) * kUnitBytes * 2, gu_chunks, max_items * (ff / 16), c.nw_gu, c.cpt_gu, c.rpw_gu, c.nbuf_gu, c.smem_gu) ||
+        !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, 2, max_items * (n / 16 / kDownGroups), c.nw_dn, c.cpt_dn, c.rpw_dn, c.nbuf_dn,
+             c.smem_dn))
         return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
     return FRX_OK;
 }
@@ -1006,6 +1015,7 @@ void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_
 template <bool GATE_UP>
 void launch_stream(const StreamParams& p, int nw, int upc, uint32_t smem, cudaStream_t stream) {
     switch (nw) {
+        case 4: launch_stream_nw<GATE_UP, 4>(p, upc, smem, stream); break;
         case 8: launch_stream_nw<GATE_UP, 8>(p, upc, smem, stream); break;
         case 12: launch_stream_nw<GATE_UP, 12>(p, upc, smem, stream); break;
         default: launch_stream_nw<GATE_UP, 16>(p, upc, smem, stream); break;
@@ -1023,6 +1033,8 @@ int set_smem_attr() {
     if (dev >= 0 && dev < 64 && done[dev]) return FRX_OK;
     const int lim = max_smem_optin();
     const void* fns[] = {
+        reinterpret_cast<const void*>(k_stream<true, 4, 4>),   reinterpret_cast<const void*>(k_stream<true, 4, 0>),
+        reinterpret_cast<const void*>(k_stream<false, 4, 4>),  reinterpret_cast<const void*>(k_stream<false, 4, 0>),
         reinterpret_cast<const void*>(k_stream<true, 8, 4>),   reinterpret_cast<const void*>(k_stream<true, 8, 0>),
         reinterpret_cast<const void*>(k_stream<false, 8, 4>),  reinterpret_cast<const void*>(k_stream<false, 8, 0>),
         reinterpret_cast<const void*>(k_stream<true, 12, 4>),  reinterpret_cast<const void*>(k_stream<true, 12, 0>),
@@ -1101,7 +1113,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
     const Layout L = make_layout(T, K, n, ff);
     if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_decode: workspace %zu < %zu", ws_bytes, L.total);
     StreamCfg cfg;
-    if (int rc = stream_cfg(n, ff, cfg)) return rc;
+    if (int rc = stream_cfg(n, ff, cfg, L.max_items)) return rc;   // max_items: the most items a chunk of tokens can make
     if (int rc = set_smem_attr()) return rc;
     auto* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + L.status);
