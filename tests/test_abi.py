@@ -40,6 +40,12 @@ def test_sizes(L):
     assert L.lib.frx_moe_prefill_workspace_bytes(4096, 10, 2048, 512, 512) > 4096 * 10 * 512 * 4
     assert L.lib.frx_moe_hits_scratch_bytes(10, 2560, 640, 3) > 0
     assert L.lib.frx_moe_layer_workspace_bytes(8, 10, 2048, 512) > L.lib.frx_moe_decode_workspace_bytes(8, 10, 2048, 512)
+    # the many-layer host form adds four staging slots, whatever the number of layers
+    assert (L.lib.frx_moe_layers_host_workspace_bytes(64, 10, 2048, 512, 512) - L.lib.frx_moe_layer_workspace_bytes(64, 10, 2048, 512)
+            >= 4 * 64 * (2 * 2048 + 512 + 1) * 4)
+    # expert-parallel buffer: two slots of partial sums, flags and counters
+    assert 2 * 64 * 2048 * 4 < L.lib.frx_ep_buffer_bytes(64, 2048) <= 2 * 64 * 2048 * 4 + 1024
+    assert L.lib.frx_ep_buffer_bytes(0, 2048) == 0
 
 
 def test_bad_arguments_are_rejected_with_a_message(L):
@@ -58,6 +64,9 @@ def test_bad_arguments_are_rejected_with_a_message(L):
     assert "workspace" in L.last_error()
     assert L.lib.frx_moe_prefill(one, 884736, 512, 2048, 512, one, one, 8, 10, one, one, 16, None) == L.ERR_WORKSPACE
     assert L.lib.frx_moe_hits(one, one, 10, one, 2560, 640, one, 1 << 30, one, None, 200) == L.ERR_SHAPE
+    assert L.lib.frx_moe_layer_ep_allreduce(one, 884736, 512, 0, 256, None, 2048, 512, one, one, None, 8, 10, one, None, None, None, one, 1 << 30,
+                                            None) == L.ERR_ARG   # no communication state
+    assert L.lib.frx_moe_layers_host(None, 884736, 512, None, 2048, 512, one, one, None, 2, 8, 10, one, one, 1 << 30, None) == L.ERR_ARG
     with pytest.raises(L.FrxError):
         L.check(L.ERR_SHAPE)
 
