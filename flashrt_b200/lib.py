@@ -60,6 +60,7 @@ SIGNATURES = {
     "frx_moe_decode_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_router_logits": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "frx_moe_layer_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_ep_buffer_bytes": (_sz, [_i, _i]),
     "frx_ep_buffer_create": (_i, [_vp, _i, _i]),

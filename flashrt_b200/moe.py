@@ -147,6 +147,20 @@ def moe_route_topk(logits: torch.Tensor, k: int, counts: torch.Tensor | None = N
     return ids, wts
 
 
+def router_logits(w_router: torch.Tensor, w_gate: torch.Tensor | None, x: torch.Tensor, stream=None):
+    """The projection in front of the router (frx_router_logits): w_router bf16 [E][n], w_gate bf16 [n]
+    or None, x fp32 [T][n] -> (logits fp32 [T][E], gate_logit fp32 [T] or None)."""
+    _dev(w_router, w_gate, x)
+    if w_router.dtype != torch.bfloat16 or (w_gate is not None and w_gate.dtype != torch.bfloat16) or x.dtype != torch.float32:
+        raise FrxError(_l.ERR_ARG, "router_logits: bf16 weights and fp32 activations")
+    T, n = x.shape
+    E = w_router.shape[0]
+    logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    gate = torch.empty(T, dtype=torch.float32, device=x.device) if w_gate is not None else None
+    check(lib.frx_router_logits(_stream(stream), _ptr(w_router), _ptr(w_gate), _ptr(x), T, E, n, _ptr(logits), _ptr(gate)))
+    return logits, gate
+
+
 def quantize_q8(x: torch.Tensor, stream=None):
     """q2_0::quantize_q8 for every row of x [T][n]: codes int8 [T][n], scales float [T][n/32]."""
     _dev(x)

@@ -179,6 +179,14 @@ int frx_moe_decode_static(const void* experts, size_t stride, int E, const void*
  * "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
 size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what);
 
+/* The projection in front of the router (k_bf16_multi, arch/qwen4exp/blocks.cu:83-120, as called at
+ * moe_fast.cu:1039-1042 and moe_stream.cu:145-149): logits[t][e] = sum_k w_router[e][k] * x[t][k],
+ * w_router bf16 [E][n] row-major, x fp32 [T][n], exact products and fp32 sums; with w_gate (bf16 [n],
+ * may be null) also gate_logit[t] = sum_k w_gate[k] * x[t][k], the shared expert's gate logit that
+ * frx_moe_layer takes. n a multiple of 256 (as in the reference), pointers 16-byte aligned. */
+int frx_router_logits(frx_stream_t stream, const void* w_router, const void* w_gate, const float* x, int T, int E, int n,
+                      float* logits, float* gate_logit);
+
 /* Router + layer in one call: logits [T][E] -> top-K -> frx_moe_decode. ids_out / wts_out [T][K]
  * (may be null) receive the routing. Workspace: frx_moe_layer_workspace_bytes. */
 size_t frx_moe_layer_workspace_bytes(int T, int K, int n, int ff);

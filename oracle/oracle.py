@@ -236,6 +236,16 @@ _port = None
 _ref = None
 
 
+def router_logits(w_bf16: np.ndarray, x: np.ndarray) -> np.ndarray:
+    """CPU restatement of the router projection (arch/qwen4exp/blocks.cu:83-120, k_bf16_multi with
+    no epilogue): y[t][r] = sum_k bf16(w[r][k]) * x[t][k]. w_bf16: uint16 [R][n], the bf16 bit
+    patterns; x: float32 [T][n]. The reference adds in fp32 in an order fixed by its launch shape;
+    this restatement adds in float64 and is what a tolerance is measured against. Parity unpinned:
+    the reference's tests hold no vector for this kernel."""
+    w = (w_bf16.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    return x.astype(np.float64) @ w.T
+
+
 def port() -> Port:
     global _port
     if _port is None:

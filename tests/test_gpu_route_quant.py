@@ -80,3 +80,25 @@ def test_quantize_q8_empty_and_bad_shape():
     assert q.shape == (0, 256)
     with pytest.raises(moe.FrxError):
         moe.quantize_q8(torch.zeros(2, 48, device="cuda"))
+
+
+@pytest.mark.parametrize("T,E,n,gate", [(1, 512, 2048, True), (64, 512, 2048, True), (7, 33, 512, False), (200, 128, 1024, True)])
+def test_router_projection(T, E, n, gate):
+    # logits = W_r x (bf16 weights, fp32 activations and sums) and the shared expert's gate logit
+    # in the same launch; tolerance against a float64 sum: fp32 accumulation over n terms
+    from oracle import oracle
+    rng = np.random.default_rng(3)
+    w = torch.from_numpy(rng.standard_normal((E, n), dtype=np.float32) * 0.05).to(torch.bfloat16)
+    wg = torch.from_numpy(rng.standard_normal(n, dtype=np.float32) * 0.05).to(torch.bfloat16) if gate else None
+    x = rng.standard_normal((T, n), dtype=np.float32)
+    logits, g = moe.router_logits(w.cuda(), wg.cuda() if gate else None, cuda(x))
+    want = oracle.router_logits(w.view(torch.int16).numpy().view(np.uint16), x)
+    scale = np.abs(want).max()
+    assert np.abs(logits.cpu().numpy() - want).max() < 2e-6 * scale * np.sqrt(n / 256)
+    if gate:
+        wantg = oracle.router_logits(wg.view(torch.int16).numpy().view(np.uint16)[None, :], x)[:, 0]
+        assert np.abs(g.cpu().numpy() - wantg).max() < 2e-6 * max(scale, np.abs(wantg).max()) * np.sqrt(n / 256)
+    # feeding the router: the ids of the GPU logits are the ids of their own values
+    ids, _ = moe.moe_route_topk(logits, min(8, E))
+    top = np.argsort(-logits.cpu().numpy(), axis=1, kind="stable")[:, :min(8, E)]
+    assert np.array_equal(ids.cpu().numpy(), top)

@@ -154,3 +154,15 @@ def test_route_ties_and_weights(port):
         p = np.exp(lg[t].astype(np.float64) - lg[t].max())
         p /= p.sum()
         assert np.abs(wts[t] - p[order] / p[order].sum()).max() < 1e-5
+
+
+def test_router_projection_restatement_widens_bf16_exactly():
+    # bf16 -> fp32 is a 16-bit shift; the restatement's float64 sum against torch's own widening
+    import torch
+    from oracle import oracle
+    rng = np.random.default_rng(5)
+    w = torch.from_numpy(rng.standard_normal((9, 256), dtype=np.float32)).to(torch.bfloat16)
+    x = rng.standard_normal((3, 256), dtype=np.float32)
+    got = oracle.router_logits(w.view(torch.int16).numpy().view(np.uint16), x)
+    want = x.astype(np.float64) @ w.to(torch.float64).numpy().T
+    assert np.array_equal(got, want)
