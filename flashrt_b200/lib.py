@@ -60,6 +60,13 @@ SIGNATURES = {
     "frx_moe_decode_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "frx_moe_layer": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_gguf_open": (_i, [_vp, C.c_char_p]),
+    "frx_gguf_close": (_i, [_vp]),
+    "frx_gguf_tensor_count": (_i, [_vp]),
+    "frx_gguf_tensor_name": (C.c_char_p, [_vp, _i]),
+    "frx_gguf_get_int": (C.c_int64, [_vp, C.c_char_p, C.c_int64]),
+    "frx_gguf_tensor": (_i, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _vp]),
+    "frx_arena_load_gguf": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "frx_router_logits": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "frx_moe_layer_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_ep_buffer_bytes": (_sz, [_i, _i]),
@@ -90,7 +97,7 @@ for _name, (_res, _args) in SIGNATURES.items():
 
 
 def last_error() -> str:
-    return lib.frx_last_error().decode()
+    return lib.frx_last_error().decode(errors="replace")
 
 
 def check(rc: int) -> None:

@@ -120,6 +120,13 @@ class ExpertArena:
         src_stride = self.blob_bytes if src_stride is None else src_stride
         check(lib.frx_arena_load_planar(self._h, layer, expert0, count, _ptr(planar), src_stride, _stream(stream)))
 
+    def read_planar(self, layer: int, expert0: int, count: int, stream=None) -> torch.Tensor:
+        """The planar form of `count` blobs of the arena (the inverse of load_planar): uint8 [count][blob_bytes]."""
+        out = torch.zeros(count, self.blob_bytes, dtype=torch.uint8, device="cuda")
+        check(lib.frx_q2_untile_experts(C.c_void_p(self.blob(layer, expert0)), self.stride, _ptr(out), self.blob_bytes, count, self.n, self.ff,
+                                        _stream(stream)))
+        return out
+
     def close(self) -> None:
         if self._h:
             lib.frx_arena_destroy(self._h)
@@ -130,6 +137,46 @@ class ExpertArena:
             self.close()
         except Exception:
             pass
+
+
+class Gguf:
+    """Metadata and tensor directory of one GGUF file (frx_gguf_open); tensor data stays on disk."""
+
+    def __init__(self, path: str):
+        self._h = C.c_void_p()
+        check(lib.frx_gguf_open(C.byref(self._h), path.encode()))
+
+    def tensor_names(self) -> list[str]:
+        return [lib.frx_gguf_tensor_name(self._h, i).decode() for i in range(lib.frx_gguf_tensor_count(self._h))]
+
+    def get_int(self, key: str, fallback: int = 0) -> int:
+        return int(lib.frx_gguf_get_int(self._h, key.encode(), fallback))
+
+    def tensor(self, name: str) -> dict:
+        typ, nd, dims, off, nbytes = C.c_uint32(), C.c_int(), (C.c_int64 * 4)(), C.c_uint64(), C.c_uint64()
+        check(lib.frx_gguf_tensor(self._h, name.encode(), C.byref(typ), C.byref(nd), dims, C.byref(off), C.byref(nbytes)))
+        return {"type": typ.value, "dims": list(dims)[:nd.value], "offset": off.value, "bytes": nbytes.value}
+
+    def close(self) -> None:
+        if self._h:
+            lib.frx_gguf_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def arena_load_gguf(arena: "ExpertArena", gguf: Gguf, layer0: int, n_layer: int, n_expert: int, stream=None) -> tuple[int, float]:
+    """Fills arena layers [layer0, layer0 + n_layer) with the Q2_0 experts of the file
+    (blk.<l>.ffn_{gate,up,down}_exps.weight): read, repacked and tiled on the device. Returns
+    (bytes read, seconds)."""
+    nbytes, secs = C.c_uint64(), C.c_double()
+    check(lib.frx_arena_load_gguf(arena._h, gguf._h, layer0, n_layer, n_expert, arena.n, arena.ff, _stream(stream), C.byref(nbytes),
+                                  C.byref(secs)))
+    return int(nbytes.value), float(secs.value)
 
 
 # ---- routing and quantization ------------------------------------------------------------------

@@ -77,3 +77,53 @@ def tie_heavy_logits(T: int, E: int, seed: int = 9) -> np.ndarray:
     reference's router test, tests/test_route_topk.cpp:24-27)."""
     g = np.random.default_rng(seed).standard_normal((T, E), dtype=np.float32) * np.float32(2.0)
     return (np.round(g * 4.0) / 4.0).astype(np.float32)
+
+
+def write_gguf(path: str, meta: dict, tensors: list, alignment: int = 32, version: int = 3) -> dict:
+    """Writes a GGUF file (the published container format) for tests and examples. meta: key ->
+    int (stored as u32, or i64 when negative or large), float (f32), bool, str, or a list of str /
+    int (an array). tensors: (name, dims fastest first, ggml type id, uint8 data) in file order.
+    Returns name -> absolute file offset of the tensor's data."""
+    import struct
+
+    def gstr(s: str) -> bytes:
+        b = s.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    def value(v) -> bytes:
+        if isinstance(v, bool):
+            return struct.pack("<IB", 7, int(v))
+        if isinstance(v, int):
+            return struct.pack("<II", 4, v) if 0 <= v < 2 ** 32 else struct.pack("<Iq", 11, v)
+        if isinstance(v, float):
+            return struct.pack("<If", 6, v)
+        if isinstance(v, str):
+            return struct.pack("<I", 8) + gstr(v)
+        if isinstance(v, list):
+            if all(isinstance(x, str) for x in v):
+                return struct.pack("<IIQ", 9, 8, len(v)) + b"".join(gstr(x) for x in v)
+            return struct.pack("<IIQ", 9, 5, len(v)) + b"".join(struct.pack("<i", x) for x in v)
+        raise TypeError(type(v))
+
+    meta = dict(meta)
+    if alignment != 32:
+        meta["general.alignment"] = alignment
+    head = struct.pack("<IIQQ", 0x46554747, version, len(tensors), len(meta))
+    for k, v in meta.items():
+        head += gstr(k) + value(v)
+    rel, at = {}, 0
+    for name, dims, typ, data in tensors:
+        at = (at + alignment - 1) // alignment * alignment
+        rel[name] = at
+        head += gstr(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, at)
+        at += data.size
+    data_start = (len(head) + alignment - 1) // alignment * alignment
+    with open(path, "wb") as f:
+        f.write(head)
+        f.write(b"\0" * (data_start - len(head)))
+        pos = 0
+        for name, dims, typ, data in tensors:
+            f.write(b"\0" * (rel[name] - pos))
+            f.write(np.ascontiguousarray(data).tobytes())
+            pos = rel[name] + data.size
+    return {name: data_start + off for name, off in rel.items()}

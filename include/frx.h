@@ -179,6 +179,26 @@ int frx_moe_decode_static(const void* experts, size_t stride, int E, const void*
  * "order" int32 [T][K]. Valid for T <= 64. Returns (size_t)-1 for other names. */
 size_t frx_moe_decode_workspace_offset(int T, int K, int n, int ff, const char* what);
 
+/* ---- GGUF container and the expert loader (core/gguf.hpp:17-60, arch/qwen4exp/experts.cpp:65-131) ----
+ * frx_gguf_open parses the metadata and the tensor directory of one GGUF file (format version 2 or
+ * 3; split files are not handled); tensor data stays on disk. frx_gguf_tensor reports a tensor's
+ * ggml type id, dimensions (fastest first, unused ones 1), absolute file offset and byte count.
+ * frx_arena_load_gguf reads the Q2_0 expert tensors blk.<l>.ffn_{gate,up,down}_exps.weight (ggml type
+ * 42, expert e's matrix at e * mat_bytes) of layers [layer0, layer0 + n_layer) and fills arena
+ * layers of the same numbers: repacked to the planar form and tiled on the device. It allocates
+ * its staging (pinned host and device) for the duration of the call and returns after the stream
+ * has drained; bytes_read / seconds (may be null) report the volume and the wall time. */
+typedef struct frx_gguf frx_gguf;
+int frx_gguf_open(frx_gguf** out, const char* path);
+int frx_gguf_close(frx_gguf* g);
+int frx_gguf_tensor_count(const frx_gguf* g);
+const char* frx_gguf_tensor_name(const frx_gguf* g, int i);
+int64_t frx_gguf_get_int(const frx_gguf* g, const char* key, int64_t fallback);   /* integer or boolean metadata */
+int frx_gguf_tensor(const frx_gguf* g, const char* name, uint32_t* type, int* n_dims, int64_t* dims4, uint64_t* file_offset,
+                    uint64_t* bytes);
+int frx_arena_load_gguf(frx_arena* a, const frx_gguf* g, int layer0, int n_layer, int n_expert, int n, int ff, frx_stream_t stream,
+                        uint64_t* bytes_read, double* seconds);
+
 /* The projection in front of the router (k_bf16_multi, arch/qwen4exp/blocks.cu:83-120, as called at
  * moe_fast.cu:1039-1042 and moe_stream.cu:145-149): logits[t][e] = sum_k w_router[e][k] * x[t][k],
  * w_router bf16 [E][n] row-major, x fp32 [T][n], exact products and fp32 sums; with w_gate (bf16 [n],
