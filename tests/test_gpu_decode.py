@@ -225,3 +225,36 @@ def test_expert_parallel_partial_sums_add_up(port):
         assert np.all(np.isnan(ys[~local]))
         total += out.cpu().numpy()
     assert rel_max(total, full) < 1e-6
+
+
+def test_layer_replayed_from_a_cuda_graph_with_new_inputs(port):
+    # the decode entry takes every per-step value from device memory, so one captured graph serves
+    # every step: replay with new activations and logits in the same buffers, compare with direct calls
+    n, ff, E, K, T = 512, 256, 32, 4, 3      # a verify window: 1 token + 2 drafts
+    ex = Experts(port, n, ff, E)
+    x, lg, gate = torch.empty(T, n, device="cuda"), torch.empty(T, E, device="cuda"), torch.empty(T, device="cuda")
+    out = torch.empty(T, n, device="cuda")
+    ws = moe.workspace(moe.moe_layer_workspace_bytes(T, K, n, ff))
+
+    def fill(seed):
+        x.copy_(cuda(synth.activations(T, n, seed=seed)))
+        lg.copy_(cuda(synth.router_logits(T, E, seed=seed + 1)))
+        gate.copy_(cuda(np.linspace(-1, 1, T).astype(np.float32) * seed))
+
+    fill(1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # first call outside capture: shared-memory attributes are set once per device
+        moe.moe_layer(ex.base, ex.stride, E, ex.shared_ptr, n, ff, x, lg, gate, K, out=out, ws=ws)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        moe.moe_layer(ex.base, ex.stride, E, ex.shared_ptr, n, ff, x, lg, gate, K, out=out, ws=ws)
+    for seed in (2, 3, 4):
+        fill(seed)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = out.clone()
+        want = moe.moe_layer(ex.base, ex.stride, E, ex.shared_ptr, n, ff, x, lg, gate, K)
+        assert torch.equal(got, want), seed
+    moe.workspace_status(ws)
