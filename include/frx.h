@@ -269,7 +269,8 @@ int frx_moe_layer_host(const void* experts, size_t stride, int E, const void* sh
  * once outside any stream capture). experts[l], shared[l] (shared may be null, or shared[l] null):
  * device blobs of layer l; x_host[l] [T][n], logits_host[l] [T][E], gate_logit_host[l] [T] (the
  * array or an entry may be null), out_host[l] [T][n]: host buffers, pinned if the copies are to
- * overlap. Results are bit-identical to L calls of frx_moe_layer_host. Returns after everything
+ * overlap. Calls on one device must not run concurrently (they share the copy streams and their
+ * events). Results are bit-identical to L calls of frx_moe_layer_host. Returns after everything
  * has drained. `ws`: device workspace of frx_moe_layers_host_workspace_bytes (independent of L:
  * inputs and outputs pass through a ring of four staging slots). The reference has no counterpart:
  * its engine keeps activations on the device between layers. */
