@@ -469,7 +469,11 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uin
 template <bool GATE_UP, int NW, int UPC>
 __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    pdl_wait();
+    // Gate/up follows the kernel that makes the work items, so it waits for it at once. Down follows
+    // the hidden-row quantizer, which itself started only after gate/up and therefore after the
+    // items were complete: down reads the items and starts streaming its weights (constant data)
+    // while the quantizer is still running, and waits for it only before it touches the hidden rows.
+    if (GATE_UP) pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kdim = GATE_UP ? p.n : p.ff;
@@ -612,6 +616,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     // every warp has left that item) and goes on to item q + 1 as soon as all shares of it are in.
     // With three buffers a warp can run one item ahead of the slowest warp.
     const int ahead = nbuf - 1;
+    if (!GATE_UP) pdl_wait();   // the first weight chunks are already in flight
     for (int q = 0; q < ahead && q < nseg; ++q) {
         build(q);
         __syncwarp();
