@@ -226,6 +226,18 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
 
 // D (16x8 s32) = A * B + C with every element of C equal to `c`; the results come back packed in
 // pairs: lo = {D[g][2t], D[g][2t+1]}, hi = the same columns of row g + 8.
+// The same with the accumulator input given as four registers (a quad loaded from shared memory).
+__device__ __forceinline__ void mma_u8s8_c4(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1, const int4& c) {
+    asm volatile(
+        "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%8,%9,%10,%11};\n\t"
+        "mov.b64 %0, {d0,d1};\n\t"
+        "mov.b64 %1, {d2,d3};\n\t}"
+        : "=l"(lo), "=l"(hi)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w));
+}
+
 __device__ __forceinline__ void mma_u8s8_bias(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1, int c) {
     asm volatile(

@@ -106,9 +106,10 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  block b for its token in one 16-byte load;
 //   a [row][k/32]  the block scale d (through fp16), divided by 16 for the second half of a
 //                  64-block (see group_mma);
-//   c [row][k/32]  -(kMagic + sum(codes)) as a float (the sum times 16 for the second half): what is
-//                  added to an accumulator that started at kMagicBits, read as a float, to
-//                  get sum((q - 1) * code) exactly.
+//   c [row][k/32]  the int32 kMagicBits - sum(codes) (the sum times 16 for the second half), stored
+//                  through a float pointer: the value an MMA accumulator starts from, so that it
+//                  ends as kMagicBits + sum((q - 1) * code), which read as a float is kMagic plus
+//                  that sum, exactly.
 __device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int lane, int8_t* __restrict__ q, float* __restrict__ a,
                                                  float* __restrict__ c) {
     float d;
@@ -120,7 +121,7 @@ __device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int
     q[row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
     if (lane == 0) {
         a[blk] = s ? d * 0.0625f : d;
-        c[blk] = -(kMagic + float(s ? 16 * sum : sum));
+        c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
     }
 }
 __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
     if (j == 0) {
         const float ds = __half2float(__float2half_rn(d));
         a[blk] = s ? ds * 0.0625f : ds;
-        c[blk] = -(kMagic + float(s ? 16 * sum : sum));
+        c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
     }
 }
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
@@ -385,7 +386,7 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, in
     s.da = off;
     off += uint32_t(nbuf) * nb * 64;    // [buffer][block][t4] float4
     s.ci = off;
-    off += uint32_t(nbuf) * nb * 64;    // [buffer][block][t4] float4
+    off += uint32_t(nbuf) * nb * 128;   // [buffer][block][t4][half] int4
     s.item = off;
     off += uint32_t(nbuf) * 64;
     s.bars = off;          // `slots` ring barriers, then kMaxItemBufs "ready" and kMaxItemBufs "done" barriers
@@ -405,21 +406,24 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, in
 // word sit at bits 0, 2, 4, 6 of each byte; the first MMA takes fields 0 and 1 (w and w >> 2
 // masked with 0x03), the second takes fields 2 and 3 *in place* (masked with 0x30, i.e. the
 // codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
-// scale table, which holds d / 16 for the second half. Every accumulator starts at kMagicBits;
-// read as a float it is kMagic + sum(q * a), and adding the bias table's -(kMagic + sum(a))
-// (times 16 for the second half) leaves sum((q - 1) * a), exactly.
+// scale table, which holds d / 16 for the second half. Every accumulator starts at the table's
+// kMagicBits - sum(a) of its token column (times 16 for the second half; the four accumulator
+// inputs of a lane are one 16-byte load, used as they come and left intact for the second group),
+// so it ends as kMagicBits + sum((q - 1) * a): read as a float and with kMagic subtracted, exactly
+// the block's integer dot product.
 // Two groups of 16 M rows (group 1 at units + gstride) share the activation fragments, scales and
 // biases of each block, which are read once for both.
 template <int UPC>   // units per call when known at compile time, else 0
 __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
                                           const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
-                                          const ulonglong2* __restrict__ ci, int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
+                                          const int4* __restrict__ ci, int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
     const int g = lane >> 2, t4 = lane & 3;
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint8_t* codes = units + lane * 16;
     const uint8_t* scales = units + kUnitCodeBytes + g * 8;
     const uint4* bf_p = bfrag + b0 * 32 + lane;
-    const ulonglong2* ci_p = ci + b0 * 4 + t4;
+    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
+    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
     const ulonglong2* da_p = da + b0 * 4 + t4;
     const int n_units = UPC ? UPC : count;
 #pragma unroll(2)
@@ -435,22 +439,22 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uin
         for (int j = 0; j < 2; ++j) {
             const int b = 2 * u + j;
             const uint4 bf = bf_p[b * 32];
-            const ulonglong2 cb = ci_p[b * 4];  // {bias0[c0], bias0[c1]}, {bias1[c0], bias1[c1]}
+            const int4 cq0 = ci_p[b * 8], cq1 = ci_p[b * 8 + 1];   // accumulator inputs: kMagicBits - sum(codes), per column, both halves
             const ulonglong2 a = da_p[b * 4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const uint32_t w0 = j ? c[r].y : c[r].x, w1 = j ? c[r].w : c[r].z;
                 const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
                 uint64_t lo0, hi0, lo1, hi1;
-                mma_u8s8_bias(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, kMagicBits);
-                mma_u8s8_bias(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, kMagicBits);
+                mma_u8s8_c4(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, cq0);
+                mma_u8s8_c4(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, cq1);
                 const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[r].x), s_hi = *reinterpret_cast<const __half2*>(&sc[r].y);
                 const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
                 const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
                 // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
                 // multiply-add rounds exactly where the reference's two statements round once.
-                const uint64_t sumi_lo = fma2(a.y, add2(lo1, cb.y), mul2(a.x, add2(lo0, cb.x)));
-                const uint64_t sumi_hi = fma2(a.y, add2(hi1, cb.y), mul2(a.x, add2(hi0, cb.x)));
+                const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
+                const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
                 // The weight scale is applied with scalar multiplies: a packed multiply followed by a
                 // packed add is contracted into one fused multiply-add by the assembler, which would
                 // round once where the reference rounds twice.
@@ -574,7 +578,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const int buf = q % nbuf;
         uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag + buf * (nb * 512));
         float* daw = reinterpret_cast<float*>(smem + sp.da + buf * (nb * 64));
-        float* ciw = reinterpret_cast<float*>(smem + sp.ci + buf * (nb * 64));
+        float* ciw = reinterpret_cast<float*>(smem + sp.ci + buf * (nb * 128));
         if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
         const int m = it->n_tok;
         // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
@@ -607,7 +611,11 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
             const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
             const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
             daw[dst] = p.aa[row * (nb * 2) + r];
-            ciw[dst] = p.ac[row * (nb * 2) + r];
+            // the MMA's accumulator input of this block half: {c0, c1, c0, c1} for the lane's two token columns and both row halves
+            const int cq = ((b * 4 + (g >> 1)) * 2 + s) * 4 + (g & 1);
+            const float cv = p.ac[row * (nb * 2) + r];
+            ciw[cq] = cv;
+            ciw[cq + 2] = cv;
         }
     };
 
@@ -629,7 +637,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
         const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da + buf * (nb * 64));
-        const ulonglong2* ci = reinterpret_cast<const ulonglong2*>(smem + sp.ci + buf * (nb * 64));
+        const int4* ci = reinterpret_cast<const int4*>(smem + sp.ci + buf * (nb * 128));
         const Item* its = reinterpret_cast<const Item*>(smem + sp.item + buf * 64);
         const int m = its->n_tok;
         const int g = lane >> 2, t4 = lane & 3;
