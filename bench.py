@@ -41,7 +41,7 @@ sys.path.insert(0, ROOT)
 N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
-NCU_GU_TRAFFIC_PER_BLOB = 224.17e6 / 367   # DRAM bytes per distinct expert blob of one gate/up launch (ncu, profiles/)
+NCU_GU_TRAFFIC_PER_BLOB = 224.33e6 / 367   # DRAM bytes per distinct expert blob of one gate/up launch (ncu, profiles/)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
 UNIT = "layer-tokens/s"
@@ -317,7 +317,7 @@ def run_frx(args):
     layer_bytes = float(np.mean([(d + 1) * EXPERT_BYTES for d in distinct])) + B * (E * 4 + N_MODEL * 8) + B * K * 8
     roofline = {"bound": "hbm", "kernel": "k_stream<gate_up>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_source": peak_src,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch: 224.17 MB for 367 distinct
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch: 224.33 MB for 367 distinct
                 # expert blobs in the ncu capture summarised in profiles/k_stream_decode_b64.md (a 2-layer
                 # case of the same kernel), scaled to this run by the distinct blobs a launch reads
                 "traffic": int(mean_local * NCU_GU_TRAFFIC_PER_BLOB), "traffic_source": "ncu capture of a 2-layer case, scaled by distinct expert blobs",
