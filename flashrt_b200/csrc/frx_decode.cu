@@ -1306,6 +1306,7 @@ int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_
         return fail(FRX_ERR_SHAPE, "frx_moe_layer_ep_allreduce: T %d (at most %d and the buffers' %d), n %d (buffers' %d)", T, kMaxChunkTokens,
                     comm->max_T, n, comm->n);
     if (int rc = check_moe_shape("frx_moe_layer_ep_allreduce", n, ff, K)) return rc;
+    if (uintptr_t(out) % 16) return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: out must be 16-byte aligned");
     if (T == 0) return FRX_OK;   // every rank skips the call alike
     // blocks of different GPUs wait on one another: all of a launch must be resident at once
     const long long blocks = (long long)((n + 256 * kEpElems - 1) / (256 * kEpElems)) * T;
