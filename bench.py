@@ -253,6 +253,22 @@ def run_frx(args):
             layer_call(l)
 
     step()
+    if comm is not None:
+        # the fused all-reduce reports a peer that did not answer in time through the workspace status;
+        # if any rank saw that, every rank drops to the NCCL form (with a fresh workspace: the status sticks)
+        try:
+            moe.workspace_status(ws)
+            fused_ok = 1
+        except moe.FrxError as exc:
+            fused_ok = 0
+            print(f"rank {rank}: fused all-reduce failed ({exc}); using NCCL", file=sys.stderr)
+        flag = torch.tensor([fused_ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            comm.close()
+            comm = None
+            ws = moe.workspace(moe.moe_layer_workspace_bytes(B, K, N_MODEL, FF), dev)
+            step()
     moe.workspace_status(ws)
     torch.cuda.synchronize()
     distinct = [int(torch.unique(ids[l]).numel()) for l in range(L)]
