@@ -373,15 +373,39 @@ def run_frx(args):
         # Copies, layer calls and all-reduces are stream-ordered; one synchronisation per step.
         xh, lh, gh = x.cpu().pin_memory(), logits.cpu().pin_memory(), gate.cpu().pin_memory()
         oh = torch.empty(L, B, N_MODEL).pin_memory()
-        xd, ld, gd, od = torch.empty_like(x[0]), torch.empty_like(logits[0]), torch.empty_like(gate[0]), torch.empty_like(out[0])
+        # two staging sets and two copy streams, so that a layer's compute overlaps the copy-in of the
+        # next layer and the copy-out of the previous one (what frx_moe_layers_host does on one GPU)
+        NB = 2
+        xd = [torch.empty_like(x[0]) for _ in range(NB)]
+        ld = [torch.empty_like(logits[0]) for _ in range(NB)]
+        gd = [torch.empty_like(gate[0]) for _ in range(NB)]
+        od = [torch.empty_like(out[0]) for _ in range(NB)]
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(NB)]
+        ev_done = [torch.cuda.Event() for _ in range(NB)]
+        ev_out = [torch.cuda.Event() for _ in range(NB)]
 
         def host_step():
+            main = torch.cuda.current_stream()
+            s_in.wait_stream(main)
             for l in range(L):
-                xd.copy_(xh[l], non_blocking=True)
-                ld.copy_(lh[l], non_blocking=True)
-                gd.copy_(gh[l], non_blocking=True)
-                ep_layer(l, xd, ld, gd, od)
-                oh[l].copy_(od, non_blocking=True)
+                b = l % NB
+                with torch.cuda.stream(s_in):
+                    if l >= NB:
+                        s_in.wait_event(ev_done[b])   # the layer that read this staging set has run
+                    xd[b].copy_(xh[l], non_blocking=True)
+                    ld[b].copy_(lh[l], non_blocking=True)
+                    gd[b].copy_(gh[l], non_blocking=True)
+                    ev_in[b].record(s_in)
+                main.wait_event(ev_in[b])
+                if l >= NB:
+                    main.wait_event(ev_out[b])        # its previous output has been copied out
+                ep_layer(l, xd[b], ld[b], gd[b], od[b])
+                ev_done[b].record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[b])
+                    oh[l].copy_(od[b], non_blocking=True)
+                    ev_out[b].record(s_out)
             torch.cuda.synchronize()
 
         for _ in range(max(1, args.warmup // 2)):
