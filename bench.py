@@ -252,6 +252,9 @@ def run_frx(args):
         for l in range(L):
             layer_call(l)
 
+    if world > 1:   # the ranks' set-up times differ; the fused all-reduce waits for a peer for 2 s at most
+        torch.cuda.synchronize()
+        dist.barrier()
     step()
     if comm is not None:
         # the fused all-reduce reports a peer that did not answer in time through the workspace status;
@@ -408,6 +411,7 @@ def run_frx(args):
                     ev_out[b].record(s_out)
             torch.cuda.synchronize()
 
+        barrier()
         for _ in range(max(1, args.warmup // 2)):
             host_step()
         barrier()
