@@ -1,6 +1,6 @@
-"""Expert-parallel layers on two real GPUs (one process per GPU, NCCL): the decode form
+"""Expert-parallel layers on two and four real GPUs (one process per GPU, NCCL): the decode form
 (replicated tokens, all-reduce) and the prefill form (sharded tokens, all-to-all) against the
-single-GPU result. Skipped on machines with fewer than two GPUs."""
+single-GPU result. Skipped on machines with fewer GPUs than ranks."""
 import os
 import sys
 
@@ -67,13 +67,14 @@ def _worker(rank, world, port_no, ret):
     dist.destroy_process_group()
 
 
-def test_two_gpu_expert_parallel_layers():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_layers(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     with ctx.Manager() as m:
         ret = m.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, 29533, ret)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, world, 29531 + world, ret)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
@@ -82,7 +83,7 @@ def test_two_gpu_expert_parallel_layers():
                 p.kill()
                 pytest.fail("a rank did not finish in time")
             assert p.exitcode == 0
-        for r in range(2):
+        for r in range(world):
             err_decode, err_prefill, ids_ok, err_fused, same_bits = ret[r]
             assert ids_ok
             assert err_decode < 1e-5 and err_prefill < 1e-5
