@@ -177,6 +177,8 @@ def run_frx(args):
     B, L = args.batch, args.layers
     if args.nw:
         moe.check(moe.lib.frx_debug_set_consumer_warps(args.nw))
+    if args.narrow is not None:
+        moe.check(moe.lib.frx_debug_set_narrow_items(args.narrow))
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     e_local = e_hi - e_lo
 
@@ -229,8 +231,14 @@ def run_frx(args):
                 print(f"peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
         ok = torch.tensor([1 if comm is not None else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 0 and comm is not None:
-            comm.close()
+        if int(ok.item()) == 0:   # some rank could not map its peers: every rank takes part in the ordered tear-down
+            torch.cuda.synchronize()
+            dist.barrier()
+            if comm is not None:
+                comm.close_mappings()
+            dist.barrier()
+            if comm is not None:
+                comm.destroy()
             comm = None
 
     def ep_layer(l: int, xin, lin, gin, o):
@@ -593,6 +601,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16)")
+    ap.add_argument("--narrow", type=int, default=None, help="tuning: 0 sends every work item through the eight-token form")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"], help="decode = configs[1] (default), prefill = configs[2]")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill tokens")
     ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform"], help="prefill routing skew")

@@ -1,6 +1,7 @@
 // Host-side plumbing of libfrx: error text, device attributes, the HBM expert arena.
 #include "frx_common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -38,6 +39,12 @@ int max_smem_optin() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
     return n;
 }
+
+// ---- the limit of device-side waits
+namespace {
+std::atomic<unsigned long long> g_wait_limit_ns{kWaitLimitNs};
+}
+uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
 
 // ---- per-kernel timing
 bool g_profile_on = false;
@@ -131,7 +138,12 @@ const char* frx_profile_class_name(int cls) {
     return cls >= 0 && cls < kNumKernelClasses ? names[cls] : "";
 }
 
-int frx_version(void) { return 1; }
+int frx_version(void) { return 2; }
+
+int frx_debug_set_wait_limit_ns(unsigned long long ns) {
+    frx::g_wait_limit_ns.store(ns ? ns : frx::kWaitLimitNs, std::memory_order_relaxed);
+    return FRX_OK;
+}
 const char* frx_last_error(void) { return g_err; }
 
 size_t frx_q2_mat_bytes(int rows, int cols) { return size_t(rows) * size_t(cols / kQK) * kBlockBytes; }

@@ -166,16 +166,19 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 
-// Waits for a barrier phase for at most kWaitLimitNs. Returns false when the wait ran out or
+// Waits for a barrier phase for at most limit_ns. Returns false when the wait ran out or
 // `*abort` was already set; it then sets `*abort` so every later wait of the block returns at
 // once, and the caller's block finishes its control flow without trusting the data.
+// The limit is a launch parameter: wait_limit_ns() on the host, 2 s unless
+// frx_debug_set_wait_limit_ns has changed it (tests shorten it to exercise the give-up paths).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+uint64_t wait_limit_ns();
 // SLEEP: back off with nanosleep after a few polls (right for waits on data from global memory,
 // where a waiting warp should leave the issue slots to working warps); without it the wait only
 // repeats try_wait, which itself suspends the thread for a short hardware-defined time (right for
 // the short hand-offs of a warp-specialised pipeline, where a sleep that overshoots delays every step).
 template <bool SLEEP = true>
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
     uint64_t t0 = 0;   // the clock is only read once the wait has lasted a while: reading it is slow
@@ -191,7 +194,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
             const uint64_t now = global_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > limit_ns) {
                 *abort = 1;
                 return false;
             }
@@ -236,6 +239,23 @@ __device__ __forceinline__ void mma_u8s8_c4(uint64_t& lo, uint64_t& hi, uint32_t
         "mov.b64 %1, {d2,d3};\n\t}"
         : "=l"(lo), "=l"(hi)
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w));
+}
+
+// Two MMAs chained into one accumulator: D = A0 * B0 + A1 * B1 + C, results packed as above. Used
+// with B operands that are zero in complementary token columns, so that the columns of D belong to
+// different row groups.
+__device__ __forceinline__ void mma_u8s8_chain2(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3,
+                                                uint32_t f0, uint32_t f1, const int4& c) {
+    asm volatile(
+        "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%14,%15,%16,%17};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%8,%9,%10,%11}, {%12,%13}, {d0,d1,d2,d3};\n\t"
+        "mov.b64 %0, {d0,d1};\n\t"
+        "mov.b64 %1, {d2,d3};\n\t}"
+        : "=l"(lo), "=l"(hi)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c.x), "r"(c.y),
+          "r"(c.z), "r"(c.w));
 }
 
 __device__ __forceinline__ void mma_u8s8_bias(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

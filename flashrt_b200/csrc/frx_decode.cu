@@ -366,6 +366,8 @@ struct StreamParams {
     int cpt;           // chunks per task
     int rpw;           // ring slots per consumer warp
     int nbuf;          // item buffers (2 or 3)
+    unsigned long long wait_ns;   // the longest a wait on a shared-memory barrier may last
+    int narrow;        // items of at most kNarrowTok tokens take units_mma_narrow (results are the same bits either way)
 };
 
 // Shared-memory plan of k_stream. The activation operand of an item (fragments, scales, biases,
@@ -468,6 +470,62 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uin
     }
 }
 
+// The narrow form of units_mma, for items of at most kNarrowTok tokens (most items of a decode
+// batch: with 64 tokens over 512 experts an expert gets 1.75 tokens on average). The MMA's eight
+// token columns are used twice: the B operand of row group 0 carries the item's tokens in columns
+// 0..3 and zeros in columns 4..7, the B operand of row group 1 zeros in columns 0..3 and the tokens
+// in columns 4..7, and the two MMAs accumulate into one D. Lanes t4 = 0, 1 then hold group 0's sums
+// of tokens (0, 1) and (2, 3), lanes t4 = 2, 3 those of group 1, so every lane's float work is on
+// live values and there is half as much of it per row. Products, scaling and the order of the
+// additions per (row, token) are those of units_mma: the results are the same bits.
+// The item buffer must have been built for the narrow form (see build in k_stream): zeros in token
+// columns 4..7 of the B fragments, scale and bias entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1.
+constexpr int kNarrowTok = 4;
+template <int UPC>
+__device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
+                                                 const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
+                                                 const int4* __restrict__ ci, int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
+    const uint8_t* codes = units + lane * 16;
+    const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
+    const uint4* bf0_p = bfrag + b0 * 32 + g * 4 + t4;               // column g: token g, or zeros for g >= 4
+    const uint4* bf1_p = bfrag + b0 * 32 + ((g + 4) & 7) * 4 + t4;   // column g + 4 (mod 8): zeros for g < 4, else token g - 4
+    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
+    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
+    const ulonglong2* da_p = da + b0 * 4 + t4;
+    const int n_units = UPC ? UPC : count;
+#pragma unroll(2)
+    for (int u = 0; u < n_units; ++u) {
+        const uint4 c0 = *reinterpret_cast<const uint4*>(codes + u * kUnitBytes);
+        const uint4 c1 = *reinterpret_cast<const uint4*>(codes + gstride + u * kUnitBytes);
+        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int b = 2 * u + j;
+            const uint4 bfa = bf0_p[b * 32], bfb = bf1_p[b * 32];
+            const int4 cq0 = ci_p[b * 8], cq1 = ci_p[b * 8 + 1];
+            const ulonglong2 a = da_p[b * 4];
+            const uint32_t w0 = j ? c0.y : c0.x, w1 = j ? c0.w : c0.z;   // group 0: rows g, g + 8
+            const uint32_t x0 = j ? c1.y : c1.x, x1 = j ? c1.w : c1.z;   // group 1
+            const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
+            uint64_t lo0, hi0, lo1, hi1;
+            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq0);
+            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq1);
+            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
+            const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
+            const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
+            const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
+            const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+            float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
+            unpack2(sumi_lo, s0, s1);
+            unpack2(sumi_hi, s2, s3);
+            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
+            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+        }
+    }
+}
+
 // UPC: units per units_mma call when known at compile time (gate/up: units per chunk; down: units
 // per group), else 0.
 template <bool GATE_UP, int NW, int UPC>
@@ -498,11 +556,21 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;            // this warp's slots
     volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
 
-    const int n_items = p.status[1];
+    // (down, before its wait: the item list was complete and flushed to the L2 before the kernel in
+    // front of this one began, but the same addresses are rewritten every layer, so the reads
+    // bypass this SM's L1, which may still hold the previous layer's lines)
+    const int n_items = GATE_UP ? p.status[1] : *reinterpret_cast<const volatile int*>(p.status + 1);
     const long long total = (long long)n_items * tasks_per_expert;
     const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
     const int ntasks = int(hi - lo);
-    if (ntasks <= 0) return;   // uniform for the block
+    if (ntasks <= 0) {   // uniform for the block
+        if (!GATE_UP) pdl_wait();   // keeps "this grid has ended" meaning "every kernel before it has ended"
+        return;
+    }
+    auto item_blob = [&](int item) -> const uint8_t* {
+        if (GATE_UP) return p.items[item].blob;
+        return *reinterpret_cast<const uint8_t* const volatile*>(&p.items[item].blob);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
@@ -525,7 +593,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const long long tau = lo + warp;
         is_item = int(tau / tasks_per_expert);
         is_task = int(tau % tasks_per_expert);
-        if (is_i < ntasks) is_blob = p.items[is_item].blob + section;
+        if (is_i < ntasks) is_blob = item_blob(is_item) + section;
     }
     auto issue_next = [&]() {   // lane 0 only
         if (is_i >= ntasks) return;
@@ -548,7 +616,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                     is_task -= tasks_per_expert;
                     ++is_item;
                 }
-                is_blob = p.items[is_item].blob + section;
+                is_blob = item_blob(is_item) + section;
             }
         }
     };
@@ -557,7 +625,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     int cs_slot = 0;
     uint32_t cs_phase = 0;   // the chunk being consumed: its slot and that slot's barrier phase
     auto chunk_wait = [&]() -> const uint8_t* {
-        mbar_wait_bounded(full + cs_slot, cs_phase, abort);
+        mbar_wait_bounded(full + cs_slot, cs_phase, abort, p.wait_ns);
         return ring + size_t(cs_slot) * chunk_bytes;
     };
     auto chunk_done = [&]() {
@@ -581,9 +649,12 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         float* ciw = reinterpret_cast<float*>(smem + sp.ci + buf * (nb * 128));
         if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
         const int m = it->n_tok;
+        const bool narrow = m <= kNarrowTok && p.narrow;   // see units_mma_narrow
         // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
         constexpr int NT = NW * 32;
         const int vpr = nb * 4;   // 16-byte vectors per row
+        if (narrow)   // token columns 4..7 of every block hold zeros
+            for (int idx = ctid; idx < nb * 16; idx += NT) reinterpret_cast<uint4*>(bw)[(idx >> 4) * 32 + 16 + (idx & 15)] = make_uint4(0u, 0u, 0u, 0u);
         for (int base = ctid; base < m * vpr; base += 4 * NT) {
             uint4 v[4];
 #pragma unroll
@@ -610,12 +681,18 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
             const int slot = it->slot[g];
             const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
             const int dst = (b * 4 + (g >> 1)) * 4 + s * 2 + (g & 1);
-            daw[dst] = p.aa[row * (nb * 2) + r];
+            const float av = p.aa[row * (nb * 2) + r];
+            daw[dst] = av;
             // the MMA's accumulator input of this block half: {c0, c1, c0, c1} for the lane's two token columns and both row halves
             const int cq = ((b * 4 + (g >> 1)) * 2 + s) * 4 + (g & 1);
             const float cv = p.ac[row * (nb * 2) + r];
             ciw[cq] = cv;
             ciw[cq + 2] = cv;
+            if (narrow) {   // lanes t4 = 2, 3 work on the same tokens as t4 = 0, 1 (for the second row group)
+                daw[dst + 8] = av;
+                ciw[cq + 16] = cv;
+                ciw[cq + 18] = cv;
+            }
         }
     };
 
@@ -632,7 +709,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     }
     for (int q = 0; q < nseg; ++q) {
         const int item = first_item + q, buf = q % nbuf;
-        mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort);
+        mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort, p.wait_ns);
         const long long seg_lo = max(lo, (long long)item * tasks_per_expert);
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
@@ -641,11 +718,60 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const Item* its = reinterpret_cast<const Item*>(smem + sp.item + buf * 64);
         const int m = its->n_tok;
         const int g = lane >> 2, t4 = lane & 3;
-        const int c0 = 2 * t4, c1 = 2 * t4 + 1;
+        const bool narrow = m <= kNarrowTok && p.narrow;
+        // the lane's two token columns, and in the narrow form the row group (of the pair) it finishes
+        const int c0 = narrow ? 2 * (t4 & 1) : 2 * t4, c1 = c0 + 1, rn = t4 >> 1;
         const int i_lo = int(seg_lo - lo), first = i_lo + (warp - i_lo % NW + NW) % NW;
         for (long long tau = lo + first; tau < seg_hi; tau += NW) {
             const int task = int(tau % tasks_per_expert);
-            if (GATE_UP) {
+            if (GATE_UP && narrow) {
+                uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
+                const int upc = units / cpt;
+                for (int c = 0; c < cpt; ++c) {
+                    const uint8_t* cp = chunk_wait();
+                    units_mma_narrow<UPC>(cp, half_bytes, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
+                    chunk_done();
+                }
+                float sum[4];
+                unpack2(acc_lo, sum[0], sum[1]);
+                unpack2(acc_hi, sum[2], sum[3]);
+                const int row = (task * 2 + rn) * 8 + g;
+                if (c0 < m) p.gu[size_t(its->slot[c0]) * p.ff + row] = make_float2(sum[0], sum[2]);
+                if (c1 < m) p.gu[size_t(its->slot[c1]) * p.ff + row] = make_float2(sum[1], sum[3]);
+            } else if (!GATE_UP && narrow) {
+                const int gpc = kDownGroups / cpt;   // groups per chunk
+                float* o0 = nullptr;
+                float* o1 = nullptr;
+                if (c0 < m) {
+                    const int sl = its->slot[c0];
+                    o0 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
+                }
+                if (c1 < m) {
+                    const int sl = its->slot[c1];
+                    o1 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
+                }
+                for (int c = 0; c < cpt; ++c) {
+                    const uint8_t* cp = chunk_wait();
+#pragma unroll 1
+                    for (int gd = 0; gd < gpc; gd += 2) {   // gpc is even
+                        uint64_t acc_lo = 0ull, acc_hi = 0ull;
+                        units_mma_narrow<UPC>(cp + size_t(gd) * group_bytes, group_bytes, units, 0, bfrag, da, ci, lane, acc_lo, acc_hi);
+                        float sum[4];
+                        unpack2(acc_lo, sum[0], sum[1]);
+                        unpack2(acc_hi, sum[2], sum[3]);
+                        const int row = ((task * cpt + c) * gpc + gd + rn) * 16 + g;
+                        if (o0) {
+                            o0[row] = sum[0];
+                            o0[row + 8] = sum[2];
+                        }
+                        if (o1) {
+                            o1[row] = sum[1];
+                            o1[row + 8] = sum[3];
+                        }
+                    }
+                    chunk_done();
+                }
+            } else if (GATE_UP) {
                 uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};   // {0.0f, 0.0f}
                 const int upc = units / cpt;
                 for (int c = 0; c < cpt; ++c) {
@@ -704,7 +830,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         if (lane == 0) mbar_arrive(done + buf);
         if (q + ahead < nseg) {
             const int nxt = (q + ahead) % nbuf;   // the buffer of item q - 1
-            if (q >= 1) mbar_wait_bounded(done + nxt, uint32_t((q - 1) / nbuf) & 1u, abort);
+            if (q >= 1) mbar_wait_bounded(done + nxt, uint32_t((q - 1) / nbuf) & 1u, abort, p.wait_ns);
             build(q + ahead);
             __syncwarp();
             if (lane == 0) mbar_arrive(ready + nxt);
@@ -743,9 +869,10 @@ __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out
 
 // ---- combine fused with the expert-parallel all-reduce over peer memory
 // Layout of a rank's communication buffer: two slots of partial sums [max_T][n] fp32, then
-// (256-byte aligned) flag words [FRX_EP_MAX_RANKS] (word q is written by rank q: the number of the
-// last call whose partial sums rank q has published), then three local words: the number of calls
-// completed and two ticket counters.
+// (256-byte aligned) flag words [FRX_EP_MAX_RANKS][kEpMaxBlocks] (word [q][b] is written by block b
+// of rank q: the number of the last call whose partial sums that block has published), then local
+// words: the number of calls completed, a ticket counter, and four cycle stamps of the last call.
+constexpr int kEpMaxBlocks = FRX_EP_MAX_BLOCKS;
 struct EpLayout {
     size_t slot_floats, flags, state, total;
 };
@@ -753,7 +880,7 @@ __host__ __device__ inline EpLayout ep_layout(int max_T, int n) {
     EpLayout L{};
     L.slot_floats = size_t(max_T) * n;
     L.flags = align_up(2 * L.slot_floats * 4);
-    L.state = L.flags + 256;
+    L.state = L.flags + size_t(FRX_EP_MAX_RANKS) * kEpMaxBlocks * 4;
     L.total = L.state + 256;
     return L;
 }
@@ -761,10 +888,12 @@ struct EpParams {
     int world, rank;
     float* partial[FRX_EP_MAX_RANKS];      // slot 0 of every rank's buffer
     uint32_t* flags[FRX_EP_MAX_RANKS];     // every rank's flag words
-    uint32_t* state;                       // local: [0] calls completed so far, [1], [2] tickets
+    uint32_t* state;                       // local: [0] calls completed so far, [1] ticket, [8..15] cycle stamps
     size_t slot_floats;
+    unsigned long long wait_ns;
 };
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -772,12 +901,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 
 // out[t] = sum over ranks (in rank order) of that rank's partial sum; this rank's partial sum is
-// what k_combine_ordered computes. A thread owns up to kEpElems output elements of one token, and
-// their partial sums never leave its registers, so no barrier inside the GPU is needed: a block
-// publishes its part, the last block to do so raises this rank's flag at the peers, and every
-// block then waits for the peers' flags (not for its own rank's). Blocks of different GPUs wait
-// on one another, so all blocks of a launch must be resident at once: the host keeps the grid
-// below the number of SMs times four.
+// what k_combine_ordered computes. A thread owns kEpElems output elements of one token, and their
+// partial sums never leave its registers, so no barrier inside the GPU is needed. Block b stores
+// its part into this rank's buffer and raises its own flag word at every peer (one thread per
+// peer: system-scope fence, then the flag store), waits for block b of every peer (the only blocks
+// whose data it reads; one thread per peer polls), then issues the loads of all peers' parts
+// before the first addition, so the reads cost one NVLink round trip, and adds them in rank
+// order: every rank gets the same bits. Blocks of different GPUs wait on one another, so all blocks
+// of a launch must be resident at once: the host keeps the grid below the number of SMs times four.
+// A slot is reused every other call, which is safe: a block sees a peer's flag of call c only
+// after that peer's kernel of call c - 1 has ended (kernels of one stream run in order), i.e. after
+// the peer has read everything of call c - 1.
 constexpr int kEpElems = 4;   // consecutive elements per thread: one 16-byte access
 __device__ __forceinline__ float4 ld_peer4(const float* p) {   // never from a cache of this GPU: the buffer is rewritten every other call
     float4 v;
@@ -793,8 +927,13 @@ __global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ o
     pdl_trigger();
     const int t = blockIdx.y;
     const int i = (blockIdx.x * 256 + threadIdx.x) * kEpElems;   // n is a multiple of 128: a thread's four elements are all inside or all outside
+    const uint32_t bid = blockIdx.y * gridDim.x + blockIdx.x;
+    const bool stamp = bid == 0 && threadIdx.x == 0;
+    long long* stamps = reinterpret_cast<long long*>(ep.state + 8);
     const uint32_t call = ep.state[0] + 1;   // the same in every block: state[0] only changes after all blocks have read it
     const size_t slot = size_t(call & 1u) * ep.slot_floats;
+    if (threadIdx.x == 0) s_fail = 0;
+    if (stamp) stamps[0] = clock64();
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (i < n) {
         for (int k = 0; k < K; ++k) {
@@ -818,58 +957,64 @@ __global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ o
         }
         *reinterpret_cast<float4*>(ep.partial[ep.rank] + slot + size_t(t) * n + i) = acc;
     }
-    // publish: the block's stores are ordered before thread 0 by the block barrier; thread 0 makes
-    // them visible to the system and takes a ticket; the last block raises this rank's flag at every peer
+    // publish and wait, one thread per peer: the block's stores are ordered before these threads by
+    // the block barrier; each makes them visible to the system, raises this block's flag at its
+    // peer, and waits for the same block of that peer (flags only grow; the signed distance makes
+    // wrap-around harmless)
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int fail_flag = 0;
-        const uint32_t blocks = gridDim.x * gridDim.y;
-        __threadfence_system();
-        if (atomicAdd(&ep.state[1], 1u) == blocks - 1) {
-            ep.state[1] = 0;
-            __threadfence_system();
-            for (int q = 0; q < ep.world; ++q)
-                if (q != ep.rank) st_release_sys(ep.flags[q] + ep.rank, call);
-        }
-        // wait for every peer's flag of this call (flags only grow; the signed distance makes wrap-around harmless)
-        const uint64_t t0 = global_ns();
-        for (int q = 0; q < ep.world && !fail_flag; ++q) {
-            if (q == ep.rank) continue;
-            uint32_t polls = 0;
-            while (int32_t(ld_acquire_sys(ep.flags[ep.rank] + q) - call) < 0) {
-                if ((++polls & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) {
-                    fail_flag = 1;
+    if (stamp) stamps[1] = clock64();
+    if (int(threadIdx.x) < ep.world && int(threadIdx.x) != ep.rank) {
+        const int q = threadIdx.x;
+        fence_acq_rel_sys();
+        st_relaxed_sys(ep.flags[q] + size_t(ep.rank) * kEpMaxBlocks + bid, call);
+        const uint32_t* theirs = ep.flags[ep.rank] + size_t(q) * kEpMaxBlocks + bid;
+        uint64_t t0 = 0;
+        uint32_t polls = 0;
+        while (int32_t(ld_acquire_sys(theirs) - call) < 0) {
+            if ((++polls & 63u) == 0) {
+                const uint64_t now = global_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > ep.wait_ns) {
+                    s_fail = 1;
                     break;
                 }
             }
         }
-        s_fail = fail_flag;
     }
     __syncthreads();
+    if (stamp) stamps[2] = clock64();
     if (s_fail) {
         if (threadIdx.x == 0) status[0] = kDevWaitTimeout;
     } else if (i < n) {
+        float4 v[FRX_EP_MAX_RANKS];
+#pragma unroll
+        for (int q = 0; q < FRX_EP_MAX_RANKS; ++q)   // every peer's part is requested before any is used
+            if (q < ep.world && q != ep.rank) v[q] = ld_peer4(ep.partial[q] + slot + size_t(t) * n + i);
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int q = 0; q < ep.world; ++q) {
-            const float4 v = q == ep.rank ? acc : ld_peer4(ep.partial[q] + slot + size_t(t) * n + i);
+#pragma unroll
+        for (int q = 0; q < FRX_EP_MAX_RANKS; ++q) {
+            if (q >= ep.world) break;
+            const float4 a = q == ep.rank ? acc : v[q];
             if (q == 0) {
-                sum = v;
+                sum = a;
             } else {
-                sum.x = __fadd_rn(sum.x, v.x);
-                sum.y = __fadd_rn(sum.y, v.y);
-                sum.z = __fadd_rn(sum.z, v.z);
-                sum.w = __fadd_rn(sum.w, v.w);
+                sum.x = __fadd_rn(sum.x, a.x);
+                sum.y = __fadd_rn(sum.y, a.y);
+                sum.z = __fadd_rn(sum.z, a.z);
+                sum.w = __fadd_rn(sum.w, a.w);
             }
         }
         *reinterpret_cast<float4*>(out + size_t(t) * n + i) = sum;
     }
-    // the call is complete on this rank once every block has passed its wait: a second ticket
-    // counts them and the last one advances the call number
+    if (stamp) stamps[3] = clock64();
+    // the call is complete on this rank once every block has passed its wait: a ticket counts
+    // them and the last one advances the call number
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t blocks = gridDim.x * gridDim.y;
-        if (atomicAdd(&ep.state[2], 1u) == blocks - 1) {
-            ep.state[2] = 0;
+        if (atomicAdd(&ep.state[1], 1u) == blocks - 1) {
+            ep.state[1] = 0;
             __threadfence();
             ep.state[0] = call;
         }
@@ -968,6 +1113,7 @@ __global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds
 // ---------------------------------------------------------------------------------------------
 
 int g_nw = 16;   // consumer warps of k_stream (8, 12 or 16)
+int g_narrow = 1; // items of at most kNarrowTok tokens take the narrow form of the inner product
 
 struct StreamCfg {
     int nw_gu = 8, nw_dn = 8;     // warps per block
@@ -1074,6 +1220,8 @@ void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaSt
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
+    p.narrow = g_narrow;
+    p.wait_ns = wait_limit_ns();
     p.cpt = cfg.cpt_gu;
     p.rpw = cfg.rpw_gu;
     p.nbuf = cfg.nbuf_gu;
@@ -1248,6 +1396,11 @@ int frx_moe_layer_ep(const void* experts, size_t stride, int E, int e_lo, int e_
     return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream);
 }
 
+size_t frx_ep_flags_offset(int max_T, int n) {
+    if (max_T < 1 || n < 1) return 0;
+    return ep_layout(max_T, n).flags;
+}
+
 size_t frx_ep_buffer_bytes(int max_T, int n) {
     if (max_T < 1 || n < 1) return 0;
     return ep_layout(max_T, n).total;
@@ -1310,7 +1463,8 @@ int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_
     if (T == 0) return FRX_OK;   // every rank skips the call alike
     // blocks of different GPUs wait on one another: all of a launch must be resident at once
     const long long blocks = (long long)((n + 256 * kEpElems - 1) / (256 * kEpElems)) * T;
-    if (blocks > 4LL * sm_count()) return fail(FRX_ERR_SHAPE, "frx_moe_layer_ep_allreduce: %lld blocks would not be resident together", blocks);
+    if (blocks > 4LL * sm_count() || blocks > kEpMaxBlocks)
+        return fail(FRX_ERR_SHAPE, "frx_moe_layer_ep_allreduce: %lld blocks would not be resident together", blocks);
     const EpLayout L = ep_layout(comm->max_T, comm->n);
     EpParams ep{};
     ep.world = comm->world;
@@ -1322,12 +1476,20 @@ int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_
     }
     ep.state = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(comm->buffer[comm->rank]) + L.state);
     ep.slot_floats = L.slot_floats;
+    ep.wait_ns = wait_limit_ns();
     const size_t d = frx_moe_decode_workspace_bytes(T, K, n, ff), r = align_up(size_t(T) * K * 4);
     if (ws_bytes < d + 2 * r) return fail(FRX_ERR_WORKSPACE, "frx_moe_layer_ep_allreduce: workspace %zu < %zu", ws_bytes, d + 2 * r);
     auto* base = static_cast<uint8_t*>(ws);
     int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
     float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
     return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream, &ep);
+}
+
+int frx_ep_debug_stamps(const void* own_buffer, int max_T, int n, long long* cycles4) {
+    if (!own_buffer || !cycles4 || max_T < 1 || n < 1) return fail(FRX_ERR_ARG, "frx_ep_debug_stamps: bad argument");
+    const EpLayout L = ep_layout(max_T, n);
+    FRX_CUDA(cudaMemcpy(cycles4, static_cast<const uint8_t*>(own_buffer) + L.state + 32, 4 * sizeof(long long), cudaMemcpyDeviceToHost));
+    return FRX_OK;
 }
 
 size_t frx_moe_layer_host_workspace_bytes(int T, int K, int n, int ff, int E) {
@@ -1463,9 +1625,13 @@ int frx_workspace_status(const void* ws, frx_stream_t stream) {
     FRX_CUDA(cudaMemcpyAsync(st, ws, sizeof st, cudaMemcpyDeviceToHost, stream));
     FRX_CUDA(cudaStreamSynchronize(stream));
     if (st[3] != kCookie || st[0] == kDevOk) return FRX_OK;
+    // reported once: the error words are cleared so that later calls on this workspace start clean
+    FRX_CUDA(cudaMemsetAsync(const_cast<void*>(ws), 0, 4, stream));
+    FRX_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(const_cast<void*>(ws)) + 8, 0, 4, stream));
+    FRX_CUDA(cudaStreamSynchronize(stream));
     switch (st[0]) {
         case kDevBadExpertId: return fail(FRX_ERR_DEVICE, "expert id out of range at slot %d", st[2]);
-        case kDevWaitTimeout: return fail(FRX_ERR_DEVICE, "a kernel's wait on a shared-memory barrier ran out");
+        case kDevWaitTimeout: return fail(FRX_ERR_DEVICE, "a kernel's bounded wait (on a shared-memory barrier or on a peer's flag) ran out");
         case kDevTooManyItems: return fail(FRX_ERR_DEVICE, "more work items than the workspace holds");
         default: return fail(FRX_ERR_DEVICE, "device error %d", st[0]);
     }
@@ -1481,10 +1647,14 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
     return FRX_OK;
 }
 
-// Tuning knob for experiments (not part of the public header): consumer warps per block.
+// Tuning knobs for measurements (process-wide, not thread-safe: set them before any compute call).
 int frx_debug_set_consumer_warps(int nw) {
     if (nw != 8 && nw != 12 && nw != 16) return FRX_ERR_ARG;
     g_nw = nw;
+    return FRX_OK;
+}
+int frx_debug_set_narrow_items(int on) {
+    g_narrow = on ? 1 : 0;
     return FRX_OK;
 }
 

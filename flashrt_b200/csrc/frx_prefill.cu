@@ -277,6 +277,7 @@ struct UmmaParams {
     float* yd;                // down: [slots][n]
     int* status;
     size_t pmax;
+    unsigned long long wait_ns;   // the longest a wait on a shared-memory barrier may last
     int n, ff;
 };
 
@@ -374,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
 
     // "free" barriers are waited on with the parity of the phase before the one about to be used,
     // which a fresh barrier reports as complete
-    auto wait_full = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, use & 1u, abort); };
-    auto wait_free = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, (use & 1u) ^ 1u, abort); };
+    auto wait_full = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, use & 1u, abort, p.wait_ns); };
+    auto wait_free = [&](int bar, uint32_t use) { return mbar_wait_bounded<false>(bars + bar, (use & 1u) ^ 1u, abort, p.wait_ns); };
 
     if (warp == 0) {
         // ---------------- producer
@@ -593,6 +594,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (*abort) {
+        // A wait ran out: bulk copies and MMAs may still be in flight. Give them time to land
+        // before tensor memory and the block's shared memory are released.
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) {
+        }
+        __syncthreads();
+    }
     if (warp == 1) tmem_free(tmem, 512);
     if (threadIdx.x == 0 && *abort) p.status[0] = kDevWaitTimeout;
 }
@@ -678,6 +687,7 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     p.yd = yd;
     p.status = status;
     p.pmax = L.pmax;
+    p.wait_ns = wait_limit_ns();
     p.n = n;
     p.ff = ff;
     const int sms = sm_count();

@@ -60,3 +60,12 @@ extern "C" int frx_moe_decode_static(const void* experts, size_t stride, int E, 
     return frx_moe_decode(experts, stride, E, shared, n, ff, x, ids, wts, gate_logit, T, K, out, nullptr, scratch, kStaticScratchBytes,
                           stream);
 }
+
+// The status of the built-in scratch: FRX_OK, or FRX_ERR_DEVICE if a kernel of an earlier
+// frx_moe_decode_static call on this device reported an error (a bad expert id, a wait that ran
+// out); reading the error clears it. Synchronises the stream; allocates nothing.
+extern "C" int frx_moe_decode_static_status(frx_stream_t stream) {
+    void* scratch = nullptr;
+    if (int rc = scratch_address(&scratch)) return rc;
+    return frx_workspace_status(scratch, stream);
+}

@@ -62,6 +62,7 @@ class EpComm:
     constructs it at the same time. The handles travel through torch.distributed (set-up only)."""
 
     def __init__(self, max_T: int, n: int, group=None):
+        self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if self.world > 8:
@@ -87,12 +88,35 @@ class EpComm:
         dist.barrier(group=group)   # every rank has mapped every buffer before anyone uses them
 
     def close(self) -> None:
+        """Collective tear-down: every rank of the group calls it at the same point. A rank's buffer
+        is freed only after every rank has drained its device (a peer's last kernel may still be
+        reading this rank's partial sums over NVLink when this rank's own last kernel has ended)
+        and every peer has closed its mapping."""
+        if not self._own:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.close_mappings()
+        dist.barrier(group=self.group)
+        self.destroy()
+
+    def close_mappings(self) -> None:
+        """Step 1 of the tear-down (after every rank has drained its device): unmap the peers' buffers."""
         for m in self._mapped:
             lib.frx_ipc_close(m)
         self._mapped = []
+
+    def destroy(self) -> None:
+        """Step 2 (after every rank has unmapped): free this rank's buffer."""
         if self._own:
             lib.frx_ep_buffer_destroy(self._own)
             self._own = C.c_void_p()
+
+    def stamps(self) -> list[int]:
+        """SM cycle stamps of this rank's last fused call (frx_ep_debug_stamps)."""
+        out = (C.c_longlong * 4)()
+        check(lib.frx_ep_debug_stamps(self._own, self.max_T, self.n, out))
+        return list(out)
 
 
 def moe_layer_ep_fused(comm: EpComm, experts_local: int, stride: int, E: int, e_lo: int, e_hi: int, shared: int | None, n: int, ff: int,

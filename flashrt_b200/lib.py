@@ -70,11 +70,17 @@ SIGNATURES = {
     "frx_router_logits": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "frx_moe_layer_ep": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_ep_buffer_bytes": (_sz, [_i, _i]),
+    "frx_ep_flags_offset": (_sz, [_i, _i]),
     "frx_ep_buffer_create": (_i, [_vp, _i, _i]),
     "frx_ep_buffer_destroy": (_i, [_vp]),
     "frx_ipc_export": (_i, [_vp, _vp]),
     "frx_ipc_open": (_i, [_vp, _vp]),
     "frx_ipc_close": (_i, [_vp]),
+    "frx_ep_debug_stamps": (_i, [_vp, _i, _i, _vp]),
+    "frx_debug_set_consumer_warps": (_i, [_i]),
+    "frx_debug_set_narrow_items": (_i, [_i]),
+    "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),
+    "frx_moe_decode_static_status": (_i, [_vp]),
     "frx_moe_layer_ep_allreduce": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "frx_moe_layer_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),

@@ -57,6 +57,18 @@ int frx_profile_begin(void);
 int frx_profile_end(float* ms, int* launches, int n_classes);
 const char* frx_profile_class_name(int cls);
 
+/* Tuning knobs for measurements and tests; no counterpart in the reference. Process-wide and not
+ * thread-safe: set them before any compute call, not while calls are in flight.
+ * frx_debug_set_consumer_warps: warps per block of the streaming expert kernel (8, 12 or 16; default 16).
+ * frx_debug_set_narrow_items: 1 (default) lets work items of at most four tokens take the narrow
+ * form of the inner product (two row groups share one MMA accumulator, half the float work per row);
+ * 0 sends every item through the eight-token form. Results are the same bits either way.
+ * frx_debug_set_wait_limit_ns: the longest a kernel waits on a barrier, a flag or a peer before it
+ * gives up and reports FRX_ERR_DEVICE through the workspace status (default 2 s; 0 restores it). */
+int frx_debug_set_consumer_warps(int nw);
+int frx_debug_set_narrow_items(int on);
+int frx_debug_set_wait_limit_ns(unsigned long long ns);
+
 /* ---- Q2_0 storage (quant/q2_0/q2_0.hpp:27-56, quant/q2_0/q2_0.cpp:43-71) ---- */
 
 /* q2_0::mat_bytes, q2_0::expert_bytes: rows * (cols / 64) * 18; gate + up + down. */
@@ -163,11 +175,12 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
  *     current); make that first call before any stream capture begins;
  *   - all calls on a device share the one array: calls whose kernels can overlap on the GPU (two
  *     streams, two host threads) race on it, so keep them on one stream or order them;
- *   - a bad expert id is flagged in the scratch, which this entry gives no way to read: check ids
- *     with frx_moe_decode + frx_workspace_status while debugging. */
+ *   - a kernel error (a bad expert id, a bounded wait that ran out) is flagged in the scratch;
+ *     frx_moe_decode_static_status reads and clears it (it synchronises the stream, allocates nothing). */
 int frx_moe_decode_static(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
                           const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out,
                           frx_stream_t stream);
+int frx_moe_decode_static_status(frx_stream_t stream);
 
 /* Byte offset, inside a frx_moe_decode workspace, of one of its buffers (for tests and debugging).
  * "xq" int8 [T][n], "xa" float [T][n/32], "xc" float [T][n/32]: the Q8 form of x as the expert
@@ -226,13 +239,14 @@ int frx_moe_layer_ep(const void* experts_local, size_t stride, int E, int e_lo, 
  *
  * Every rank owns one communication buffer (frx_ep_buffer_create; device memory that other
  * processes of the node map through CUDA IPC: frx_ipc_export / frx_ipc_open). It holds two slots of
- * partial sums [max_T][n] fp32, one flag word per peer and two local counters. frx_ep_comm lists
+ * partial sums [max_T][n] fp32, one flag word per peer and block, and a few local counters. frx_ep_comm lists
  * every rank's buffer as mapped on this device (entry `rank` is the local one).
  *
  * frx_moe_layer_ep_allreduce = frx_moe_layer_ep, but its last kernel, after forming this rank's
  * weighted partial sums, stores them into the rank's own buffer, tells every peer (one flag word
- * each, release at system scope), waits until every peer has told it (bounded: after 2 s the
- * workspace status reports a time-out and the kernel finishes), and adds the peers' partial sums
+ * per block, release at system scope), waits until every peer has told it (bounded: after 2 s, or
+ * the limit set with frx_debug_set_wait_limit_ns, the workspace status reports a time-out and the
+ * kernel finishes without hanging), and adds the peers' partial sums
  * to its own, in rank order on every rank, so all ranks get the same bits. `out` then holds the
  * complete layer output on every rank. No NCCL call is involved, so a step can be captured in a
  * CUDA graph. All ranks must make the same sequence of calls with the same comm; T <= 64 and
@@ -243,13 +257,26 @@ typedef struct frx_ep_comm {
     int max_T, n;
     void* buffer[FRX_EP_MAX_RANKS]; /* every rank's communication buffer, as mapped on this device */
 } frx_ep_comm;
+#define FRX_EP_MAX_BLOCKS 1024
 size_t frx_ep_buffer_bytes(int max_T, int n);
+/* Byte offset of the flag words inside a buffer: uint32 [FRX_EP_MAX_RANKS][FRX_EP_MAX_BLOCKS], word
+ * [q][b] = number of the last call whose partial sums block b of rank q has published here. The two
+ * slots of partial sums (slot = call number & 1, calls counted from 1) start at offset 0 and
+ * max_T * n * 4. For tests and debugging. */
+size_t frx_ep_flags_offset(int max_T, int n);
 int frx_ep_buffer_create(void** buffer, int max_T, int n);   /* allocated and zeroed; once, at set-up */
 int frx_ep_buffer_destroy(void* buffer);
 #define FRX_IPC_HANDLE_BYTES 64
 int frx_ipc_export(const void* buffer, void* handle);        /* handle: FRX_IPC_HANDLE_BYTES bytes to send to the peers */
 int frx_ipc_open(const void* handle, void** mapped);         /* a peer's buffer on this device */
 int frx_ipc_close(void* mapped);
+/* Tear-down order: a buffer may be destroyed only after every rank has finished its last call that
+ * uses it (device synchronised) and every peer has closed its mapping of it; a peer's last kernel
+ * may otherwise still be reading it over NVLink. */
+/* Measurement aid: SM cycle stamps (clock64 of block 0) of the last frx_moe_layer_ep_allreduce call
+ * on this rank: [0] kernel start, [1] partial sums stored, [2] every peer's flag seen, [3] peers'
+ * parts read and summed. own_buffer is this rank's buffer; the call copies synchronously. */
+int frx_ep_debug_stamps(const void* own_buffer, int max_T, int n, long long* cycles4);
 int frx_moe_layer_ep_allreduce(const void* experts_local, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff,
                                const float* x, const float* logits, const float* gate_logit, int T, int K, float* out,
                                int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
@@ -279,8 +306,10 @@ int frx_moe_layers_host(const void* const* experts, size_t stride, int E, const 
                         const float* const* x_host, const float* const* logits_host, const float* const* gate_logit_host,
                         int L, int T, int K, float* const* out_host, void* ws, size_t ws_bytes, frx_stream_t stream);
 
-/* After the stream has drained: FRX_OK, or FRX_ERR_DEVICE if a kernel of a call that used this
- * workspace reported an error (then frx_last_error() says which). */
+/* Waits for the stream, then: FRX_OK, or FRX_ERR_DEVICE if a kernel of a call that used this
+ * workspace reported an error (then frx_last_error() says which: an expert id out of range, more
+ * work items than the workspace holds, or a bounded wait that ran out). An error is reported once:
+ * the call clears it, so later calls on the same workspace start clean. */
 int frx_workspace_status(const void* ws, frx_stream_t stream);
 
 /* ---- qwen4exp::moe_hits (arch/qwen4exp/moe_fast.hpp:134-142) ----

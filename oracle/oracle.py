@@ -20,9 +20,21 @@ _PORT = os.path.join(_HERE, "liboracle.so")
 _REF = os.path.join(_HERE, "_ref", "libfrx_ref.so")
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def find_reference() -> str | None:
+    """The reference source tree: $FRX_REF_ROOT, else a directory named "reference" beside the
+    repository. None when there is none (then only a prebuilt _ref library can be used)."""
+    cands = [os.environ.get("FRX_REF_ROOT"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "quant", "q2_0", "q2_0.cpp")):
+            return c
+    return None
+
+
+def build(ref_root: str | None = None) -> None:
     """Compiles both checkers (the reference one only if the reference tree is present)."""
-    subprocess.run(["make", "-C", _HERE, f"REF={ref_root}"], check=True, capture_output=True)
+    ref_root = ref_root or find_reference()
+    cmd = ["make", "-C", _HERE] + ([f"REF={ref_root}"] if ref_root else [])
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 def _p(a: np.ndarray | None):

@@ -43,8 +43,9 @@ def test_sizes(L):
     # the many-layer host form adds four staging slots, whatever the number of layers
     assert (L.lib.frx_moe_layers_host_workspace_bytes(64, 10, 2048, 512, 512) - L.lib.frx_moe_layer_workspace_bytes(64, 10, 2048, 512)
             >= 4 * 64 * (2 * 2048 + 512 + 1) * 4)
-    # expert-parallel buffer: two slots of partial sums, flags and counters
-    assert 2 * 64 * 2048 * 4 < L.lib.frx_ep_buffer_bytes(64, 2048) <= 2 * 64 * 2048 * 4 + 1024
+    # expert-parallel buffer: two slots of partial sums, one flag word per (rank, block), counters
+    assert L.lib.frx_ep_flags_offset(64, 2048) == 2 * 64 * 2048 * 4
+    assert L.lib.frx_ep_buffer_bytes(64, 2048) == 2 * 64 * 2048 * 4 + 8 * 1024 * 4 + 256
     assert L.lib.frx_ep_buffer_bytes(0, 2048) == 0
 
 

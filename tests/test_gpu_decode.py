@@ -258,3 +258,56 @@ def test_layer_replayed_from_a_cuda_graph_with_new_inputs(port):
         want = moe.moe_layer(ex.base, ex.stride, E, ex.shared_ptr, n, ff, x, lg, gate, K)
         assert torch.equal(got, want), seed
     moe.workspace_status(ws)
+
+
+def test_narrow_and_wide_item_forms_give_the_same_bits(port):
+    # items of at most four tokens take another arrangement of the same products (two row groups in
+    # one MMA accumulator); with the knob off every item takes the eight-token form
+    from flashrt_b200.lib import check, lib
+    n, ff, E, K, T = 1024, 256, 96, 6, 40        # 2.5 tokens per expert: narrow and wide items mixed
+    ex = Experts(port, n, ff, E, direct=True)
+    x = synth.activations(T, n)
+    ids, wts, _ = port.route(synth.router_logits(T, E), K)
+    gate = np.linspace(-1, 1, T).astype(np.float32)
+    try:
+        check(lib.frx_debug_set_narrow_items(0))
+        out_w, ys_w = run_decode(ex, x, ids, wts, gate)
+    finally:
+        check(lib.frx_debug_set_narrow_items(1))
+    out_n, ys_n = run_decode(ex, x, ids, wts, gate)
+    assert np.array_equal(ys_n, ys_w) and np.array_equal(out_n, out_w)
+    ref_out, ref_ys, _ = port.moe_layer(ex.routed_planar(), ex.blob_bytes, ex.shared_planar, n, ff, x, ids, wts, gate, n_threads=8,
+                                        want_slots=True)
+    assert max(rel_max(ys_n[s], ref_ys[s]) for s in range(T * K)) < 1e-5
+    assert rel_max(out_n, ref_out) < 1e-5
+
+
+@pytest.mark.parametrize("T", [3, 64])
+def test_full_layer_shape_on_a_slot_sample(port, T):
+    # BASELINE configs[1] (and the 3-token verify window of configs[3]) at the full shape: 512 experts
+    # + shared, hidden 2048, intermediate 512, top-10. The oracle computes a sample of slots (every
+    # expert FFN is independent) and the combined output of two tokens.
+    n, ff, E, K = 2048, 512, 512, 10
+    ex = Experts(port, n, ff, E, direct=True)
+    x, lg = synth.activations(T, n), synth.router_logits(T, E)
+    gate = np.random.default_rng(5).standard_normal(T).astype(np.float32)
+    ids, wts, _ = port.route(lg, K)
+    ids_o = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    wts_o = torch.empty(T, K, device="cuda")
+    ws = moe.workspace(moe.moe_layer_workspace_bytes(T, K, n, ff))
+    out = moe.moe_layer(ex.base, ex.stride, E, ex.shared_ptr, n, ff, cuda(x), cuda(lg), cuda(gate), K, ids_out=ids_o, wts_out=wts_o, ws=ws)
+    moe.workspace_status(ws)
+    assert np.array_equal(ids_o.cpu().numpy(), ids)                    # router ids bit-exact
+    _, ys = run_decode(ex, x, ids, wts, gate)
+    xq, xd = port.quantize_q8(x)
+    rng = np.random.default_rng(6)
+    for s in rng.choice(T * K, size=min(24, T * K), replace=False):
+        t, k = divmod(int(s), K)
+        want = port.expert_ffn(ex.planar[ids[t, k]], n, ff, xq[t], xd[t])
+        assert rel_max(ys[s], want) < 1e-5, (s, rel_max(ys[s], want))
+    got = out.cpu().numpy()
+    for t in (0, T - 1):
+        by_id = np.argsort(ids[t])          # the layer sums a token's experts in ascending id
+        want = port.moe_layer(np.ascontiguousarray(ex.planar[ids[t][by_id]]), ex.blob_bytes, ex.shared_planar, n, ff, x[t:t + 1],
+                              np.arange(K, dtype=np.int32)[None], wts[t:t + 1][:, by_id], gate[t:t + 1])
+        assert rel_max(got[t:t + 1], want) < 1e-5

@@ -9,6 +9,7 @@ import pytest
 import torch
 
 from flashrt_b200 import moe, synth
+from flashrt_b200.lib import check, lib
 from helpers import Experts, cuda
 
 pytestmark = pytest.mark.gpu
@@ -17,6 +18,12 @@ pytestmark = pytest.mark.gpu
 def test_static_scratch_matches_workspace_entry_twice(port):
     n, ff, E = 512, 256, 16
     ex = Experts(port, n, ff, E)
+    # The first call on a device looks up the scratch array (the CUDA runtime may load that part of
+    # the library image, array included, only then): made here, before device memory is watched.
+    z = torch.zeros(1, n, device="cuda")
+    moe.moe_decode_static(ex.base, ex.stride, E, None, n, ff, z, torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                          torch.ones(1, 1, device="cuda"), None, torch.empty_like(z))
+    torch.cuda.synchronize()
     for call, (T, K, seed) in enumerate([(7, 4, 1), (3, 6, 2)]):
         x = synth.activations(T, n, seed=seed)
         ids, wts, _ = port.route(synth.router_logits(T, E, seed=seed + 10), K)
@@ -26,9 +33,13 @@ def test_static_scratch_matches_workspace_entry_twice(port):
         out = torch.full((T, n), float("nan"), device="cuda")
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()        # cudaMemGetInfo: also sees a cudaMalloc made inside the library
         moe.moe_decode_static(ex.base, ex.stride, E, ex.shared_ptr, n, ff, dx, di, dw, dg, out)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
         assert torch.cuda.memory_allocated() == before, "the call must not allocate through torch"
+        assert free_after >= free_before, f"the call took {free_before - free_after} bytes of device memory"
+        check(lib.frx_moe_decode_static_status(moe._stream()))
         got, ref = out.cpu().numpy(), want.cpu().numpy()
         assert np.isfinite(got).all()
         assert np.array_equal(got, ref), f"call {call}: static-scratch output differs from the workspace entry"
