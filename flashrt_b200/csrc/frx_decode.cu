@@ -8,6 +8,8 @@
 #include "frx_common.cuh"
 #include "frx_route.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cstring>
 #include <mutex>
 
@@ -68,8 +70,10 @@ Layout make_layout(int T, int K, int n, int ff) {
 // ---------------------------------------------------------------------------------------------
 // Q8 quantization of 32 values held one per lane: returns the code; lane 0 gets scale and sum.
 // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16.
-__device__ __forceinline__ int q8_block(float v, float& d_out, int& sum_out) {
-    float am = fabsf(v);
+// `partner`: with activation blocks of 64 (moe_q2::run's block64 option, kernels/cuda/moe_q2.cu:58-77)
+// the value at the same place of the other half of the 64-block, which shares the scale; else 0.
+__device__ __forceinline__ int q8_block(float v, float& d_out, int& sum_out, float partner = 0.0f) {
+    float am = fmaxf(fabsf(v), fabsf(partner));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
     const float d = __fdiv_rn(am, 127.0f);
@@ -111,10 +115,10 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  ends as kMagicBits + sum((q - 1) * code), which read as a float is kMagic plus
 //                  that sum, exactly.
 __device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int lane, int8_t* __restrict__ q, float* __restrict__ a,
-                                                 float* __restrict__ c) {
+                                                 float* __restrict__ c, float partner = 0.0f) {
     float d;
     int sum;
-    const int code = q8_block(v, d, sum);
+    const int code = q8_block(v, d, sum, partner);
     const int bpr = k / kQ8;
     const size_t row = blk / bpr;
     const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
@@ -125,8 +129,8 @@ __device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int
     }
 }
 __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
-                                                 float* __restrict__ a, float* __restrict__ c) {
-    quant_frag_value(x[blk * kQ8 + lane], k, blk, lane, q, a, c);
+                                                 float* __restrict__ a, float* __restrict__ c, bool block64 = false) {
+    quant_frag_value(x[blk * kQ8 + lane], k, blk, lane, q, a, c, block64 ? x[(blk ^ 1) * kQ8 + lane] : 0.0f);
 }
 // The hidden rows: gu holds (gate x, up x) pairs; h = silu(gate x) * up x is formed here, where
 // there are thousands of independent threads to hide the latency of the exponential, stored, and
@@ -136,7 +140,8 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
 // another rank computes them, and nothing here reads their hidden values.
 __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
                                                       int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c,
-                                                      const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi) {
+                                                      const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi,
+                                                      int block64) {
     pdl_wait();
     pdl_trigger();
     const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
@@ -164,6 +169,7 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
     float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if (block64) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));   // sixteen lanes hold one 64-block
     const float d = __fdiv_rn(am, 127.0f);
     const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
     int code[4], sum = 0;
@@ -187,11 +193,11 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
     }
 }
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
-                                                    float* __restrict__ a, float* __restrict__ c) {
+                                                    float* __restrict__ a, float* __restrict__ c, int block64) {
     pdl_wait();
     pdl_trigger();
     const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (blk < n_blocks) quant_frag_block(x, k, blk, threadIdx.x & 31, q, a, c);
+    if (blk < n_blocks) quant_frag_block(x, k, blk, threadIdx.x & 31, q, a, c, block64 != 0);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -367,6 +373,8 @@ struct StreamParams {
     int rpw;           // ring slots per consumer warp
     int nbuf;          // item buffers (2 or 3)
     unsigned long long wait_ns;   // the longest a wait on a shared-memory barrier may last
+    int block64;       // hidden rows quantized with one scale per 64 values (moe_q2::run's block64 option)
+    int y_bf16;        // down: y holds bf16 rows (moe_q2::run's yd_bf16 option)
     int narrow;        // items of at most kNarrowTok tokens take units_mma_narrow (results are the same bits either way)
 };
 
@@ -700,6 +708,21 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     // its tasks of item q builds its share of item q + nbuf - 1 (into the buffer item q - 1 used, once
     // every warp has left that item) and goes on to item q + 1 as soon as all shares of it are in.
     // With three buffers a warp can run one item ahead of the slowest warp.
+    // down: the output row of a slot (routed slots in y, float or bf16 rows; shared-expert slots in ysh,
+    // always float), and the store of rows `row` and `row + 8` of it
+    auto out_row = [&](int sl) -> float* {
+        if (sl >= p.TK) return p.ysh + size_t(sl - p.TK) * p.n;
+        return p.y_bf16 ? reinterpret_cast<float*>(reinterpret_cast<__nv_bfloat16*>(p.y) + size_t(sl) * p.n) : p.y + size_t(sl) * p.n;
+    };
+    auto put2 = [&](float* o, int row, float v0, float v8) {
+        if (p.y_bf16) {
+            reinterpret_cast<__nv_bfloat16*>(o)[row] = __float2bfloat16_rn(v0);
+            reinterpret_cast<__nv_bfloat16*>(o)[row + 8] = __float2bfloat16_rn(v8);
+        } else {
+            o[row] = v0;
+            o[row + 8] = v8;
+        }
+    };
     const int ahead = nbuf - 1;
     if (!GATE_UP) pdl_wait();   // the first weight chunks are already in flight
     for (int q = 0; q < ahead && q < nseg; ++q) {
@@ -742,14 +765,8 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                 const int gpc = kDownGroups / cpt;   // groups per chunk
                 float* o0 = nullptr;
                 float* o1 = nullptr;
-                if (c0 < m) {
-                    const int sl = its->slot[c0];
-                    o0 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                }
-                if (c1 < m) {
-                    const int sl = its->slot[c1];
-                    o1 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                }
+                if (c0 < m) o0 = out_row(its->slot[c0]);
+                if (c1 < m) o1 = out_row(its->slot[c1]);
                 for (int c = 0; c < cpt; ++c) {
                     const uint8_t* cp = chunk_wait();
 #pragma unroll 1
@@ -760,14 +777,8 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                         unpack2(acc_lo, sum[0], sum[1]);
                         unpack2(acc_hi, sum[2], sum[3]);
                         const int row = ((task * cpt + c) * gpc + gd + rn) * 16 + g;
-                        if (o0) {
-                            o0[row] = sum[0];
-                            o0[row + 8] = sum[2];
-                        }
-                        if (o1) {
-                            o1[row] = sum[1];
-                            o1[row + 8] = sum[3];
-                        }
+                        if (o0) put2(o0, row, sum[0], sum[2]);
+                        if (o1) put2(o1, row, sum[1], sum[3]);
                     }
                     chunk_done();
                 }
@@ -798,28 +809,16 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                         units_mma<UPC>(cp + size_t(gd) * group_bytes, group_bytes, units, 0, bfrag, da, ci, lane, acc_lo, acc_hi);
                         float* o0 = nullptr;
                         float* o1 = nullptr;
-                        if (c0 < m) {
-                            const int sl = its->slot[c0];
-                            o0 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                        }
-                        if (c1 < m) {
-                            const int sl = its->slot[c1];
-                            o1 = sl < p.TK ? p.y + size_t(sl) * p.n : p.ysh + size_t(sl - p.TK) * p.n;
-                        }
+                        if (c0 < m) o0 = out_row(its->slot[c0]);
+                        if (c1 < m) o1 = out_row(its->slot[c1]);
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
                             float sum[4];
                             unpack2(acc_lo[r], sum[0], sum[1]);
                             unpack2(acc_hi[r], sum[2], sum[3]);
                             const int row = ((task * cpt + c) * gpc + gd + r) * 16 + g;
-                            if (o0) {
-                                o0[row] = sum[0];
-                                o0[row + 8] = sum[2];
-                            }
-                            if (o1) {
-                                o1[row] = sum[1];
-                                o1[row + 8] = sum[3];
-                            }
+                            if (o0) put2(o0, row, sum[0], sum[2]);
+                            if (o1) put2(o1, row, sum[1], sum[3]);
                         }
                     }
                     chunk_done();
@@ -1214,9 +1213,9 @@ struct ActBufs {
 // The expert FFN over the items of p: quantize x, gate/up + SwiGLU into p.h, quantize the
 // hidden rows, down. x has x_rows rows of p.n values; p.h has h_rows rows of p.ff values.
 // (The grouping kernel that fills p.items may be enqueued before or after the first quantizer.)
-void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaStream_t stream) {
+void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaStream_t stream, int block64 = 0) {
     const size_t nblk = size_t(x_rows) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c, block64));
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
@@ -1230,7 +1229,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -1775,6 +1774,11 @@ size_t frx_moe_prefill_stream_workspace_bytes(int T, int K, int n, int ff, int E
 
 int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
                            float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_prefill_stream_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+}
+
+int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                              void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
     if (!experts || !x || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
     if (int rc = check_moe_shape("frx_moe_prefill", n, ff, K)) return rc;
     if (T < 0 || E < 1 || E > 4096 || size_t(T) * K > (size_t(1) << 30)) return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, E %d", T, E);
@@ -1795,7 +1799,7 @@ int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int
     int32_t* perm = reinterpret_cast<int32_t*>(base + L.perm);
     Item* items = reinterpret_cast<Item*>(base + L.items);
     const int S = T * K;
-    launch_quant_x(x, T, n, act_x(base, L), stream);
+    launch_quant_x(x, T, n, act_x(base, L), stream, block64);
     FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
     FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items));
     FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
@@ -1806,7 +1810,9 @@ int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int
     p.status = status;
     p.gu = reinterpret_cast<float2*>(base + L.gu);
     p.h = reinterpret_cast<float*>(base + L.h);
-    p.y = yd;
+    p.y = static_cast<float*>(yd);
+    p.y_bf16 = yd_bf16 ? 1 : 0;
+    p.block64 = block64 ? 1 : 0;
     p.ysh = nullptr;
     p.n = n;
     p.ff = ff;

@@ -22,6 +22,8 @@
 // All waits are bounded; a wait that runs out sets the workspace status word and the block drains.
 #include "frx_umma.cuh"
 
+#include <cuda_bf16.h>
+
 #include <mutex>
 
 namespace frx {
@@ -196,8 +198,8 @@ __global__ void __launch_bounds__(256) k_pfu_gather(const int* __restrict__ boun
 }
 
 // Natural-order Q8 of x rows (q2_0::quantize_q8): warp per 32-block.
-__device__ __forceinline__ int q8_block_pf(float v, float& d_out) {
-    float am = fabsf(v);
+__device__ __forceinline__ int q8_block_pf(float v, float& d_out, float partner) {
+    float am = fmaxf(fabsf(v), fabsf(partner));   // partner: the other half of a 64-value scale block (block64), else 0
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
     const float d = __fdiv_rn(am, 127.0f);
@@ -207,12 +209,12 @@ __device__ __forceinline__ int q8_block_pf(float v, float& d_out) {
 }
 
 __global__ void __launch_bounds__(256) k_pfu_quant_x(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ q,
-                                                     float* __restrict__ d) {
+                                                     float* __restrict__ d, int block64) {
     const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= n_blocks) return;
     float dd;
-    const int c = q8_block_pf(x[blk * kQ8 + lane], dd);
+    const int c = q8_block_pf(x[blk * kQ8 + lane], dd, block64 ? x[(blk ^ 1) * kQ8 + lane] : 0.0f);
     q[blk * kQ8 + lane] = int8_t(c);
     if (lane == 0) d[blk] = dd;
 }
@@ -223,7 +225,8 @@ __global__ void __launch_bounds__(256) k_pfu_quant_x(const float* __restrict__ x
 // formed here (eight independent exponentials per thread hide their latency), the block maximum
 // comes from two shuffles, and each thread stores its chunk whole.
 __global__ void __launch_bounds__(256) k_pfu_quant_h(const float2* __restrict__ hf, int ff, size_t pmax, const int* __restrict__ meta,
-                                                     const int32_t* __restrict__ pslot, uint8_t* __restrict__ hg, float* __restrict__ ha) {
+                                                     const int32_t* __restrict__ pslot, uint8_t* __restrict__ hg, float* __restrict__ ha,
+                                                     int block64) {
     const int cpr = ff / 8;   // chunks per row
     const size_t chunk = size_t(blockIdx.x) * 256 + threadIdx.x;
     const size_t p = chunk / cpr;
@@ -248,6 +251,7 @@ __global__ void __launch_bounds__(256) k_pfu_quant_h(const float2* __restrict__ 
     }
     am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
     am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    if (block64) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));   // eight lanes hold one 64-value scale block
     // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16
     const float d = __fdiv_rn(am, 127.0f);
     const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
@@ -279,6 +283,7 @@ struct UmmaParams {
     size_t pmax;
     unsigned long long wait_ns;   // the longest a wait on a shared-memory barrier may last
     int n, ff;
+    int y_bf16;               // down: yd holds bf16 rows
 };
 
 struct PfSmem {
@@ -585,8 +590,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_pf_umma(const UmmaParams p) {
                         const float v0 = acc[2 * i], v1 = acc[2 * i + 1];
                         const int pos = p0 + 32 * cq + 2 * i;
                         const int sl0 = p.pslot[pos], sl1 = p.pslot[pos + 1];
-                        if (sl0 >= 0) p.yd[size_t(sl0) * p.n + orow] = v0;
-                        if (sl1 >= 0) p.yd[size_t(sl1) * p.n + orow] = v1;
+                        if (p.y_bf16) {
+                            __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(p.yd);
+                            if (sl0 >= 0) yb[size_t(sl0) * p.n + orow] = __float2bfloat16_rn(v0);
+                            if (sl1 >= 0) yb[size_t(sl1) * p.n + orow] = __float2bfloat16_rn(v1);
+                        } else {
+                            if (sl0 >= 0) p.yd[size_t(sl0) * p.n + orow] = v0;
+                            if (sl1 >= 0) p.yd[size_t(sl1) * p.n + orow] = v1;
+                        }
                     }
                 }
             }
@@ -629,8 +640,8 @@ extern "C" {
 
 // the streaming form lives in frx_decode.cu
 size_t frx_moe_prefill_stream_workspace_bytes(int T, int K, int n, int ff, int E);
-int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
-                           float* yd, void* ws, size_t ws_bytes, frx_stream_t stream);
+int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                              void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
 
 size_t frx_moe_prefill_umma_workspace_bytes(int T, int K, int n, int ff, int E) {
     if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK || E < 1) return 0;
@@ -639,6 +650,11 @@ size_t frx_moe_prefill_umma_workspace_bytes(int T, int K, int n, int ff, int E) 
 
 int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
                          float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_prefill_umma_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+}
+
+int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                            void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
     if (!experts || !x || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
     if (n < kUnitK || ff < kUnitK || n % kUnitK || ff % kUnitK || n > 8192 || ff > 8192)
         return fail(FRX_ERR_SHAPE, "frx_moe_prefill: n %d and ff %d must be multiples of %d, at most 8192", n, ff, kUnitK);
@@ -668,7 +684,7 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     float* xd = reinterpret_cast<float*>(base + L.xd);
     const int S = T * K;
     const size_t nblk = size_t(T) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_pfu_quant_x<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, xq, xd));
+    FRX_LAUNCH(kKQuant, stream, k_pfu_quant_x<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, xq, xd, block64));
     FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
     FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, 1 << 30));
     FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
@@ -684,7 +700,8 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     p.tb_n = tb_n;
     p.pslot = pslot;
     p.hf = reinterpret_cast<float2*>(base + L.hf);
-    p.yd = yd;
+    p.yd = static_cast<float*>(yd);
+    p.y_bf16 = yd_bf16 ? 1 : 0;
     p.status = status;
     p.pmax = L.pmax;
     p.wait_ns = wait_limit_ns();
@@ -696,7 +713,7 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     FRX_LAUNCH(kKGateUp, stream, k_pf_umma<true><<<sms, kThreads, pf_smem().total, stream>>>(p));
     const size_t hchunks = L.pmax * size_t(ff / 8);
     FRX_LAUNCH(kKQuant, stream, k_pfu_quant_h<<<unsigned((hchunks + 255) / 256), 256, 0, stream>>>((const float2*)p.hf, ff, L.pmax, meta, pslot, base + L.hg,
-                                                                                    reinterpret_cast<float*>(base + L.ha)));
+                                                                                    reinterpret_cast<float*>(base + L.ha), block64));
     p.act = base + L.hg;
     p.act_scale = reinterpret_cast<const float*>(base + L.ha);
     FRX_LAUNCH(kKDown, stream, k_pf_umma<false><<<sms, kThreads, pf_smem().total, stream>>>(p));
@@ -718,9 +735,14 @@ size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E) {
 
 int frx_moe_prefill(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
                     float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_prefill_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+}
+
+int frx_moe_prefill_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                       void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
     if (T > 0 && K > 0 && E > 0 && size_t(T) * K >= size_t(kUmmaMinTokensPerExpert) * E)
-        return frx_moe_prefill_umma(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream);
-    return frx_moe_prefill_stream(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream);
+        return frx_moe_prefill_umma_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, block64, yd_bf16);
+    return frx_moe_prefill_stream_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, block64, yd_bf16);
 }
 
 }  // extern "C"

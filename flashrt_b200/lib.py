@@ -28,7 +28,7 @@ if not os.path.exists(LIB_PATH):
 
 lib = C.CDLL(LIB_PATH)
 
-_vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+_vp, _sz, _i, _i64 = C.c_void_p, C.c_size_t, C.c_int, C.c_int64
 
 # name -> (restype, argtypes); every symbol include/frx.h declares
 SIGNATURES = {
@@ -94,6 +94,22 @@ SIGNATURES = {
     "frx_moe_prefill": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "frx_moe_prefill_umma": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "frx_moe_prefill_stream": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_moe_prefill_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
+    "frx_moe_prefill_umma_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
+    "frx_moe_prefill_stream_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
+    "frx_gemv_q8_1_bytes": (_sz, [_i64, _i]),
+    "frx_gemv_row_bytes": (_i64, [C.c_uint32, _i64]),
+    "frx_gemv_quantize_q8_1": (_i, [_vp, _i64, _i, _vp, _vp]),
+    "frx_gemv_swiglu_q8_1": (_i, [_vp, _vp, _i64, _i, _vp, _vp]),
+    "frx_gemv_matvec_q": (_i, [C.c_uint32, _vp, _vp, _vp, _i64, _i64, _i, _vp]),
+    "frx_gemv_matvec": (_i, [C.c_uint32, _vp, _vp, _vp, _i64, _i64, _i, _vp, _vp]),
+    "frx_gemv_moe_q2_0": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i, _vp]),
+    "frx_gemv_moe_q": (_i, [C.c_uint32, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _i64, _i, _vp]),
+    "frx_gemm_workspace_bytes": (_sz, [_i64, _i64]),
+    "frx_gemm_moe_prepare": (_i, [_vp, C.c_uint32, _i, _vp, _i, _vp, _i64, _i, _i64, _vp, _sz, _vp]),
+    "frx_gemm_moe_run": (_i, [_vp, _vp, _i64, _vp, _i64, _vp]),
+    "frx_gemm_moe": (_i, [C.c_uint32, _vp, _i64, _i, _vp, _i, _vp, _i64, _i, _vp, _i64, _i64, _vp, _sz, _vp]),
+    "frx_convert_q8_0_to_q2_0": (_i, [_vp, _vp, _sz, _vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -428,3 +428,115 @@ class moe_q2:
         fn = {"auto": lib.frx_moe_prefill, "umma": lib.frx_moe_prefill_umma, "stream": lib.frx_moe_prefill_stream}[form]
         check(fn(C.c_void_p(experts), stride, E, n, ff, _ptr(x), _ptr(ids), T, K, _ptr(yd), wp, wb, _stream(stream)))
         return yd
+
+    @staticmethod
+    def run_ex(experts: int, stride: int, E: int, n: int, ff: int, x: torch.Tensor, ids: torch.Tensor, block64: bool = False,
+               yd_bf16: bool = False, ws: torch.Tensor | None = None, stream=None, form: str = "auto") -> torch.Tensor:
+        """moe_q2::run with its two options: activation scale blocks of 64, and bf16 output rows."""
+        _dev(x, ids)
+        T, K = ids.shape
+        yd = torch.empty(T * K, n, dtype=torch.bfloat16 if yd_bf16 else torch.float32, device=x.device)
+        if ws is None:
+            ws = workspace(moe_q2.workspace_bytes(T, K, n, ff, E), x.device)
+        wp, wb = _ws_ptr(ws)
+        fn = {"auto": lib.frx_moe_prefill_ex, "umma": lib.frx_moe_prefill_umma_ex, "stream": lib.frx_moe_prefill_stream_ex}[form]
+        check(fn(C.c_void_p(experts), stride, E, n, ff, _ptr(x), _ptr(ids), T, K, _ptr(yd), wp, wb, _stream(stream), int(block64), int(yd_bf16)))
+        return yd
+
+
+class gemv:
+    """The reference's gemv:: functions for ggml-layout Q2_0 weights (kernels/cuda/ggml_gemv.h:26-65)."""
+
+    @staticmethod
+    def q8_1_bytes(ncols: int, n_tok: int) -> int:
+        return int(lib.frx_gemv_q8_1_bytes(ncols, n_tok))
+
+    @staticmethod
+    def row_bytes(ggml_type: int, ncols: int) -> int:
+        return int(lib.frx_gemv_row_bytes(ggml_type, ncols))
+
+    @staticmethod
+    def quantize_q8_1(x: torch.Tensor, stream=None) -> torch.Tensor:
+        _dev(x)
+        n_tok, ncols = x.shape
+        xq = torch.empty(gemv.q8_1_bytes(ncols, n_tok), dtype=torch.uint8, device=x.device)
+        check(lib.frx_gemv_quantize_q8_1(_ptr(x), ncols, n_tok, _ptr(xq), _stream(stream)))
+        return xq
+
+    @staticmethod
+    def swiglu_q8_1(g: torch.Tensor, u: torch.Tensor, stream=None) -> torch.Tensor:
+        _dev(g, u)
+        n_tok, ncols = g.shape
+        xq = torch.empty(gemv.q8_1_bytes(ncols, n_tok), dtype=torch.uint8, device=g.device)
+        check(lib.frx_gemv_swiglu_q8_1(_ptr(g), _ptr(u), ncols, n_tok, _ptr(xq), _stream(stream)))
+        return xq
+
+    @staticmethod
+    def moe_q(ggml_type: int, w: torch.Tensor, gate: torch.Tensor | None, xq: torch.Tensor, ids: torch.Tensor, ncols: int, nrows: int,
+              expert_stride_bytes: int, act_per_expert: bool, stream=None) -> torch.Tensor:
+        """dst [n_tok][k][nrows] = W_{ids[t][j]} x (silu(G x) * (W x) with gate)."""
+        _dev(w, gate, xq, ids)
+        n_tok, k = ids.shape
+        dst = torch.empty(n_tok, k, nrows, dtype=torch.float32, device=w.device)
+        check(lib.frx_gemv_moe_q(ggml_type, _ptr(w), _ptr(gate), _ptr(xq), _ptr(ids), _ptr(dst), n_tok, k, ncols, nrows, expert_stride_bytes,
+                                 int(act_per_expert), _stream(stream)))
+        return dst
+
+    @staticmethod
+    def moe_q2_0(w: torch.Tensor, gate: torch.Tensor | None, xq: torch.Tensor, ids: torch.Tensor, ncols: int, nrows: int,
+                 slot_stride_bytes: int, per_channel_act: bool, stream=None) -> torch.Tensor:
+        _dev(w, gate, xq, ids)
+        n_ids = ids.numel()
+        dst = torch.empty(n_ids, nrows, dtype=torch.float32, device=w.device)
+        check(lib.frx_gemv_moe_q2_0(_ptr(w), _ptr(gate), _ptr(xq), _ptr(ids), _ptr(dst), n_ids, ncols, nrows, slot_stride_bytes,
+                                    int(per_channel_act), _stream(stream)))
+        return dst
+
+    @staticmethod
+    def matvec(ggml_type: int, W: torch.Tensor, x: torch.Tensor, nrows: int, stream=None) -> torch.Tensor:
+        _dev(W, x)
+        n_tok, ncols = x.shape
+        y = torch.empty(n_tok, nrows, dtype=torch.float32, device=x.device)
+        scratch = torch.empty(gemv.q8_1_bytes(ncols, n_tok), dtype=torch.uint8, device=x.device)
+        check(lib.frx_gemv_matvec(ggml_type, _ptr(W), _ptr(x), _ptr(y), ncols, nrows, n_tok, _ptr(scratch), _stream(stream)))
+        return y
+
+
+class _GemmPlan(C.Structure):
+    _fields_ = [("type", C.c_uint32), ("n_experts", C.c_int), ("K", C.c_int), ("T", C.c_int64), ("ncols", C.c_int64), ("rows", C.c_int64),
+                ("x_per_slot", C.c_int), ("ws", C.c_void_p)]
+
+
+class gemm:
+    """The reference's grouped expert products for ggml-layout Q2_0 weights (kernels/cuda/ggml_gemm.h:50-68)."""
+
+    @staticmethod
+    def workspace_bytes(ncols: int, rows: int) -> int:
+        return int(lib.frx_gemm_workspace_bytes(ncols, rows))
+
+    @staticmethod
+    def moe_prepare(ggml_type: int, n_experts: int, x: torch.Tensor, x_per_slot: bool, ids: torch.Tensor, ncols: int, ws: torch.Tensor,
+                    stream=None) -> _GemmPlan:
+        _dev(x, ids)
+        T, K = ids.shape
+        plan = _GemmPlan()
+        wp, wb = _ws_ptr(ws)
+        check(lib.frx_gemm_moe_prepare(C.byref(plan), ggml_type, n_experts, _ptr(x), int(x_per_slot), _ptr(ids), T, K, ncols, wp, wb,
+                                       _stream(stream)))
+        return plan
+
+    @staticmethod
+    def moe_run(plan: _GemmPlan, W: torch.Tensor, expert_stride_bytes: int, nrows: int, stream=None) -> torch.Tensor:
+        _dev(W)
+        y = torch.empty(plan.T, plan.K, nrows, dtype=torch.float32, device=W.device)
+        check(lib.frx_gemm_moe_run(C.byref(plan), _ptr(W), expert_stride_bytes, _ptr(y), nrows, _stream(stream)))
+        return y
+
+
+def convert_q8_0_to_q2_0(src: torch.Tensor, stream=None) -> torch.Tensor:
+    """qwen4exp::convert_q8_0_to_q2_0 on the device: uint8 [n * 68] Q8_0 block pairs -> uint8 [n * 18] Q2_0 blocks."""
+    _dev(src)
+    n = src.numel() // 68
+    dst = torch.empty(n * 18, dtype=torch.uint8, device=src.device)
+    check(lib.frx_convert_q8_0_to_q2_0(_ptr(src), _ptr(dst), n, _stream(stream)))
+    return dst

@@ -345,6 +345,77 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
                          int K, float* yd, void* ws, size_t ws_bytes, frx_stream_t stream);
 int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
                            int K, float* yd, void* ws, size_t ws_bytes, frx_stream_t stream);
+/* The same with moe_q2::run's two options (kernels/cuda/moe_q2.h:26-30). block64: activations (x and
+ * the hidden rows) are quantized with one scale per 64 values instead of per 32 (the scale still
+ * passes through fp16 and codes round half away from zero; the reference's CPU path has no such
+ * mode, so this one is checked against it within the reference test's own bound,
+ * tests/test_moe_q2.cpp:139-141). yd_bf16: yd receives bf16 rows [T*K][n] (round to nearest) as
+ * arch/qwen4exp/moe_stream.cu:164-177 wants them. */
+int frx_moe_prefill_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
+                       int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
+int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
+                            int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
+int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
+                              int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
+
+/* ---- ggml-layout entry points: gemv:: (kernels/cuda/ggml_gemv.h:26-65) and gemm::
+ * (kernels/cuda/ggml_gemm.h:27-68) for ggml type 42 (Q2_0), as the draft head's MoE calls them
+ * (arch/qwen4exp/mtp.cu:631-670). Weights are in ggml's own layout, not the tiled one: rows of
+ * 18-byte blocks {fp16 d; 16 code bytes, element j in byte j / 4 at bit 2 * (j % 4)}, row-major
+ * [nrows][ncols], expert e at w + e * expert_stride_bytes. Activations are ggml Q8_1 rows: blocks
+ * {fp16 d; fp16 sum; 32 int8}, every row padded with zeros to a multiple of 512 values. The
+ * arithmetic is ggml's vec_dot_q2_0_q8_1 (third_party/ggml/src/ggml-cuda/vecdotq.cuh:728-771): per
+ * 32 values an exact integer sum, scaled d_w * d_a * sum in float, chunks added in float. ncols a
+ * multiple of 128; pointers and strides multiples of 4 bytes (16 for the bulk-copy fast path); no
+ * zeroed tail is needed after the weights (the reference's kernels want gemv::kWeightTailPad).
+ * Any other ggml type returns FRX_ERR_SHAPE. bool arguments of the reference are ints here. */
+size_t frx_gemv_q8_1_bytes(int64_t ncols, int n_tok);              /* gemv::q8_1_bytes */
+int64_t frx_gemv_row_bytes(uint32_t ggml_type, int64_t ncols);     /* gemv::row_bytes; 0 for other types */
+/* gemv::quantize_q8_1: x [n_tok][ncols] -> Q8_1 rows (d = amax / 127, q = roundf(x / d)) */
+int frx_gemv_quantize_q8_1(const float* x, int64_t ncols, int n_tok, void* xq, frx_stream_t stream);
+/* gemv::swiglu_q8_1: the same of silu(g) * u */
+int frx_gemv_swiglu_q8_1(const float* g, const float* u, int64_t ncols, int n_tok, void* xq, frx_stream_t stream);
+/* gemv::matvec_q / gemv::matvec: y [n_tok][nrows] = W x, n_tok <= 8; matvec quantizes x into scratch first */
+int frx_gemv_matvec_q(uint32_t ggml_type, const void* W, const void* xq, float* y, int64_t ncols, int64_t nrows, int n_tok,
+                      frx_stream_t stream);
+int frx_gemv_matvec(uint32_t ggml_type, const void* W, const float* x, float* y, int64_t ncols, int64_t nrows, int n_tok, void* scratch,
+                    frx_stream_t stream);
+/* gemv::moe_q2_0: dst [n_ids][nrows], channel i uses expert ids[i] and activation row 0 (or row i with
+ * per_channel_act); with gate, silu(G x) * (W x). */
+int frx_gemv_moe_q2_0(const void* w, const void* gate, const void* xq, const int32_t* ids, float* dst, int n_ids, int64_t ncols,
+                      int64_t nrows, int64_t slot_stride_bytes, int per_channel_act, frx_stream_t stream);
+/* gemv::moe_q: dst [n_tok][k][nrows] = W_{ids[t][j]} x, x = Q8_1 row t (or row t * k + j with
+ * act_per_expert); with gate, silu(G x) * (W x). n_tok <= 8. */
+int frx_gemv_moe_q(uint32_t ggml_type, const void* w, const void* gate, const void* xq, const int32_t* ids, float* dst, int n_tok, int k,
+                   int64_t ncols, int64_t nrows, int64_t expert_stride_bytes, int act_per_expert, frx_stream_t stream);
+
+/* gemm::moe_prepare / moe_run / moe / workspace_bytes: grouped expert products for many tokens.
+ * prepare quantizes the activations (row t of x [T][ncols], or row t * K + k of x [T][K][ncols] with
+ * x_per_slot) and groups the T * K slots by expert in `ws`, entirely on the device: unlike the
+ * reference's it does not wait for the stream. run multiplies one expert tensor: y [T][K][nrows].
+ * The plan points into ws, which must stay untouched between prepare and the runs that use it.
+ * n_experts <= 4096. ws: 256-byte aligned, frx_gemm_workspace_bytes(ncols, T * K). */
+typedef struct frx_gemm_moe_plan {
+    uint32_t type;
+    int n_experts, K;
+    int64_t T, ncols, rows;
+    int x_per_slot;
+    void* ws;
+} frx_gemm_moe_plan;
+size_t frx_gemm_workspace_bytes(int64_t ncols, int64_t rows);
+int frx_gemm_moe_prepare(frx_gemm_moe_plan* plan, uint32_t ggml_type, int n_experts, const float* x, int x_per_slot, const int32_t* ids,
+                         int64_t T, int K, int64_t ncols, void* ws, size_t ws_bytes, frx_stream_t stream);
+int frx_gemm_moe_run(const frx_gemm_moe_plan* plan, const void* W, int64_t expert_stride_bytes, float* y, int64_t nrows,
+                     frx_stream_t stream);
+int frx_gemm_moe(uint32_t ggml_type, const void* W, int64_t expert_stride_bytes, int n_experts, const float* x, int x_per_slot,
+                 const int32_t* ids, int64_t T, int K, float* y, int64_t ncols, int64_t nrows, void* ws, size_t ws_bytes,
+                 frx_stream_t stream);
+
+/* convert_q8_0_to_q2_0 (arch/qwen4exp/mtp.hpp:40, mtp.cu:129-215) on the device: nblocks64 pairs of
+ * Q8_0 blocks {fp16 d; 32 int8} (68 bytes) -> ggml Q2_0 blocks (18 bytes): for each 64 values the
+ * scale among 24 candidates (amax / 2.5 .. amax, through fp16) with the least squared error, codes
+ * clamp(round(x / d), -1, 2) + 1. Bit-identical to the reference's host function. Device pointers. */
+int frx_convert_q8_0_to_q2_0(const void* src_q8_0, void* dst_q2_0, size_t nblocks64, frx_stream_t stream);
 
 #ifdef __cplusplus
 }

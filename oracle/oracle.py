@@ -60,6 +60,12 @@ class Port:
         lib.orc_expert_bytes.restype = C.c_size_t
         lib.orc_dot_ggml.restype = C.c_float
         lib.orc_dot_ggml.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        lib.orc_dot_q2_0_q8_1.restype = C.c_double
+        lib.orc_dot_q2_0_q8_1.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        lib.orc_quantize_q8_1.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        lib.orc_moe_q2_0.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                     C.c_size_t, C.c_int]
+        lib.orc_convert_q8_0_to_q2_0.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
         lib.orc_moe_layer.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                       C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_int]
@@ -122,6 +128,34 @@ class Port:
         hd = np.empty(ff // 32, np.float32)
         self.lib.orc_expert_ffn(_p(blob), n, ff, _p(xq), _p(xd), _p(out), _p(h), _p(hq), _p(hd))
         return (out, h, hq, hd) if want_hidden else out
+
+    # ---- ggml-layout pieces
+    @staticmethod
+    def q8_1_row_bytes(ncols: int) -> int:
+        return (ncols + 511) // 512 * 512 // 32 * 36
+
+    def quantize_q8_1(self, x: np.ndarray) -> np.ndarray:
+        """x [n_tok][ncols] -> uint8 [n_tok][q8_1_row_bytes]."""
+        x = np.ascontiguousarray(x, np.float32)
+        n_tok, ncols = x.shape
+        out = np.zeros((n_tok, self.q8_1_row_bytes(ncols)), np.uint8)
+        self.lib.orc_quantize_q8_1(_p(x), ncols, n_tok, _p(out))
+        return out
+
+    def moe_q2_0(self, w: np.ndarray, gate: np.ndarray | None, xq: np.ndarray, ids: np.ndarray, ncols: int, nrows: int,
+                 expert_stride: int, act_per_expert: bool) -> np.ndarray:
+        """gemv::moe_q for Q2_0: dst [n_tok][k][nrows]."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        n_tok, k = ids.shape
+        dst = np.empty((n_tok, k, nrows), np.float32)
+        self.lib.orc_moe_q2_0(_p(w), _p(gate), _p(xq), _p(ids), _p(dst), n_tok, k, ncols, nrows, expert_stride, int(act_per_expert))
+        return dst
+
+    def convert_q8_0_to_q2_0(self, src: np.ndarray) -> np.ndarray:
+        n = src.size // 68
+        dst = np.zeros(n * 18, np.uint8)
+        self.lib.orc_convert_q8_0_to_q2_0(_p(src), _p(dst), n)
+        return dst
 
     def route(self, logits: np.ndarray, K: int):
         logits = np.ascontiguousarray(logits, np.float32)
@@ -256,6 +290,24 @@ def router_logits(w_bf16: np.ndarray, x: np.ndarray) -> np.ndarray:
     the reference's tests hold no vector for this kernel."""
     w = (w_bf16.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
     return x.astype(np.float64) @ w.T
+
+
+_REF_MTP = os.path.join(_HERE, "_ref", "libfrx_ref_mtp.so")
+_ref_mtp = None
+
+
+def ref_convert_q8_0_to_q2_0(src: np.ndarray, threads: int = 4) -> np.ndarray | None:
+    """The reference's own requantizer (arch/qwen4exp/mtp.cu compiled unmodified), or None when that
+    library has not been built."""
+    global _ref_mtp
+    if _ref_mtp is None:
+        if not os.path.exists(_REF_MTP):
+            return None
+        _ref_mtp = C.CDLL(_REF_MTP, mode=os.RTLD_LAZY)
+    n = src.size // 68
+    dst = np.zeros(n * 18, np.uint8)
+    _ref_mtp.ref_convert_q8_0_to_q2_0(_p(src), _p(dst), C.c_size_t(n), threads)
+    return dst
 
 
 def port() -> Port:

@@ -68,6 +68,21 @@ void orc_moe_layer(const uint8_t* experts, size_t stride, const uint8_t* shared,
                    const int32_t* ids, const float* wts, int K, const float* gate_logit, float* out, float* yslot,
                    float* ysh, int n_threads);
 
+/* ---- ggml-layout pieces (ggml_oracle.c) ---- */
+
+/* third_party/ggml/src/ggml-cuda/quantize.cu:54-101 as called by kernels/cuda/ggml_gemv.cu:82-87:
+ * x [n_tok][ncols] -> Q8_1 rows of 36-byte blocks {fp16 d; fp16 sum; 32 int8}, rows padded with
+ * zeros to a multiple of 512 values. */
+void orc_quantize_q8_1(const float* x, int ncols, int n_tok, uint8_t* out);
+/* third_party/ggml/src/ggml-cuda/vecdotq.cuh:728-771: one row of ggml Q2_0 blocks against one
+ * Q8_1 row; the per-chunk values d2 * d8 * sumi (float) are added in double. */
+double orc_dot_q2_0_q8_1(const uint8_t* wrow, int ncols, const uint8_t* xq_row);
+/* kernels/cuda/ggml_gemv.h:56-65 (gemv::moe_q) for Q2_0 */
+void orc_moe_q2_0(const uint8_t* w, const uint8_t* gate, const uint8_t* xq, const int32_t* ids, float* dst, int n_tok, int k, int ncols,
+                  int nrows, size_t expert_stride, int act_per_expert);
+/* tests/test_mtp_convert.cu:34-62, arch/qwen4exp/mtp.cu:129-201: Q8_0 block pairs -> ggml Q2_0 blocks */
+void orc_convert_q8_0_to_q2_0(const uint8_t* src, uint8_t* dst, size_t nblocks64);
+
 #ifdef __cplusplus
 }
 #endif

@@ -85,7 +85,14 @@ def test_cpp_shim_compiles_against_the_header():
            "void f(cudaStream_t s, const uint8_t* e, const float* x, const int32_t* ids, void* yd, void* ws, int32_t* o, float* w) {\n"
            "  flashrt::moe_q2::run(e, 884736, 512, 2048, 512, x, ids, 8, 10, yd, ws, flashrt::moe_q2::workspace_bytes(8, 10, 2048, 512, 512), s);\n"
            "  flashrt::qwen4exp::moe_route_topk(s, x, 8, 512, 10, o, w, nullptr);\n"
-           "  flashrt::qwen4exp::moe_hits(nullptr, ids, 10, x, 2560, 640, ws, w, s, 3);\n}\n")
+           "  flashrt::qwen4exp::moe_hits(nullptr, ids, 10, x, 2560, 640, ws, w, s, 3);\n"
+           "  flashrt::moe_q2::run(e, 884736, 512, 2048, 512, x, ids, 8, 10, yd, ws, 1 << 20, s, true, true);\n"
+           # the draft head's MoE as arch/qwen4exp/mtp.cu:636-666 writes it
+           "  const int64_t gu = flashrt::gemv::row_bytes(42, 2048) * 512;\n"
+           "  flashrt::gemv::quantize_q8_1(x, 2048, 3, ws, s);\n"
+           "  flashrt::gemv::moe_q(42, e, e, ws, ids, w, 3, 10, 2048, 512, gu, false, s);\n"
+           "  const flashrt::gemm::MoePlan p = flashrt::gemm::moe_prepare(42, 512, x, false, ids, 64, 10, 2048, ws, flashrt::gemm::workspace_bytes(2048, 640), s);\n"
+           "  flashrt::gemm::moe_run(p, e, gu, w, 512, s);\n}\n")
     with tempfile.NamedTemporaryFile("w", suffix=".cpp") as f:
         f.write(src)
         f.flush()
