@@ -14,7 +14,15 @@ The JSON line carries: `value` with inputs resident in HBM (the 48 layer calls r
 CUDA graph); `e2e` through frx_moe_layers_host with pinned host buffers, copies inside the timed
 region; `roofline` of the gate/up streaming kernel from CUDA events around each of its launches;
 `cpu_baseline`, the reference's own CPU path (oracle/_ref, AVX-512 moe_cpu on all physical cores)
-on a bounded sample of the same workload.
+on a bounded sample of the same workload. The headline keys describe configs[1] at batch 64; the
+other configurations ride along in the same line, each with its own parity figure against the
+CPU oracle at the full shape (512 experts):
+  `decode_batches`  configs[1] at batch 1, 4 and 16: us per layer, layer-tokens/s, fraction of the HBM peak;
+  `prefill`         configs[2] (one GPU: 4,096 tokens, Zipf routing) or configs[4] (--gpus N: 16,384
+                    tokens, uniform and Zipf routing, expert parallel): tokens/s, TFLOP/s of the
+                    expert products, fraction of the measured bf16 peak, the kernel form taken;
+  `verify_stack`    configs[3]: the 48 layers chained (x_next = rmsnorm_unit(x + y)) for a window of
+                    three tokens: tokens/s, us per layer, HBM fraction (latency-limited by nature).
 
 With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the experts of every layer
 are sharded over the ranks (expert parallel), activations and routing are replicated, and each
@@ -127,6 +135,50 @@ def time_cpu(ref, planar, x, ids, wts, workers: int, reps: int) -> float:
     return ref.moe_cpu_timed(planar, EXPERT_BYTES, (E + 1) * EXPERT_BYTES, n_layers, E + 1, N_MODEL, FF, x, ids, wts, workers, reps)
 
 
+def cpu_workers_sweep(ref, planar, x, ids, wts, reps: int = 24) -> dict:
+    """The reference's moe_cpu at its own sweet spots (6 and 8 workers) and on all physical cores:
+    mean, median and 99th percentile of the time of one layer call, and the implied weight bandwidth."""
+    n_layers, B = x.shape[0], x.shape[1]
+    allc = max(1, ref.physical_cpus())
+    out = {}
+    for w in sorted({min(6, allc), min(8, allc), allc}):
+        secs = ref.moe_cpu_times(planar, EXPERT_BYTES, (E + 1) * EXPERT_BYTES, n_layers, E + 1, N_MODEL, FF, x, ids, wts, w, reps)[n_layers:]
+        distinct = float(np.mean([len(np.unique(ids[l])) for l in range(n_layers)]))
+        out[str(w)] = {"mean_us": round(float(secs.mean()) * 1e6, 1), "p50_us": round(float(np.percentile(secs, 50)) * 1e6, 1),
+                       "p99_us": round(float(np.percentile(secs, 99)) * 1e6, 1), "calls": int(secs.size),
+                       "weight_GBps": round(distinct * EXPERT_BYTES / float(secs.mean()) / 1e9, 1)}
+    return out
+
+
+def cpu_config0(ref) -> dict:
+    """BASELINE configs[0]: one Q2_0 expert GEMV (512 x 2048, batch 1) on one host thread, the
+    reference's AVX-512 kernel and its scalar form, with the matrix in cache and streamed from DRAM
+    (a ring of 1,024 matrices, 300 MB)."""
+    from flashrt_b200 import synth
+    rng = np.random.default_rng(synth.SEED_WEIGHTS)
+    rows, cols, mb = 512, 2048, 294912
+    ring = 1024
+    mats = rng.integers(0, 256, size=ring * mb, dtype=np.uint8)
+    d = np.abs(rng.standard_normal(ring * rows * (cols // 64), dtype=np.float32) * np.float32(0.02)).astype(np.float16)
+    d[d == 0] = np.float16(6.103515625e-05)
+    mats.reshape(ring, mb)[:, rows * (cols // 64) * 16:] = d.view(np.uint8).reshape(ring, -1)
+    x = synth.activations(1, cols)[0]
+    alg = mb + cols + cols // 32 * 4 + rows * 4          # weights + Q8 activation + output
+    res = {"shape": "512 x 2048 (out x in), batch 1, one thread", "algorithmic_bytes": alg}
+    for name, avx, reps_c, reps_d in (("matvec_avx512", True, 4000, 4096), ("matvec_ref", False, 60, 64)):
+        if avx and not ref.have_avx512():
+            continue
+        sec_c, y_c = ref.matvec_timed(mats, 1, rows, cols, x, avx, reps_c)
+        sec_d, _ = ref.matvec_timed(mats, ring, rows, cols, x, avx, reps_d)
+        res[name] = {"cached_us": round(sec_c * 1e6, 2), "dram_us": round(sec_d * 1e6, 2), "dram_GBps": round(alg / sec_d / 1e9, 2)}
+        res.setdefault("_y", {})[name] = y_c
+    if "matvec_avx512" in res.get("_y", {}) and "matvec_ref" in res["_y"]:
+        a, b = res["_y"]["matvec_avx512"], res["_y"]["matvec_ref"]
+        res["avx512_vs_scalar_max_err_over_rms"] = float(np.abs(a - b).max() / np.sqrt(np.mean(b.astype(np.float64) ** 2)))
+    res.pop("_y", None)
+    return res
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -149,6 +201,8 @@ def run_reference(args):
     ms = dt / args.steps * 1e3
     value = B * cpu_layers / (dt / args.steps)
     sample = f"{cpu_layers} layers x {B} tokens per step (1.36 GB of experts), quantize + entry lists + moe_cpu per layer"
+    sweep = cpu_workers_sweep(ref, planar, x, ids, wts)
+    config0 = cpu_config0(ref)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -156,16 +210,23 @@ def run_reference(args):
         "config": {"workload": f"configs[1]: one Q2_0 MoE layer decode, batch {B}, hidden 2048, 512 experts + shared, top-10",
                    "batch": B, "layers_per_step": cpu_layers},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": workers, "kind": "reference", "sample": sample,
-                         "avx512_vnni": ref.have_avx512()},
+                         "avx512_vnni": ref.have_avx512(), "workers_sweep": sweep},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config0": config0,
     }))
+
+
+def rel_max(a, b) -> float:
+    """max |a - b| over the RMS of b (the reference's error measure, tests/test_q2_0.cpp:117-124)."""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.sqrt(np.mean(b ** 2)), 1e-30))
 
 
 def run_frx(args):
     import torch
     import torch.distributed as dist
 
-    from flashrt_b200 import moe
+    from flashrt_b200 import moe, synth
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -179,6 +240,8 @@ def run_frx(args):
         moe.check(moe.lib.frx_debug_set_consumer_warps(args.nw))
     if args.narrow is not None:
         moe.check(moe.lib.frx_debug_set_narrow_items(args.narrow))
+    if args.gu_chunks:
+        moe.check(moe.lib.frx_debug_set_gate_up_chunks(args.gu_chunks))
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     e_local = e_hi - e_lo
 
@@ -241,24 +304,25 @@ def run_frx(args):
                 comm.destroy()
             comm = None
 
-    def ep_layer(l: int, xin, lin, gin, o):
+    def layer(l: int, xin, lin, gin, o, ids_l, wts_l, ws_):
+        """One MoE layer call on device tensors: the plain entry on one GPU, the expert-parallel one otherwise."""
+        if world == 1:
+            moe.moe_layer(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, xin, lin, gin, K,
+                          out=o, ids_out=ids_l, wts_out=wts_l, ws=ws_)
+            return
         shared_blob = arena.blob(l, e_local) if rank == 0 else None
         if comm is not None:
             ep.moe_layer_ep_fused(comm, arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o,
-                                  ids[l], wts[l], ws)
+                                  ids_l, wts_l, ws_)
         else:
-            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o, ids[l], wts[l], ws)
+            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o, ids_l, wts_l, ws_)
 
-    def layer_call(l: int):
-        if world == 1:
-            moe.moe_layer(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, x[l], logits[l], gate[l], K,
-                          out=out[l], ids_out=ids[l], wts_out=wts[l], ws=ws)
-        else:
-            ep_layer(l, x[l], logits[l], gate[l], out[l])
+    def ep_layer(l: int, xin, lin, gin, o):
+        layer(l, xin, lin, gin, o, ids[l], wts[l], ws)
 
     def step():
         for l in range(L):
-            layer_call(l)
+            layer(l, x[l], logits[l], gate[l], out[l], ids[l], wts[l], ws)
 
     if world > 1:   # the ranks' set-up times differ; the fused all-reduce waits for a peer for 2 s at most
         torch.cuda.synchronize()
@@ -266,7 +330,7 @@ def run_frx(args):
     step()
     if comm is not None:
         # the fused all-reduce reports a peer that did not answer in time through the workspace status;
-        # if any rank saw that, every rank drops to the NCCL form (with a fresh workspace: the status sticks)
+        # if any rank saw that, every rank drops to the NCCL form
         try:
             moe.workspace_status(ws)
             fused_ok = 1
@@ -278,7 +342,6 @@ def run_frx(args):
         if int(flag.item()) == 0:
             comm.close()
             comm = None
-            ws = moe.workspace(moe.moe_layer_workspace_bytes(B, K, N_MODEL, FF), dev)
             step()
     moe.workspace_status(ws)
     torch.cuda.synchronize()
@@ -290,10 +353,49 @@ def run_frx(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- value: inputs resident in HBM; the 48 layer calls replayed from one CUDA graph. With
-    # NCCL all-reduces on the path the launches stay plain (capturing them together with these
-    # kernels did not complete on the 2-GPU box, so it is not attempted).
+    # With NCCL all-reduces on the path the launches stay plain: a capture of NCCL collectives
+    # together with these kernels once failed to complete, so it is not attempted.
     use_graph = (world == 1 or comm is not None) and not args.no_graph
+
+    def timeit(fn, warmup: int, steps: int) -> float:
+        """Milliseconds per call of fn (device time by CUDA events, the maximum over the ranks); fn is
+        replayed from one CUDA graph where that is possible."""
+        run = fn
+        if use_graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            run = graph.replay
+        for _ in range(warmup):
+            run()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            run()
+        b.record()
+        barrier()
+        t = a.elapsed_time(b) / steps
+        if world > 1:
+            tt = torch.tensor([t], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        return t
+
+    # ---- value: inputs resident in HBM; the 48 layer calls replayed from one CUDA graph
+    sampler = ClockSampler(local) if rank == 0 else None
+    begun = [False]
+
+    def timed_region_begins():
+        if sampler and not begun[0]:
+            sampler.begin()
+            begun[0] = True
+
     run = step
     if use_graph:
         side = torch.cuda.Stream()
@@ -305,12 +407,10 @@ def run_frx(args):
         with torch.cuda.graph(graph):
             step()
         run = graph.replay
-    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         run()
     barrier()
-    if sampler:
-        sampler.begin()
+    timed_region_begins()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -341,12 +441,15 @@ def run_frx(args):
     mean_local = float(np.mean(local_distinct)) + (1.0 if rank == 0 or world == 1 else 0.0)
     gu_alg_bytes = mean_local * GU_BYTES + B * (N_MODEL + N_MODEL // 32 * 8) + B * (K + 1) * FF * 4
     achieved = gu_alg_bytes / (gu_us * 1e-6) / 1e9
-    layer_bytes = float(np.mean([(d + 1) * EXPERT_BYTES for d in distinct])) + B * (E * 4 + N_MODEL * 8) + B * K * 8
+
+    def layer_alg_bytes(dist_list, Bt):
+        return float(np.mean([(d + 1) * EXPERT_BYTES for d in dist_list])) + Bt * (E * 4 + N_MODEL * 8) + Bt * K * 8
+
+    layer_bytes = layer_alg_bytes(distinct, B)
     roofline = {"bound": "hbm", "kernel": "k_stream<gate_up>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_source": peak_src,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch: 224.33 MB for 367 distinct
-                # expert blobs in the ncu capture summarised in profiles/k_stream_decode_b64.md (a 2-layer
-                # case of the same kernel), scaled to this run by the distinct blobs a launch reads
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture of a 2-layer
+                # case of the same kernel, scaled to this run by the distinct blobs a launch reads
                 "traffic": int(mean_local * NCU_GU_TRAFFIC_PER_BLOB), "traffic_source": "ncu capture of a 2-layer case, scaled by distinct expert blobs",
                 "algorithmic_bytes_per_launch": int(gu_alg_bytes), "us_per_launch": gu_us,
                 "timing": "CUDA events around each launch, a separate pass of the same steps without the CUDA graph",
@@ -378,6 +481,7 @@ def run_frx(args):
         assert torch.equal(oh.to(dev), out), "host entry and device entry disagree"
         e2e = {"value": B * L / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
                "h2d_bytes_per_step": L * B * (N_MODEL + E + 1) * 4, "d2h_bytes_per_step": L * B * N_MODEL * 4}
+        del hws
     else:
         # Expert parallel: the activations and logits are replicated, so every rank copies its own
         # from pinned host memory; the all-reduced result goes back to host memory on every rank.
@@ -435,12 +539,35 @@ def run_frx(args):
         e2e = {"value": B * L / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
                "h2d_bytes_per_step": world * L * B * (N_MODEL + E + 1) * 4, "d2h_bytes_per_step": world * L * B * N_MODEL * 4}
 
-    # ---- CPU baseline: the reference's CPU path on a bounded sample (rank 0, single GPU runs only)
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    # ---- the CPU checker (rank 0): the reference's own CPU path where its library travelled with the
+    # repository, else the scalar restatement
+    oracle = ref = port = None
+    if rank == 0 and not args.no_cpu:
         from oracle import oracle
         ref = oracle.ref()
+        port = oracle.port()
+
+    def cpu_layer(planar, x_np, ids_np, wts_np, gate_np):
+        """One layer (routed experts + shared expert) on the CPU: planar [E + 1][blob]."""
+        Bt = x_np.shape[0]
         if ref is not None:
+            idh = np.concatenate([ids_np, np.full((Bt, 1), E, np.int32)], axis=1)
+            gsig = (1.0 / (1.0 + np.exp(-gate_np.astype(np.float32)))).astype(np.float32)[:, None]
+            wth = np.concatenate([wts_np, gsig], axis=1).astype(np.float32)
+            return ref.moe_cpu(planar, EXPERT_BYTES, E + 1, N_MODEL, FF, x_np, idh, wth, workers=max(1, ref.physical_cpus()))
+        return port.moe_layer(planar[:E], EXPERT_BYTES, planar[E], N_MODEL, FF, x_np, ids_np, wts_np, gate_np, n_threads=8)
+
+    def parity_layer0(x_t, ids_t, wts_t, gate_t, out_t):
+        """max |GPU - CPU| / RMS for layer 0 at the full shape (rank 0 only, else None)."""
+        if rank != 0 or port is None or 0 not in keep:
+            return None
+        o = cpu_layer(keep[0], x_t.cpu().numpy(), ids_t.cpu().numpy(), wts_t.cpu().numpy(), gate_t.cpu().numpy())
+        return rel_max(out_t.cpu().numpy(), o)
+
+    # ---- CPU baseline: the reference's CPU path on a bounded sample (rank 0, single GPU runs only)
+    cpu = None
+    if rank == 0 and not args.no_cpu:
+        if world == 1 and ref is not None:
             nl = len(keep)
             planar = np.stack([keep[l] for l in range(nl)])
             idh = np.concatenate([ids[:nl].cpu().numpy(), np.full((nl, B, 1), E, np.int32)], axis=2)
@@ -453,13 +580,15 @@ def run_frx(args):
             sec = time_cpu(ref, planar, xs, idh, wth, workers, reps)
             cpu = {"value": B / sec, "unit": UNIT, "cores": workers, "kind": "reference",
                    "sample": f"{reps} moe_cpu layer calls over {nl} layers x {B} tokens (same weights, routing and activations "
-                             f"as the GPU run), {sec * 1e3:.3f} ms per layer", "avx512_vnni": ref.have_avx512()}
-            # the GPU result against the reference's CPU result on the same inputs
-            o = ref.moe_cpu(planar[0], EXPERT_BYTES, E + 1, N_MODEL, FF, xs[0], idh[0], wth[0], workers=workers)
-            got = out[0].cpu().numpy()
-            cpu["gpu_vs_cpu_max_err_over_rms"] = float(np.abs(got - o).max() / np.sqrt(np.mean(o.astype(np.float64) ** 2)))
-        else:
+                             f"as the GPU run), {sec * 1e3:.3f} ms per layer", "avx512_vnni": ref.have_avx512(),
+                   "workers_sweep": cpu_workers_sweep(ref, planar, xs, idh, wth)}
+        elif world == 1:
             cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+        else:
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference" if ref is not None else "port",
+                   "sample": "not timed on a multi-GPU run (the single-GPU run carries the CPU timing); parity only"}
+        # the GPU result against the CPU result on the same inputs, at every N
+        cpu["gpu_vs_cpu_max_err_over_rms"] = parity_layer0(x[0], ids[0], wts[0], gate[0], out[0])
 
     if world > 1:   # every rank must hold the same routing and the same reduced output
         chk = torch.stack([out.double().sum(), ids.double().sum()])
@@ -467,6 +596,38 @@ def run_frx(args):
         dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
         assert torch.equal(lo_, hi_), "ranks disagree on the layer output"
+
+    # ---- the other configurations, each with its own parity figure
+    extra_steps = max(5, min(args.steps, 20))
+    decode_batches, verify_stack, prefill = None, None, None
+    if not args.no_extras:
+        decode_batches = {}
+        for Bs in (1, 4, 16):
+            if Bs >= B:
+                continue
+            xs_, ls_, gs_ = x[:, :Bs].contiguous(), logits[:, :Bs].contiguous(), gate[:, :Bs].contiguous()
+            ob = torch.empty(L, Bs, N_MODEL, device=dev)
+            ib = torch.empty(L, Bs, K, dtype=torch.int32, device=dev)
+            wb = torch.empty(L, Bs, K, device=dev)
+            wsb = moe.workspace(moe.moe_layer_workspace_bytes(Bs, K, N_MODEL, FF), dev)
+
+            def step_b():
+                for l in range(L):
+                    layer(l, xs_[l], ls_[l], gs_[l], ob[l], ib[l], wb[l], wsb)
+
+            tb = timeit(step_b, 3, extra_steps)
+            moe.workspace_status(wsb)
+            db = [int(torch.unique(ib[l]).numel()) for l in range(L)]
+            lb = layer_alg_bytes(db, Bs)
+            decode_batches[str(Bs)] = {"us_per_layer": round(tb * 1e3 / L, 2), "value": round(Bs * L / (tb * 1e-3), 1), "unit": UNIT,
+                                       "distinct_experts_per_layer_mean": float(np.mean(db)), "algorithmic_bytes_per_layer": int(lb),
+                                       "frac_of_peak": round(lb / world / (tb * 1e-3 / L) / 1e9 / peak, 4),
+                                       "parity_max_err_over_rms": parity_layer0(xs_[0], ib[0], wb[0], gs_[0], ob[0])}
+            del wsb
+        verify_stack = bench_verify_stack(torch, moe, synth, dev, rank, world, L, layer, timeit, layer_planar, x, logits, gate, port, peak,
+                                          extra_steps)
+        prefill = bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, extra_steps)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -478,11 +639,165 @@ def run_frx(args):
                        "cuda_graph": use_graph,
                        "all_reduce": "none" if world == 1 else ("fused into the combine kernel, peer memory over NVLink" if comm is not None else "NCCL")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": sum(v["launches"] for v in kernels.values()), "kernels": kernels,
-            "roofline": roofline, "cpu_baseline": cpu,
+            "roofline": roofline, "cpu_baseline": cpu, "decode_batches": decode_batches, "prefill": prefill, "verify_stack": verify_stack,
         }
         print(json.dumps(line))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_verify_stack(torch, moe, synth, dev, rank, world, L, layer, timeit, layer_planar, x, logits, gate, port, peak, steps):
+    """BASELINE configs[3]: the expert stack walked by a speculative-verify window of three tokens
+    (1 + 2 drafts), the layers chained by x_next = rmsnorm_unit(x + y) in fp32, router logits
+    pre-generated per layer; expert parallel when launched on several GPUs. The step is bound by
+    48 x (five dependent kernels + the exchange), not by HBM: the fraction says how far."""
+    T3 = 3
+    ls_, gs_ = logits[:, :T3].contiguous(), gate[:, :T3].contiguous()
+    xs = torch.empty(L + 1, T3, N_MODEL, device=dev)       # xs[l]: the input of layer l
+    xs[0].copy_(x[0, :T3])
+    ys = torch.empty(L, T3, N_MODEL, device=dev)
+    ib = torch.empty(L, T3, K, dtype=torch.int32, device=dev)
+    wb = torch.empty(L, T3, K, device=dev)
+    wsb = moe.workspace(moe.moe_layer_workspace_bytes(T3, K, N_MODEL, FF), dev)
+
+    def step():
+        for l in range(L):
+            layer(l, xs[l], ls_[l], gs_[l], ys[l], ib[l], wb[l], wsb)
+            moe.chain_rmsnorm_unit(xs[l], ys[l], out=xs[l + 1])
+
+    t = timeit(step, 3, steps)
+    moe.workspace_status(wsb)
+    db = [int(torch.unique(ib[l]).numel()) for l in range(L)]
+    step_bytes = float(sum((d + 1) * EXPERT_BYTES for d in db))
+    res = {"workload": f"configs[3]: {L} chained layers, {T3} tokens per step, 512 experts top-10 + shared, ep{world}",
+           "value": round(T3 / (t * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(t, 4), "us_per_layer": round(t * 1e3 / L, 2),
+           "algorithmic_bytes_per_step": int(step_bytes), "hbm_frac_of_peak": round(step_bytes / world / (t * 1e-3) / 1e9 / peak, 4),
+           "note": "latency-limited: a layer is five dependent kernels (plus the exchange on several GPUs) over about 10 MB of weights"}
+    if rank == 0 and port is not None:
+        # Parity. The oracle needs only the experts the window uses: each layer's blobs are regenerated
+        # on the device and the used ones copied out. Two figures: every layer's output against the
+        # oracle's layer on the same input (and the join bit for bit), and the last layer's output
+        # against the oracle run free over the whole chain.
+        x_free = xs[0].cpu().numpy()
+        worst, join_exact, ids_exact, y_free = 0.0, True, True, None
+        for l in range(L):
+            p = layer_planar(l)
+            idl, wl, gl = ib[l].cpu().numpy(), wb[l].cpu().numpy(), gs_[l].cpu().numpy()
+            uniq = np.unique(idl)
+            sel = p[torch.from_numpy(np.append(uniq, E).astype(np.int64)).to(dev)].cpu().numpy()
+            del p
+            loc = np.searchsorted(uniq, idl).astype(np.int32)
+            ids_exact = ids_exact and bool(np.array_equal(port.route(ls_[l].cpu().numpy(), K)[0], idl))
+            x_l, y_l = xs[l].cpu().numpy(), ys[l].cpu().numpy()
+            y_or = port.moe_layer(np.ascontiguousarray(sel[:-1]), EXPERT_BYTES, sel[-1], N_MODEL, FF, x_l, loc, wl, gl, n_threads=8)
+            worst = max(worst, rel_max(y_l, y_or))
+            join_exact = join_exact and bool(np.array_equal(port.chain_rmsnorm_unit(x_l, y_l), xs[l + 1].cpu().numpy()))
+            y_free = port.moe_layer(np.ascontiguousarray(sel[:-1]), EXPERT_BYTES, sel[-1], N_MODEL, FF, x_free, loc, wl, gl, n_threads=8)
+            x_free = port.chain_rmsnorm_unit(x_free, y_free)
+        res["parity"] = {"per_layer_max_err_over_rms": worst, "layer_join_bit_exact": join_exact, "router_ids_bit_exact": ids_exact,
+                         "last_layer_free_running_err_over_rms": rel_max(ys[L - 1].cpu().numpy(), y_free),
+                         "checker": "scalar restatement of the reference's CPU path, every layer"}
+    return res
+
+
+def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, steps):
+    """BASELINE configs[2] (one GPU: 4,096 tokens, Zipf routing) or configs[4] (several GPUs: 16,384
+    tokens, uniform and Zipf routing, tokens and experts sharded, all-to-all dispatch and combine)
+    on the experts of layer 0. A step is route + grouped expert products + combine."""
+    from flashrt_b200 import ep
+    peak_tf = 1657.0
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak_tf = float(json.load(open(pk))["bf16_tflops"])
+    T = 4096 if world == 1 else 16384
+    Tl = T // world
+    res = {}
+    for routing in (("zipf",) if world == 1 else ("uniform", "zipf")):
+        xa = synth.activations(T, N_MODEL, through_bf16=True)
+        la = synth.zipf_logits(T, E) if routing == "zipf" else synth.router_logits(T, E)
+        x = torch.from_numpy(xa[rank * Tl:(rank + 1) * Tl]).to(dev)
+        lg = torch.from_numpy(la[rank * Tl:(rank + 1) * Tl]).to(dev)
+        keepers = {}
+        if world == 1:
+            ws = moe.workspace(moe.moe_q2.workspace_bytes(T, K, N_MODEL, FF, E), dev)
+            yd = torch.empty(T * K, N_MODEL, device=dev)
+            out = torch.empty(T, N_MODEL, device=dev)
+
+            def step():
+                ids, wts = moe.moe_route_topk(lg, K)
+                moe.moe_q2.run(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, ids, yd=yd, ws=ws)
+                moe.moe_combine(yd.view(T, K, N_MODEL), wts, None, None, None, out=out)
+                keepers["ids"], keepers["wts"] = ids, wts
+        else:
+            pipe = ep.PrefillEp(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, Tl, K)
+
+            def step():
+                keepers["out"], keepers["ids"], keepers["wts"] = pipe.run(x, lg)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = a.elapsed_time(b) / steps
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        ncls = 8
+        pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
+        moe.check(moe.lib.frx_profile_begin())
+        step()
+        moe.check(moe.lib.frx_profile_end(pms, pn, ncls))
+        names = [moe.lib.frx_profile_class_name(i).decode() for i in range(ncls)]
+        kus = {names[i]: round(1e3 * float(pms[i]), 2) for i in range(ncls) if pn[i]}
+        flops = T * K * 3 * 2 * N_MODEL * FF
+        gemm_ms = (kus.get("gate_up", 0.0) + kus.get("down", 0.0)) / 1e3
+        ids_all = keepers["ids"]
+        cnt = torch.bincount(ids_all.reshape(-1).to(torch.int64), minlength=E)
+        entry = {"workload": f"configs[{2 if world == 1 else 4}]: one MoE layer prefill, {T} tokens, hidden 2048, 512 experts top-10, "
+                             f"{routing} routing, ep{world}",
+                 "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 4), "kernels_us": kus,
+                 "flops_per_step": flops, "tflops_step": round(flops / (ms * 1e-3) / 1e12, 1),
+                 "tflops_expert_products_rank0": round(flops / world / max(gemm_ms, 1e-9) / 1e9, 1) if gemm_ms else None,
+                 "frac_of_bf16_peak_step": round(flops / world / (ms * 1e-3) / 1e12 / peak_tf, 4), "peak_tflops": peak_tf,
+                 "form": ("tcgen05" if Tl * K >= 256 * (e_hi - e_lo) else "streaming") if world == 1 else "streaming or tcgen05 by the rank's slot count",
+                 "tokens_per_expert_rank0": {"mean": float(cnt.float().mean()), "max": int(cnt.max()), "min": int(cnt.min())}}
+        if rank == 0 and port is not None and 0 in keep:
+            ids_np, wts_np = ids_all.cpu().numpy(), keepers["wts"].cpu().numpy()
+            xl = xa[:Tl]
+            ids_or, _, _ = port.route(la[:64], K)
+            entry["router_ids_bit_exact_64_tokens"] = bool(np.array_equal(ids_or, ids_np[:64]))
+            xq, xd = port.quantize_q8(xl[:8])
+            if world == 1:
+                ys = yd.view(T, K, N_MODEL)
+                worst = 0.0
+                rng = np.random.default_rng(1)
+                for t_, k_ in zip(rng.integers(0, 8, 12), rng.integers(0, K, 12)):
+                    want = port.expert_ffn(keep[0][ids_np[t_, k_]], N_MODEL, FF, xq[t_], xd[t_])
+                    worst = max(worst, rel_max(ys[t_, k_].cpu().numpy(), want))
+                entry["parity_slot_sample_max_err_over_rms"] = worst
+                got = out[:2].cpu().numpy()
+            else:
+                got = keepers["out"][:2].cpu().numpy()
+            want = np.stack([port.moe_layer(np.ascontiguousarray(keep[0][np.sort(ids_np[t_])]), EXPERT_BYTES, None, N_MODEL, FF, xl[t_:t_ + 1],
+                                            np.arange(K, dtype=np.int32)[None], wts_np[t_:t_ + 1][:, np.argsort(ids_np[t_])], None)[0]
+                             for t_ in range(2)])
+            entry["parity_layer_output_2_tokens_max_err_over_rms"] = rel_max(got, want)
+        res[routing] = entry
+        if world == 1:
+            del ws, yd, out
+    return res
 
 
 def run_prefill(args):
@@ -600,7 +915,9 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16)")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: skip the decode_batches, prefill and verify_stack keys")
+    ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16, 20)")
+    ap.add_argument("--gu-chunks", type=int, default=0, help="tuning: K slices per gate/up task")
     ap.add_argument("--narrow", type=int, default=None, help="tuning: 0 sends every work item through the eight-token form")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"], help="decode = configs[1] (default), prefill = configs[2]")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill tokens")

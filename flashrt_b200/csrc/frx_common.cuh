@@ -246,16 +246,16 @@ __device__ __forceinline__ void mma_u8s8_c4(uint64_t& lo, uint64_t& hi, uint32_t
 // different row groups.
 __device__ __forceinline__ void mma_u8s8_chain2(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3,
-                                                uint32_t f0, uint32_t f1, const int4& c) {
+                                                uint32_t f0, uint32_t f1, int c0, int c1) {
+    // the accumulator input is {c0, c1} for the lane's two token columns, in both row halves
     asm volatile(
         "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%14,%15,%16,%17};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%14,%15,%14,%15};\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%8,%9,%10,%11}, {%12,%13}, {d0,d1,d2,d3};\n\t"
         "mov.b64 %0, {d0,d1};\n\t"
         "mov.b64 %1, {d2,d3};\n\t}"
         : "=l"(lo), "=l"(hi)
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c.x), "r"(c.y),
-          "r"(c.z), "r"(c.w));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c0), "r"(c1));
 }
 
 __device__ __forceinline__ void mma_u8s8_bias(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

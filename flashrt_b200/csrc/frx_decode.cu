@@ -512,14 +512,14 @@ __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ uni
         for (int j = 0; j < 2; ++j) {
             const int b = 2 * u + j;
             const uint4 bfa = bf0_p[b * 32], bfb = bf1_p[b * 32];
-            const int4 cq0 = ci_p[b * 8], cq1 = ci_p[b * 8 + 1];
+            const int4 cq = ci_p[b * 8];   // {c0, c1} of the first half of the block, {c0, c1} of the second
             const ulonglong2 a = da_p[b * 4];
             const uint32_t w0 = j ? c0.y : c0.x, w1 = j ? c0.w : c0.z;   // group 0: rows g, g + 8
             const uint32_t x0 = j ? c1.y : c1.x, x1 = j ? c1.w : c1.z;   // group 1
             const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
             uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq0);
-            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq1);
+            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq.x, cq.y);
+            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq.z, cq.w);
             const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
             const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
             const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
@@ -692,14 +692,18 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
             const float av = p.aa[row * (nb * 2) + r];
             daw[dst] = av;
             // the MMA's accumulator input of this block half: {c0, c1, c0, c1} for the lane's two token columns and both row halves
-            const int cq = ((b * 4 + (g >> 1)) * 2 + s) * 4 + (g & 1);
             const float cv = p.ac[row * (nb * 2) + r];
-            ciw[cq] = cv;
-            ciw[cq + 2] = cv;
-            if (narrow) {   // lanes t4 = 2, 3 work on the same tokens as t4 = 0, 1 (for the second row group)
-                daw[dst + 8] = av;
+            if (narrow) {
+                // one quad per (block, t4): {c0, c1} of the first half, {c0, c1} of the second; lanes
+                // t4 = 2, 3 work on the same tokens as t4 = 0, 1 (for the second row group)
+                const int cq = (b * 4 + (g >> 1)) * 8 + s * 2 + (g & 1);
+                ciw[cq] = cv;
                 ciw[cq + 16] = cv;
-                ciw[cq + 18] = cv;
+                daw[dst + 8] = av;
+            } else {
+                const int cq = ((b * 4 + (g >> 1)) * 2 + s) * 4 + (g & 1);
+                ciw[cq] = cv;
+                ciw[cq + 2] = cv;
             }
         }
     };
@@ -1113,6 +1117,7 @@ __global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds
 
 int g_nw = 16;   // consumer warps of k_stream (8, 12 or 16)
 int g_narrow = 1; // items of at most kNarrowTok tokens take the narrow form of the inner product
+int g_gu_chunks = 0;   // chunks per gate/up task (0: by shape)
 
 struct StreamCfg {
     int nw_gu = 8, nw_dn = 8;     // warps per block
@@ -1139,7 +1144,7 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
         int first = g_nw;
         if (max_tasks > 0 && max_tasks <= 4LL * sms) first = 4;
         else if (max_tasks > 0 && max_tasks <= 8LL * sms) first = 8;
-        const int prefs[3] = {first, first > 12 ? 12 : 8, 8};
+        const int prefs[3] = {first, first > 16 ? 16 : first > 12 ? 12 : 8, 8};
         for (int k = 0; k < 3; ++k) {
             nw = prefs[k];
             for (nbuf = kMaxItemBufs; nbuf >= 2; --nbuf)
@@ -1152,7 +1157,8 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
     };
     const int gu_units = n / kUnitK, dn_units = ff / kUnitK;
     // gate/up: a task is two groups, fetched in K slices; down: kDownGroups groups in two chunks of whole groups
-    const int gu_chunks = gu_units % 4 == 0 ? 4 : gu_units % 2 == 0 ? 2 : 1;
+    int gu_chunks = gu_units % 4 == 0 ? 4 : gu_units % 2 == 0 ? 2 : 1;
+    if (g_gu_chunks > 0 && gu_units % g_gu_chunks == 0) gu_chunks = g_gu_chunks;
     if (!fit(n, uint32_t(gu_units) * kUnitBytes * 2, gu_chunks, max_items * (ff / 16), c.nw_gu, c.cpt_gu, c.rpw_gu, c.nbuf_gu, c.smem_gu) ||
         !fit(ff, uint32_t(dn_units) * kUnitBytes * kDownGroups, 2, max_items * (n / 16 / kDownGroups), c.nw_dn, c.cpt_dn, c.rpw_dn, c.nbuf_dn,
              c.smem_dn))
@@ -1167,7 +1173,7 @@ void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_
     if (upc == kFixed)
         launch_pdl(k_stream<GATE_UP, NW, kFixed>, dim3(sms), dim3(NW * 32), smem, stream, p);
     else
-        launch_pdl(k_stream<GATE_UP, NW, 0>, dim3(sms), dim3(NW * 32), smem, stream, p);
+        launch_pdl(k_stream<GATE_UP, NW, 0>, dim3(sms), dim3(NW * 32), smem, stream, p);   // any other split of K
 }
 
 template <bool GATE_UP>
@@ -1176,6 +1182,7 @@ void launch_stream(const StreamParams& p, int nw, int upc, uint32_t smem, cudaSt
         case 4: launch_stream_nw<GATE_UP, 4>(p, upc, smem, stream); break;
         case 8: launch_stream_nw<GATE_UP, 8>(p, upc, smem, stream); break;
         case 12: launch_stream_nw<GATE_UP, 12>(p, upc, smem, stream); break;
+        case 20: launch_stream_nw<GATE_UP, 20>(p, upc, smem, stream); break;
         default: launch_stream_nw<GATE_UP, 16>(p, upc, smem, stream); break;
     }
 }
@@ -1198,7 +1205,9 @@ int set_smem_attr() {
         reinterpret_cast<const void*>(k_stream<true, 12, 4>),  reinterpret_cast<const void*>(k_stream<true, 12, 0>),
         reinterpret_cast<const void*>(k_stream<false, 12, 4>), reinterpret_cast<const void*>(k_stream<false, 12, 0>),
         reinterpret_cast<const void*>(k_stream<true, 16, 4>),  reinterpret_cast<const void*>(k_stream<true, 16, 0>),
-        reinterpret_cast<const void*>(k_stream<false, 16, 4>), reinterpret_cast<const void*>(k_stream<false, 16, 0>)};
+        reinterpret_cast<const void*>(k_stream<false, 16, 4>), reinterpret_cast<const void*>(k_stream<false, 16, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 20, 4>),  reinterpret_cast<const void*>(k_stream<true, 20, 0>),
+        reinterpret_cast<const void*>(k_stream<false, 20, 4>), reinterpret_cast<const void*>(k_stream<false, 20, 0>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
@@ -1647,8 +1656,13 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
 }
 
 // Tuning knobs for measurements (process-wide, not thread-safe: set them before any compute call).
+int frx_debug_set_gate_up_chunks(int chunks) {
+    if (chunks < 0 || chunks > 16) return FRX_ERR_ARG;
+    g_gu_chunks = chunks;
+    return FRX_OK;
+}
 int frx_debug_set_consumer_warps(int nw) {
-    if (nw != 8 && nw != 12 && nw != 16) return FRX_ERR_ARG;
+    if (nw != 8 && nw != 12 && nw != 16 && nw != 20) return FRX_ERR_ARG;
     g_nw = nw;
     return FRX_OK;
 }

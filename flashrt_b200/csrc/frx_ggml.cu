@@ -312,7 +312,7 @@ int launch_dot(DotArgs a, int grid_x, cudaStream_t stream) {
     a.tma = ((uintptr_t(a.w) | uintptr_t(a.gate) | a.expert_stride | tile_bytes) % 16 == 0) ? 1 : 0;
     a.wait_ns = wait_limit_ns();
     const DotSmem sm = dot_smem(NT, a.ncols, int(tile_bytes), GATE);
-    if (int(sm.total) > max_smem_optin()) return fail(FRX_ERR_SHAPE, "ggml-layout product: ncols %d needs %u bytes of shared memory", a.ncols, sm.total);
+    if (int(sm.total) > max_smem_optin() - 1024) return fail(FRX_ERR_SHAPE, "ggml-layout product: ncols %d needs %u bytes of shared memory", a.ncols, sm.total);
     static std::mutex mu;
     static unsigned set_mask[64] = {};
     int dev = 0;
@@ -321,7 +321,7 @@ int launch_dot(DotArgs a, int grid_x, cudaStream_t stream) {
         std::lock_guard<std::mutex> lk(mu);
         const unsigned bit = 1u << ((NT > 1 ? 2 : 0) + (GATE ? 1 : 0));
         if (dev >= 0 && dev < 64 && !(set_mask[dev] & bit)) {
-            FRX_CUDA(cudaFuncSetAttribute(k_ggml_dot<NT, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin()));
+            FRX_CUDA(cudaFuncSetAttribute(k_ggml_dot<NT, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 1024));   // less the static part
             set_mask[dev] |= bit;
         }
     }

@@ -78,6 +78,7 @@ SIGNATURES = {
     "frx_ipc_close": (_i, [_vp]),
     "frx_ep_debug_stamps": (_i, [_vp, _i, _i, _vp]),
     "frx_debug_set_consumer_warps": (_i, [_i]),
+    "frx_debug_set_gate_up_chunks": (_i, [_i]),
     "frx_debug_set_narrow_items": (_i, [_i]),
     "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),
     "frx_moe_decode_static_status": (_i, [_vp]),
@@ -97,6 +98,7 @@ SIGNATURES = {
     "frx_moe_prefill_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
     "frx_moe_prefill_umma_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
     "frx_moe_prefill_stream_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
+    "frx_chain_rmsnorm_unit": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "frx_gemv_q8_1_bytes": (_sz, [_i64, _i]),
     "frx_gemv_row_bytes": (_i64, [C.c_uint32, _i64]),
     "frx_gemv_quantize_q8_1": (_i, [_vp, _i64, _i, _vp, _vp]),

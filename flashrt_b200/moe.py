@@ -540,3 +540,13 @@ def convert_q8_0_to_q2_0(src: torch.Tensor, stream=None) -> torch.Tensor:
     dst = torch.empty(n * 18, dtype=torch.uint8, device=src.device)
     check(lib.frx_convert_q8_0_to_q2_0(_ptr(src), _ptr(dst), n, _stream(stream)))
     return dst
+
+
+def chain_rmsnorm_unit(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """The layer join of the chained-stack benchmark: (x + y) / sqrt(mean((x + y)^2) + 1e-6) per row."""
+    _dev(x, y, out)
+    T, n = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    check(lib.frx_chain_rmsnorm_unit(_ptr(x), _ptr(y), _ptr(out), T, n, _stream(stream)))
+    return out

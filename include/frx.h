@@ -59,13 +59,15 @@ const char* frx_profile_class_name(int cls);
 
 /* Tuning knobs for measurements and tests; no counterpart in the reference. Process-wide and not
  * thread-safe: set them before any compute call, not while calls are in flight.
- * frx_debug_set_consumer_warps: warps per block of the streaming expert kernel (8, 12 or 16; default 16).
+ * frx_debug_set_consumer_warps: warps per block of the streaming expert kernel (8, 12, 16 or 20; default 16).
+ * frx_debug_set_gate_up_chunks: the number of K slices a gate/up task is fetched in (0: chosen by shape).
  * frx_debug_set_narrow_items: 1 (default) lets work items of at most four tokens take the narrow
  * form of the inner product (two row groups share one MMA accumulator, half the float work per row);
  * 0 sends every item through the eight-token form. Results are the same bits either way.
  * frx_debug_set_wait_limit_ns: the longest a kernel waits on a barrier, a flag or a peer before it
  * gives up and reports FRX_ERR_DEVICE through the workspace status (default 2 s; 0 restores it). */
 int frx_debug_set_consumer_warps(int nw);
+int frx_debug_set_gate_up_chunks(int chunks);
 int frx_debug_set_narrow_items(int on);
 int frx_debug_set_wait_limit_ns(unsigned long long ns);
 
@@ -357,6 +359,13 @@ int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, in
                             int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
 int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
                               int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
+
+/* The join between layers of the chained expert-stack benchmark (a 48-layer stack walked by a
+ * window of three tokens): x_next[t] = r / sqrt(mean(r^2) + 1e-6), r = x[t] + y[t], an RMS norm
+ * with unit weight. No counterpart in the reference, whose MoE layers are joined by its attention
+ * blocks. x_next may be x. The operation order is fixed (see frx_chain.cu) so that a CPU
+ * restatement gives the same bits. T rows of n floats. */
+int frx_chain_rmsnorm_unit(const float* x, const float* y, float* x_next, int T, int n, frx_stream_t stream);
 
 /* ---- ggml-layout entry points: gemv:: (kernels/cuda/ggml_gemv.h:26-65) and gemm::
  * (kernels/cuda/ggml_gemm.h:27-68) for ggml type 42 (Q2_0), as the draft head's MoE calls them

@@ -129,6 +129,12 @@ class Port:
         self.lib.orc_expert_ffn(_p(blob), n, ff, _p(xq), _p(xd), _p(out), _p(h), _p(hq), _p(hd))
         return (out, h, hq, hd) if want_hidden else out
 
+    def chain_rmsnorm_unit(self, x: np.ndarray, y: np.ndarray) -> np.ndarray:
+        x, y = np.ascontiguousarray(x, np.float32), np.ascontiguousarray(y, np.float32)
+        out = np.empty_like(x)
+        self.lib.orc_chain_rmsnorm_unit(_p(x), _p(y), _p(out), x.shape[0], x.shape[1])
+        return out
+
     # ---- ggml-layout pieces
     @staticmethod
     def q8_1_row_bytes(ncols: int) -> int:
@@ -201,6 +207,27 @@ class Ref:
         lib.ref_moe_cpu_timed.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
                                           C.c_int]
+
+    def moe_cpu_times(self, experts, stride, layer_stride, n_layers, E, n, ff, x, ids, wts, workers, reps) -> np.ndarray:
+        """Seconds of each of `reps` moe_cpu calls (quantize + entry list + moe_cpu), cycling over n_layers."""
+        x = np.ascontiguousarray(x, np.float32)
+        ids = np.ascontiguousarray(ids, np.int32)
+        wts = np.ascontiguousarray(wts, np.float32)
+        T, K = ids.shape[-2], ids.shape[-1]
+        out = np.empty((T, n), np.float32)
+        secs = np.zeros(reps, np.float64)
+        self.lib.ref_moe_cpu_times(_p(experts), C.c_size_t(stride), C.c_size_t(layer_stride), n_layers, E, n, ff, _p(x), T, _p(ids), _p(wts), K,
+                                   _p(out), workers, reps, _p(secs))
+        return secs
+
+    def matvec_timed(self, mats: np.ndarray, n_mats: int, rows: int, cols: int, x: np.ndarray, avx: bool, reps: int):
+        """(seconds per call, y) of one planar matrix x one token on one thread, cycling over n_mats matrices."""
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros(rows, np.float32)
+        fn = self.lib.ref_matvec_timed
+        fn.restype = C.c_double
+        sec = fn(_p(mats), n_mats, rows, cols, _p(x), _p(y), int(avx), reps)
+        return float(sec), y
 
     def have_avx512(self) -> bool:
         return bool(self.lib.ref_have_avx512())

@@ -322,3 +322,31 @@ void orc_moe_layer(const uint8_t* experts, size_t stride, const uint8_t* shared,
     free(xq);
     free(xd);
 }
+
+/* The layer join of the chained expert-stack benchmark (no reference counterpart: the benchmark
+ * definition itself): out = r / sqrt(mean(r^2) + 1e-6), r = x + y, with the operation order of the
+ * GPU kernel: 32 partial sums of squares in double, partial l over elements l, l + 32, ... in
+ * that order, combined by a butterfly (offsets 16, 8, 4, 2, 1), then one double division and
+ * square root, the factor rounded to float. */
+void orc_chain_rmsnorm_unit(const float* x, const float* y, float* out, int T, int n) {
+    for (int t = 0; t < T; ++t) {
+        const float* xr = x + (size_t)t * n;
+        const float* yr = y + (size_t)t * n;
+        double part[32];
+        for (int l = 0; l < 32; ++l) {
+            double ss = 0.0;
+            for (int i = l; i < n; i += 32) {
+                const float r = xr[i] + yr[i];
+                ss += (double)r * (double)r;
+            }
+            part[l] = ss;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            double nxt[32];
+            for (int l = 0; l < 32; ++l) nxt[l] = part[l] + part[l ^ o];
+            memcpy(part, nxt, sizeof part);
+        }
+        const float inv = (float)(1.0 / sqrt(part[0] / (double)n + 1e-6));
+        for (int i = 0; i < n; ++i) out[(size_t)t * n + i] = (xr[i] + yr[i]) * inv;
+    }
+}

@@ -68,6 +68,10 @@ void orc_moe_layer(const uint8_t* experts, size_t stride, const uint8_t* shared,
                    const int32_t* ids, const float* wts, int K, const float* gate_logit, float* out, float* yslot,
                    float* ysh, int n_threads);
 
+/* The layer join of the chained expert-stack benchmark: out[t] = r / sqrt(mean(r^2) + 1e-6), r = x[t] + y[t],
+ * in the operation order of the GPU kernel (bit-identical). */
+void orc_chain_rmsnorm_unit(const float* x, const float* y, float* out, int T, int n);
+
 /* ---- ggml-layout pieces (ggml_oracle.c) ---- */
 
 /* third_party/ggml/src/ggml-cuda/quantize.cu:54-101 as called by kernels/cuda/ggml_gemv.cu:82-87:

@@ -147,6 +147,39 @@ double ref_moe_cpu_timed(const uint8_t* experts, size_t stride, size_t layer_str
     return std::chrono::duration<double>(t1 - t0).count() / reps;
 }
 
+// The same loop with every call timed on its own: secs [reps] receives the seconds of each call
+// (for the median and the tail of the CPU baseline).
+void ref_moe_cpu_times(const uint8_t* experts, size_t stride, size_t layer_stride, int n_layers, int E, int n, int ff, const float* x,
+                       int T, const int32_t* ids, const float* wts, int K, float* out, int workers, int reps, double* secs) {
+    const ExpertShape s{n, ff};
+    CpuPool& p = pool(workers);
+    std::vector<uint8_t> scratch(moe_cpu_scratch_bytes(s, T * K, workers));
+    for (int r = 0; r < reps; ++r) {
+        const int l = r % n_layers;
+        const auto t0 = std::chrono::steady_clock::now();
+        Acts a(x + size_t(l) * T * n, T, n);
+        const std::vector<Miss> miss =
+            build_entries(experts + size_t(l) * layer_stride, stride, E, ids + size_t(l) * T * K, wts + size_t(l) * T * K, T, K);
+        moe_cpu(p, s, miss.data(), int(miss.size()), a.a.data(), T, out, n, scratch.data());
+        secs[r] = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    }
+}
+
+// One planar matrix times one token on one thread, `reps` times, cycling over n_mats matrices laid
+// out back to back (many matrices: the weights come from DRAM; one: from cache). The activation is
+// quantized once outside the timed loop, as the reference's own micro-benchmark does. Returns
+// seconds per call; y [rows] holds the last result.
+double ref_matvec_timed(const uint8_t* mats, int n_mats, int rows, int cols, const float* x, float* y, int avx, int reps) {
+    Acts a(x, 1, cols);
+    const size_t mb = mat_bytes(rows, cols);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int r = 0; r < reps; ++r) {
+        const Mat w = mat_view(mats + size_t(r % n_mats) * mb, rows, cols);
+        (avx ? matvec_avx512 : matvec_ref)(w, a.a.data(), 1, 0, rows, y, rows);
+    }
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() / reps;
+}
+
 void ref_pool_release() {
     g_pool.reset();
     g_pool_n = 0;

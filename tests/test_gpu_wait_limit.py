@@ -63,7 +63,7 @@ def test_fused_all_reduce_gives_up_after_the_limit_and_recovers(port):
         moe.workspace_status(ws)
     finally:
         check(lib.frx_debug_set_wait_limit_ns(0))
-    want = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, dx, cuda(ids), cuda(wts), None)
+    want = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, dx, ids_o, wts_o, None)   # the routing weights of the call itself
     assert np.array_equal(ids_o.cpu().numpy(), ids)
     assert torch.equal(out, want + 1.0)
     del own_t, peer_t
