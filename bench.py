@@ -626,7 +626,7 @@ def run_frx(args):
             del wsb
         verify_stack = bench_verify_stack(torch, moe, synth, dev, rank, world, L, layer, timeit, layer_planar, x, logits, gate, port, peak,
                                           extra_steps)
-        prefill = bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, extra_steps)
+        prefill = bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, extra_steps, layer_planar)
 
     if rank == 0:
         line = {
@@ -702,7 +702,7 @@ def bench_verify_stack(torch, moe, synth, dev, rank, world, L, layer, timeit, la
     return res
 
 
-def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, steps):
+def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, e_hi, keep, port, steps, layer_planar):
     """BASELINE configs[2] (one GPU: 4,096 tokens, Zipf routing) or configs[4] (several GPUs: 16,384
     tokens, uniform and Zipf routing, tokens and experts sharded, all-to-all dispatch and combine)
     on the experts of layer 0. A step is route + grouped expert products + combine."""
@@ -731,7 +731,21 @@ def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, 
                 moe.moe_combine(yd.view(T, K, N_MODEL), wts, None, None, None, out=out)
                 keepers["ids"], keepers["wts"] = ids, wts
         else:
-            pipe = ep.PrefillEp(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, Tl, K)
+            # Skewed routing: the experts are dealt to the ranks round-robin in order of popularity (a
+            # load-time decision: the counts of one routing pass over the tokens), uniform routing keeps
+            # contiguous ranges. A dealt placement gets its own arena, loaded with this rank's experts.
+            owner, ptr, stride_ = None, arena.blob(0, 0), arena.stride
+            if routing == "zipf":
+                top = torch.topk(torch.from_numpy(la).to(dev), K, dim=1).indices
+                counts = torch.bincount(top.reshape(-1), minlength=E).cpu().numpy()
+                owner = ep.expert_placement(counts, world)
+                mine = np.nonzero(owner == rank)[0]
+                keepers["arena"] = moe.ExpertArena(1, len(mine), N_MODEL, FF)
+                p0 = layer_planar(0)
+                keepers["arena"].load_planar(0, 0, len(mine), p0[torch.from_numpy(mine).to(dev)].contiguous().view(-1))
+                del p0
+                ptr, stride_ = keepers["arena"].blob(0, 0), keepers["arena"].stride
+            pipe = ep.PrefillEp(ptr, stride_, E, N_MODEL, FF, Tl, K, owner=owner)
 
             def step():
                 keepers["out"], keepers["ids"], keepers["wts"] = pipe.run(x, lg)
@@ -771,7 +785,9 @@ def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, 
                  "flops_per_step": flops, "tflops_step": round(flops / (ms * 1e-3) / 1e12, 1),
                  "tflops_expert_products_rank0": round(flops / world / max(gemm_ms, 1e-9) / 1e9, 1) if gemm_ms else None,
                  "frac_of_bf16_peak_step": round(flops / world / (ms * 1e-3) / 1e12 / peak_tf, 4), "peak_tflops": peak_tf,
-                 "form": ("tcgen05" if Tl * K >= 256 * (e_hi - e_lo) else "streaming") if world == 1 else "streaming or tcgen05 by the rank's slot count",
+                 "form": ("tcgen05" if T * K >= 256 * E else "streaming") if world == 1
+                 else "streaming per chunk of 4 (slots per expert and chunk below 256); Q8 all-gather dispatch, fp32 reduce-scatter combine, "
+                      + ("experts dealt round-robin by popularity" if routing == "zipf" else "contiguous expert ranges"),
                  "tokens_per_expert_rank0": {"mean": float(cnt.float().mean()), "max": int(cnt.max()), "min": int(cnt.min())}}
         if rank == 0 and port is not None and 0 in keep:
             ids_np, wts_np = ids_all.cpu().numpy(), keepers["wts"].cpu().numpy()
@@ -842,13 +858,15 @@ def run_prefill(args):
     yd = torch.empty(Tl * K, N_MODEL, device=dev)
     out = torch.empty(Tl, N_MODEL, device=dev)
 
+    pipe = ep.PrefillEp(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, Tl, K) if world > 1 else None
+
     def step():
         if world == 1:
             ids, wts = moe.moe_route_topk(logits, K)
             moe.moe_q2.run(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, ids, yd=yd, ws=ws, form=args.form)
             moe.moe_combine(yd.view(Tl, K, N_MODEL), wts, None, None, None, out=out)
         else:
-            ep.moe_prefill_ep(arena.blob(0, 0), arena.stride, E, N_MODEL, FF, x, logits, K)
+            pipe.run(x, logits)
 
     def barrier():
         if world > 1:

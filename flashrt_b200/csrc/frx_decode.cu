@@ -141,7 +141,7 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
 __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
                                                       int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c,
                                                       const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi,
-                                                      int block64) {
+                                                      int block64, const int32_t* __restrict__ e_map) {
     pdl_wait();
     pdl_trigger();
     const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
         const size_t r = blk / size_t(k / kQ8);
         if (r < size_t(routed_rows)) {
             const int e = slot_ids[r];
-            live = e >= e_lo && e < e_hi;
+            live = e_map ? e_map[e] >= 0 : (e >= e_lo && e < e_hi);   // (ids were range-checked by the grouping kernels)
         }
     }
     const int j = int(quad & 7);        // values 4 j .. 4 j + 3 of the block
@@ -192,6 +192,29 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
         c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
     }
 }
+// Activations that arrive already quantized (natural order: codes [rows][k] int8, block scales
+// [rows][k/32] float, as frx_quantize_q8 writes them) into the fragment form above: a permutation
+// of the codes, the scale table, and the accumulator inputs from the block sums of the codes.
+__global__ void __launch_bounds__(256) k_q8_to_frag(const int8_t* __restrict__ xq, const float* __restrict__ xd, int k, size_t n_blocks,
+                                                    int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
+    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= n_blocks) return;
+    const int code = xq[blk * kQ8 + lane];
+    int sum = code;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const int bpr = k / kQ8;
+    const size_t row = blk / bpr;
+    const int rb = int(blk % bpr), b = rb >> 1, sh = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
+    q[row * k + ((b * 4 + t) * 4 + sh * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
+    if (lane == 0) {
+        const float d = xd[blk];
+        a[blk] = sh ? d * 0.0625f : d;
+        c[blk] = __int_as_float(kMagicBits - (sh ? 16 * sum : sum));
+    }
+}
+
 __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
                                                     float* __restrict__ a, float* __restrict__ c, int block64) {
     pdl_wait();
@@ -364,6 +387,7 @@ struct StreamParams {
     const float* ac;
     const int32_t* slot_ids;   // expert parallel: the expert of every routed slot (else null), and the range held here
     int e_lo, e_hi;
+    const int32_t* e_map;      // or, instead of a range: for every expert its index among those held here, -1 if elsewhere
     float2* gu;        // [slots][ff]   (gate x, up x) per hidden element, written by GATE_UP
     float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by the quantizer of the hidden rows
     float* y;          // [T*K][n]      routed slots (down)
@@ -1024,6 +1048,46 @@ __global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ o
     }
 }
 
+// Expert-parallel prefill: this rank's part of the weighted sum, out[t] = sum over the token's
+// slots whose expert is held here (e_map[id] >= 0), in ascending expert id, of w * y; tokens with
+// no such slot get zeros (the rows are then summed over the ranks). One block per token.
+__global__ void __launch_bounds__(256) k_combine_partial(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
+                                                         const int32_t* __restrict__ ids, const int32_t* __restrict__ e_map, int n, int K) {
+    __shared__ int s_slot[32];
+    __shared__ float s_w[32];
+    __shared__ int s_cnt;
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) s_cnt = 0;
+    __syncthreads();
+    if (int(threadIdx.x) < K) {
+        const int k = threadIdx.x, e = ids[size_t(t) * K + k];
+        if (e_map[e] >= 0) {
+            int rank = 0;   // among the token's local slots, by expert id (then by k)
+            for (int j = 0; j < K; ++j) {
+                const int ej = ids[size_t(t) * K + j];
+                if (e_map[ej] >= 0 && (ej < e || (ej == e && j < k))) ++rank;
+            }
+            s_slot[rank] = t * K + k;
+            s_w[rank] = wts[size_t(t) * K + k];
+            atomicAdd(&s_cnt, 1);
+        }
+    }
+    __syncthreads();
+    const int cnt = s_cnt;
+    for (int i = threadIdx.x * 4; i < n; i += 256 * 4) {
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int r = 0; r < cnt; ++r) {
+            const float w = s_w[r];
+            const float4 v = *reinterpret_cast<const float4*>(y + size_t(s_slot[r]) * n + i);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+        }
+        *reinterpret_cast<float4*>(out + size_t(t) * n + i) = acc;
+    }
+}
+
 // k_moe_combine / k_stream_combine semantics: k order, as the hit list gives it
 __global__ void __launch_bounds__(256) k_combine_hits(float* __restrict__ out, const float* __restrict__ yh,
                                                       const float* __restrict__ w, const int32_t* __restrict__ hit_n,
@@ -1238,7 +1302,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -1779,23 +1843,16 @@ PfLayout pf_layout(int T, int K, int n, int ff, int E) {
     L.total = off;
     return L;
 }
-}  // namespace
-
-size_t frx_moe_prefill_stream_workspace_bytes(int T, int K, int n, int ff, int E) {
-    if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK || E < 1) return 0;
-    return pf_layout(T, K, n, ff, E).total;
-}
-
-int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
-                           float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
-    return frx_moe_prefill_stream_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
-}
-
-int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
-                              void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
-    if (!experts || !x || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
+// The streaming form of the prefill-sized product. With e_map (expert parallel) `experts` holds the
+// E experts of this rank and slots of other experts are skipped; with xq / xd the activations
+// arrive already quantized (natural order) and x is not read.
+int prefill_stream_impl(const void* experts, size_t stride, int E, const int32_t* e_map, int E_all, int n, int ff, const float* x,
+                        const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, void* yd, void* ws, size_t ws_bytes,
+                        cudaStream_t stream, int block64, int yd_bf16) {
+    if (!experts || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
     if (int rc = check_moe_shape("frx_moe_prefill", n, ff, K)) return rc;
-    if (T < 0 || E < 1 || E > 4096 || size_t(T) * K > (size_t(1) << 30)) return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, E %d", T, E);
+    if (T < 0 || E < 1 || E > 4096 || E_all < E || E_all > 4096 || size_t(T) * K > (size_t(1) << 30))
+        return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, E %d (of %d)", T, E, E_all);
     if ((uintptr_t(experts) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_prefill: experts and stride must be 16-byte aligned, ws 256-byte aligned");
     if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_prefill: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
@@ -1813,10 +1870,16 @@ int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, 
     int32_t* perm = reinterpret_cast<int32_t*>(base + L.perm);
     Item* items = reinterpret_cast<Item*>(base + L.items);
     const int S = T * K;
-    launch_quant_x(x, T, n, act_x(base, L), stream, block64);
-    FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
+    const ActBufs xb = act_x(base, L);
+    if (xq) {
+        const size_t nblk = size_t(T) * (n / kQ8);
+        FRX_LAUNCH(kKQuant, stream, k_q8_to_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xq, xd, n, nblk, xb.q, xb.a, xb.c));
+    } else {
+        launch_quant_x(x, T, n, xb, stream, block64);
+    }
+    FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status, e_map, E_all));
     FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, L.max_items));
-    FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
+    FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm, e_map, E_all));
     FRX_LAUNCH(kKGroup, stream, k_pf_items<<<(L.max_items + 255) / 256, 256, 0, stream>>>(bounds, item_off, E, perm, static_cast<const uint8_t*>(experts), stride,
                                                              status, items));
     StreamParams p{};
@@ -1832,7 +1895,46 @@ int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, 
     p.ff = ff;
     p.K = K;
     p.TK = S;
-    launch_ffn(p, act_x(base, L), act_h(base, L), size_t(S), cfg, stream);
+    if (e_map) {   // the hidden-row quantizer skips the rows of slots held elsewhere
+        p.slot_ids = ids;
+        p.e_map = e_map;
+    }
+    launch_ffn(p, xb, act_h(base, L), size_t(S), cfg, stream);
+    FRX_CUDA(cudaGetLastError());
+    return FRX_OK;
+}
+
+}  // namespace
+
+size_t frx_moe_prefill_stream_workspace_bytes(int T, int K, int n, int ff, int E) {
+    if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK || E < 1) return 0;
+    return pf_layout(T, K, n, ff, E).total;
+}
+
+int frx_moe_prefill_stream(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                           float* yd, void* ws, size_t ws_bytes, frx_stream_t stream) {
+    return frx_moe_prefill_stream_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+}
+
+int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                              void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
+    if (!x) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
+    return prefill_stream_impl(experts, stride, E, nullptr, E, n, ff, x, nullptr, nullptr, ids, T, K, yd, ws, ws_bytes, stream, block64, yd_bf16);
+}
+
+int frx_moe_prefill_stream_q8_ep(const void* experts_local, size_t stride, int E_local, const int32_t* e_map, int E_all, int n, int ff,
+                                 const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, float* yd, void* ws, size_t ws_bytes,
+                                 frx_stream_t stream) {
+    if (!xq || !xd || !e_map) return fail(FRX_ERR_ARG, "frx_moe_prefill_q8_ep: null pointer");
+    return prefill_stream_impl(experts_local, stride, E_local, e_map, E_all, n, ff, nullptr, xq, xd, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+}
+
+int frx_moe_combine_partial(float* out, const float* yd, const float* wts, const int32_t* ids, const int32_t* e_map, int n, int K, int T,
+                            frx_stream_t stream) {
+    if (!out || !yd || !wts || !ids || !e_map) return fail(FRX_ERR_ARG, "frx_moe_combine_partial: null pointer");
+    if (n < 4 || n % 4 || K < 1 || K > 32 || T < 0) return fail(FRX_ERR_SHAPE, "frx_moe_combine_partial: n %d, K %d, T %d", n, K, T);
+    if (T == 0) return FRX_OK;
+    FRX_LAUNCH(kKCombine, stream, k_combine_partial<<<unsigned(T), 256, 0, stream>>>(out, yd, wts, ids, e_map, n, K));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }

@@ -396,11 +396,7 @@ __global__ void __launch_bounds__(256) k_q8_0_to_q2_0(const uint8_t* __restrict_
     }
     uint8_t* o = dst + b * 18;
     if (lane < 16) o[2 + lane] = uint8_t(byte);
-    if (lane == 0) {
-        const uint16_t dh = __half_as_ushort(__float2half_rn(best_d));
-        o[0] = uint8_t(dh & 0xff);
-        o[1] = uint8_t(dh >> 8);
-    }
+    if (lane == 0) *reinterpret_cast<__half*>(o) = __float2half_rn(best_d);   // blocks are 18 bytes: the scale is 2-byte aligned
 }
 
 // ---- grouped plan in a workspace

@@ -9,9 +9,21 @@ constexpr int kCookie = 0x46525831;   // marks a workspace whose status words ha
 // Slots are cut into chunks of 1024.
 constexpr int kChunkSlots = 1024;
 
+// Expert parallel: with `e_map` (one entry per expert of the whole layer, E_all of them), ids name
+// experts of the whole layer, e_map[id] is the index of the expert among those held here or -1, and
+// slots of experts held elsewhere take no part; E is then the number of experts held here.
+__device__ __forceinline__ int local_expert(int id, int E, const int32_t* __restrict__ e_map, int E_all, bool& bad) {
+    if (!e_map) {
+        bad = id < 0 || id >= E;
+        return bad ? -1 : id;
+    }
+    bad = id < 0 || id >= E_all;
+    return bad ? -1 : e_map[id];
+}
+
 // per chunk: how many of its slots go to each expert
 __global__ void __launch_bounds__(256) k_pf_hist(const int32_t* __restrict__ ids, int S, int E, int* __restrict__ chunk_cnt,
-                                                 int* __restrict__ status) {
+                                                 int* __restrict__ status, const int32_t* __restrict__ e_map = nullptr, int E_all = 0) {
     extern __shared__ int hist[];
     if (blockIdx.x == 0 && threadIdx.x == 0 && status[3] != kCookie) {
         status[0] = kDevOk;
@@ -22,11 +34,12 @@ __global__ void __launch_bounds__(256) k_pf_hist(const int32_t* __restrict__ ids
     __syncthreads();
     const int s0 = blockIdx.x * kChunkSlots;
     for (int s = s0 + threadIdx.x; s < min(S, s0 + kChunkSlots); s += blockDim.x) {
-        const int e = ids[s];
-        if (e < 0 || e >= E) {
+        bool bad;
+        const int e = local_expert(ids[s], E, e_map, E_all, bad);
+        if (bad) {
             status[0] = kDevBadExpertId;
             status[2] = s;
-        } else {
+        } else if (e >= 0) {
             atomicAdd(&hist[e], 1);   // integer counts: exact whatever the order
         }
     }
@@ -85,14 +98,16 @@ __global__ void __launch_bounds__(1024) k_pf_scan(int* __restrict__ chunk_cnt, i
 
 // per chunk, one warp: every slot's position in the grouped order (by expert, then slot order)
 __global__ void __launch_bounds__(32) k_pf_place(const int32_t* __restrict__ ids, int S, int E, const int* __restrict__ chunk_off,
-                                                 const int* __restrict__ bounds, int32_t* __restrict__ perm) {
+                                                 const int* __restrict__ bounds, int32_t* __restrict__ perm,
+                                                 const int32_t* __restrict__ e_map = nullptr, int E_all = 0) {
     extern __shared__ int cursor[];
     const int lane = threadIdx.x, c = blockIdx.x;
     for (int e = lane; e < E; e += 32) cursor[e] = bounds[e] + chunk_off[size_t(c) * E + e];
     __syncwarp();
     for (int it = 0; it < kChunkSlots / 32; ++it) {
         const int s = c * kChunkSlots + it * 32 + lane;
-        const int e = s < S ? ids[s] : -1;
+        bool bad = false;
+        const int e = s < S ? local_expert(ids[s], E, e_map, E_all, bad) : -1;
         const bool ok = e >= 0 && e < E;
         const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
         const int rank = __popc(peers & ((1u << lane) - 1));

@@ -636,12 +636,19 @@ int set_pf_attr() {
 
 using namespace frx;
 
+// The tensor-memory form pays per 128-row x 64-weight step whatever the number of tokens in the tile,
+// so it is taken only when experts get many tokens on average.
+constexpr int kUmmaMinTokensPerExpert = 256;
+
 extern "C" {
 
 // the streaming form lives in frx_decode.cu
 size_t frx_moe_prefill_stream_workspace_bytes(int T, int K, int n, int ff, int E);
 int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
                               void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
+int frx_moe_prefill_stream_q8_ep(const void* experts_local, size_t stride, int E_local, const int32_t* e_map, int E_all, int n, int ff,
+                                 const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, float* yd, void* ws, size_t ws_bytes,
+                                 frx_stream_t stream);
 
 size_t frx_moe_prefill_umma_workspace_bytes(int T, int K, int n, int ff, int E) {
     if (T < 1 || K < 1 || n < kUnitK || ff < kUnitK || E < 1) return 0;
@@ -653,12 +660,13 @@ int frx_moe_prefill_umma(const void* experts, size_t stride, int E, int n, int f
     return frx_moe_prefill_umma_ex(experts, stride, E, n, ff, x, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
 }
 
-int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
-                            void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
-    if (!experts || !x || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
+static int prefill_umma_impl(const void* experts, size_t stride, int E, const int32_t* e_map, int E_all, int n, int ff, const float* x,
+                             const int8_t* xq_in, const float* xd_in, const int32_t* ids, int T, int K, void* yd, void* ws, size_t ws_bytes,
+                             frx_stream_t stream, int block64, int yd_bf16) {
+    if (!experts || !ids || !yd || !ws) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
     if (n < kUnitK || ff < kUnitK || n % kUnitK || ff % kUnitK || n > 8192 || ff > 8192)
         return fail(FRX_ERR_SHAPE, "frx_moe_prefill: n %d and ff %d must be multiples of %d, at most 8192", n, ff, kUnitK);
-    if (K < 1 || K > 32 || T < 0 || E < 1 || E > 4096 || size_t(T) * K > (size_t(1) << 28))
+    if (K < 1 || K > 32 || T < 0 || E < 1 || E > 4096 || E_all < E || E_all > 4096 || size_t(T) * K > (size_t(1) << 28))
         return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, K %d, E %d", T, K, E);
     if ((uintptr_t(experts) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_prefill: experts and stride must be 16-byte aligned, ws 256-byte aligned");
@@ -680,14 +688,16 @@ int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, in
     int* tb_p0 = reinterpret_cast<int*>(base + L.tb_p0);
     int* tb_n = reinterpret_cast<int*>(base + L.tb_n);
     int32_t* pslot = reinterpret_cast<int32_t*>(base + L.pslot);
-    int8_t* xq = reinterpret_cast<int8_t*>(base + L.xq);
-    float* xd = reinterpret_cast<float*>(base + L.xd);
+    const int8_t* xq = xq_in ? xq_in : reinterpret_cast<const int8_t*>(base + L.xq);
+    const float* xd = xd_in ? xd_in : reinterpret_cast<const float*>(base + L.xd);
     const int S = T * K;
     const size_t nblk = size_t(T) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_pfu_quant_x<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, xq, xd, block64));
-    FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status));
+    if (!xq_in)   // else the activations arrived already quantized
+        FRX_LAUNCH(kKQuant, stream, k_pfu_quant_x<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, reinterpret_cast<int8_t*>(base + L.xq),
+                                                                                   reinterpret_cast<float*>(base + L.xd), block64));
+    FRX_LAUNCH(kKGroup, stream, k_pf_hist<<<L.n_chunks, 256, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, status, e_map, E_all));
     FRX_LAUNCH(kKGroup, stream, k_pf_scan<<<1, 1024, 0, stream>>>(chunk_cnt, L.n_chunks, E, bounds, item_off, status, 1 << 30));
-    FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm));
+    FRX_LAUNCH(kKGroup, stream, k_pf_place<<<L.n_chunks, 32, size_t(E) * 4, stream>>>(ids, S, E, chunk_cnt, bounds, perm, e_map, E_all));
     FRX_LAUNCH(kKGroup, stream, k_pfu_plan<<<1, 1024, 0, stream>>>(bounds, E, pb, tbo, meta, tb_e, tb_p0, tb_n, L.max_tb, status));
     FRX_LAUNCH(kKGroup, stream, k_pfu_gather<<<unsigned(L.pmax / 8), 256, 0, stream>>>(bounds, pb, E, perm, meta, K, n, L.pmax, xq, xd, base + L.xg,
                                                                                    reinterpret_cast<float*>(base + L.xa), pslot));
@@ -721,11 +731,29 @@ int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, in
     return FRX_OK;
 }
 
+int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T, int K,
+                            void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16) {
+    if (!x) return fail(FRX_ERR_ARG, "frx_moe_prefill: null pointer");
+    return prefill_umma_impl(experts, stride, E, nullptr, E, n, ff, x, nullptr, nullptr, ids, T, K, yd, ws, ws_bytes, stream, block64, yd_bf16);
+}
+
+// ---- expert-parallel prefill on activations that arrive quantized: this rank holds E_local
+// experts (e_map[id] = index here, or -1), the T tokens are all the tokens whose slots may land here
+int frx_moe_prefill_q8_ep(const void* experts_local, size_t stride, int E_local, const int32_t* e_map, int E_all, int n, int ff,
+                          const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, float* yd, void* ws, size_t ws_bytes,
+                          frx_stream_t stream, int form) {
+    if (!xq || !xd || !e_map) return fail(FRX_ERR_ARG, "frx_moe_prefill_q8_ep: null pointer");
+    if (form < 0 || form > 2) return fail(FRX_ERR_ARG, "frx_moe_prefill_q8_ep: form %d", form);
+    // the expected number of slots per local expert is T * K / E_all (the counts stay on the device)
+    const bool umma = form == 2 || (form == 0 && T > 0 && size_t(T) * K >= size_t(kUmmaMinTokensPerExpert) * size_t(E_all));
+    if (umma) return prefill_umma_impl(experts_local, stride, E_local, e_map, E_all, n, ff, nullptr, xq, xd, ids, T, K, yd, ws, ws_bytes, stream, 0, 0);
+    return frx_moe_prefill_stream_q8_ep(experts_local, stride, E_local, e_map, E_all, n, ff, xq, xd, ids, T, K, yd, ws, ws_bytes, stream);
+}
+
 // ---- the public entry. Both forms compute the same bits; the choice is by measured speed: the
 // tensor-memory form pays per 128-row x 64-weight step whatever the number of tokens in the tile,
 // so it is taken only when experts get many tokens on average (256 or more, where it is on a par
 // with or ahead of the streaming form on B200), and the streaming form otherwise.
-constexpr int kUmmaMinTokensPerExpert = 256;
 
 size_t frx_moe_prefill_workspace_bytes(int T, int K, int n, int ff, int E) {
     const size_t a = frx_moe_prefill_stream_workspace_bytes(T, K, n, ff, E), b = frx_moe_prefill_umma_workspace_bytes(T, K, n, ff, E);

@@ -133,53 +133,122 @@ def moe_layer_ep_fused(comm: EpComm, experts_local: int, stride: int, E: int, e_
     return out
 
 
-def moe_prefill_ep(experts_local: int, stride: int, E: int, n: int, ff: int, x: torch.Tensor, logits: torch.Tensor, K: int,
-                   group=None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Prefill-sized expert-parallel layer. Tokens are sharded over the ranks (x, logits are this
-    rank's tokens), experts too (this rank holds expert_range(rank, world, E), E divisible by the
-    world size). Each rank routes its tokens, sends every (token, expert) slot's activations to the
-    rank that holds the expert (all-to-all), runs the grouped expert product on what it received,
-    returns the results (all-to-all) and sums them with the routing weights.
+def expert_placement(counts, world: int) -> "np.ndarray":
+    """Owner rank of every expert, dealing the experts round-robin in order of popularity (counts:
+    tokens routed to each expert on some sample), so that the hot experts of a skewed router do not
+    all land on one rank. Ties keep the lower expert id first."""
+    import numpy as np
+    counts = np.asarray(counts)
+    order = np.lexsort((np.arange(counts.size), -counts))
+    owner = np.empty(counts.size, np.int32)
+    owner[order] = np.arange(counts.size, dtype=np.int32) % world
+    return owner
 
-    Returns (out [T_local][n], ids, wts). One host synchronisation (the split sizes), as the
-    reference's grouped path has one."""
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    rank = dist.get_rank(group) if dist.is_initialized() else 0
-    if E % world:
-        raise moe.FrxError(1, f"moe_prefill_ep: {E} experts do not divide over {world} ranks")
-    per = E // world
-    T = x.shape[0]
-    ids, wts = moe.moe_route_topk(logits, K)
-    flat = ids.reshape(-1).to(torch.int64)
-    dest = flat // per
-    order = torch.sort(dest, stable=True).indices                 # slots grouped by destination rank
-    send_counts = torch.bincount(dest, minlength=world)
-    recv_counts = torch.empty_like(send_counts)
-    if world > 1:
-        dist.all_to_all_single(recv_counts, send_counts, group=group)
-    else:
-        recv_counts.copy_(send_counts)
-    sc, rc = send_counts.tolist(), recv_counts.tolist()           # the one host synchronisation
-    tok = (order // K)
-    send_x = x.index_select(0, tok).contiguous()                  # [S][n]
-    send_e = (flat.index_select(0, order) - dest.index_select(0, order) * per).to(torch.int32).contiguous()
-    R = int(sum(rc))
-    recv_x = torch.empty(R, n, dtype=x.dtype, device=x.device)
-    recv_e = torch.empty(R, dtype=torch.int32, device=x.device)
-    if world > 1:
-        dist.all_to_all_single(recv_x, send_x, output_split_sizes=rc, input_split_sizes=sc, group=group)
-        dist.all_to_all_single(recv_e, send_e, output_split_sizes=rc, input_split_sizes=sc, group=group)
-    else:
-        recv_x, recv_e = send_x, send_e
-    y = torch.empty(R, n, dtype=torch.float32, device=x.device)
-    if R:
-        moe.moe_q2.run(experts_local, stride, per, n, ff, recv_x, recv_e.view(R, 1), yd=y)
-    back = torch.empty(T * K, n, dtype=torch.float32, device=x.device)
-    if world > 1:
-        dist.all_to_all_single(back, y, output_split_sizes=sc, input_split_sizes=rc, group=group)
-    else:
-        back = y
-    yd = torch.empty_like(back)
-    yd.index_copy_(0, order, back)                                # slot order t * K + k again
-    out = moe.moe_combine(yd.view(T, K, n), wts, None, None, None)
-    return out, ids, wts
+
+class PrefillEp:
+    """Expert-parallel prefill of one MoE layer: tokens and experts are both sharded over the ranks.
+
+    Every rank routes and quantizes its own tokens (int8 codes + one float scale per 32 values:
+    2,304 bytes per token instead of 8,192), the ranks all-gather the quantized tokens and the
+    routing, each rank runs the grouped expert products over all gathered tokens but only over the
+    slots whose expert it holds (frx_moe_prefill_q8_ep consumes the quantized form directly), forms
+    its part of every token's weighted sum, and a reduce-scatter of those rows gives every rank the
+    outputs of its own tokens. The tokens are cut into chunks, and the exchanges run on a second
+    stream, so a chunk's all-gather and the previous chunk's reduce-scatter overlap the expert
+    products of the chunk in between. Nothing waits for the host: counts stay on the device.
+
+    `owner` [E] gives the rank of every expert (default: contiguous ranges); this rank's experts lie
+    at experts_local + i * stride in ascending expert id. All ranks construct it with the same
+    arguments and call run() together."""
+
+    def __init__(self, experts_local: int, stride: int, E: int, n: int, ff: int, T_local: int, K: int, owner=None, chunks: int = 4,
+                 group=None, device=None, form: int = 0):
+        import numpy as np
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        dev = device or torch.device("cuda", torch.cuda.current_device())
+        if owner is None:
+            owner = np.empty(E, np.int32)
+            for r in range(self.world):
+                lo, hi = expert_range(r, self.world, E)
+                owner[lo:hi] = r
+        owner = np.asarray(owner, np.int32)
+        mine = np.nonzero(owner == self.rank)[0]
+        e_map = np.full(E, -1, np.int32)
+        e_map[mine] = np.arange(mine.size, dtype=np.int32)
+        self.e_map = torch.from_numpy(e_map).to(dev)
+        self.E_local = int(mine.size)
+        while chunks > 1 and T_local % chunks:
+            chunks -= 1
+        self.chunks, self.Tc = chunks, T_local // chunks
+        self.experts_local, self.stride, self.E, self.n, self.ff, self.T_local, self.K, self.form = experts_local, stride, E, n, ff, T_local, K, form
+        Tg = self.world * self.Tc
+        self.meta_w = n // 32 + 2 * K                     # per token: block scales, expert ids, routing weights (32-bit words)
+        self.xq_l = torch.empty(chunks, self.Tc, n, dtype=torch.int8, device=dev)
+        self.meta_l = torch.empty(chunks, self.Tc, self.meta_w, dtype=torch.int32, device=dev)
+        self.xq_g = torch.empty(chunks, Tg, n, dtype=torch.int8, device=dev)
+        self.meta_g = torch.empty(chunks, Tg, self.meta_w, dtype=torch.int32, device=dev)
+        self.yd = torch.empty(Tg * K, n, dtype=torch.float32, device=dev)
+        self.part = torch.empty(2, Tg, n, dtype=torch.float32, device=dev)
+        self.out = torch.empty(T_local, n, dtype=torch.float32, device=dev)
+        self.ws = moe.workspace(moe.moe_q2.workspace_bytes(Tg, K, n, ff, max(1, self.E_local)), dev)
+        self.comm = torch.cuda.Stream(device=dev)
+        self.ev_gathered = [torch.cuda.Event() for _ in range(chunks)]
+        self.ev_part = [torch.cuda.Event() for _ in range(chunks)]
+        self.ev_scattered = [torch.cuda.Event() for _ in range(chunks)]
+
+    def run(self, x: torch.Tensor, logits: torch.Tensor):
+        """x [T_local][n], logits [T_local][E] -> (out [T_local][n], ids, wts). out is reused by the next call."""
+        n, K, Tc, world = self.n, self.K, self.Tc, self.world
+        main = torch.cuda.current_stream()
+        ids, wts = moe.moe_route_topk(logits, K)
+        for c in range(self.chunks):
+            sl = slice(c * Tc, (c + 1) * Tc)
+            xd = torch.empty(Tc, n // 32, dtype=torch.float32, device=x.device)
+            check(lib.frx_quantize_q8(moe._stream(), moe._ptr(x[sl]), Tc, n, moe._ptr(self.xq_l[c]), moe._ptr(xd)))
+            m = self.meta_l[c]
+            m[:, :n // 32] = xd.view(torch.int32)
+            m[:, n // 32:n // 32 + K] = ids[sl]
+            m[:, n // 32 + K:] = wts[sl].view(torch.int32)
+            if world > 1:
+                self.comm.wait_stream(main)
+                with torch.cuda.stream(self.comm):
+                    dist.all_gather_into_tensor(self.xq_g[c].view(-1), self.xq_l[c].view(-1), group=self.group)
+                    dist.all_gather_into_tensor(self.meta_g[c].view(-1), self.meta_l[c].view(-1), group=self.group)
+                    self.ev_gathered[c].record(self.comm)
+            else:
+                self.xq_g[c].copy_(self.xq_l[c])
+                self.meta_g[c].copy_(self.meta_l[c])
+        Tg = world * Tc
+        wp, wb = moe._ws_ptr(self.ws)
+        for c in range(self.chunks):
+            if world > 1:
+                main.wait_event(self.ev_gathered[c])
+            mg = self.meta_g[c]
+            xd_g = mg[:, :n // 32].contiguous().view(torch.float32)
+            ids_g = mg[:, n // 32:n // 32 + K].contiguous()
+            wts_g = mg[:, n // 32 + K:].contiguous().view(torch.float32)
+            check(lib.frx_moe_prefill_q8_ep(C.c_void_p(self.experts_local), self.stride, self.E_local, moe._ptr(self.e_map), self.E, n, self.ff,
+                                            moe._ptr(self.xq_g[c]), moe._ptr(xd_g), moe._ptr(ids_g), Tg, K, moe._ptr(self.yd), wp, wb,
+                                            moe._stream(), self.form))
+            part = self.part[c % 2]
+            if c >= 2 and world > 1:
+                main.wait_event(self.ev_scattered[c - 2])     # the exchange that read this buffer has finished
+            check(lib.frx_moe_combine_partial(moe._ptr(part), moe._ptr(self.yd), moe._ptr(wts_g), moe._ptr(ids_g), moe._ptr(self.e_map), n, K,
+                                              Tg, moe._stream()))
+            dst = self.out[c * Tc:(c + 1) * Tc]
+            if world > 1:
+                self.ev_part[c].record(main)
+                with torch.cuda.stream(self.comm):
+                    self.comm.wait_event(self.ev_part[c])
+                    dist.reduce_scatter_tensor(dst.view(-1), part.view(-1), group=self.group)
+                    self.ev_scattered[c].record(self.comm)
+            else:
+                dst.copy_(part)
+        if world > 1:
+            main.wait_stream(self.comm)
+        return self.out, ids, wts
+
+    def status(self) -> None:
+        moe.workspace_status(self.ws)

@@ -99,6 +99,9 @@ SIGNATURES = {
     "frx_moe_prefill_umma_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
     "frx_moe_prefill_stream_ex": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i, _i]),
     "frx_chain_rmsnorm_unit": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "frx_moe_prefill_q8_ep": (_i, [_vp, _sz, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp, _i]),
+    "frx_moe_prefill_stream_q8_ep": (_i, [_vp, _sz, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "frx_moe_combine_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "frx_gemv_q8_1_bytes": (_sz, [_i64, _i]),
     "frx_gemv_row_bytes": (_i64, [C.c_uint32, _i64]),
     "frx_gemv_quantize_q8_1": (_i, [_vp, _i64, _i, _vp, _vp]),

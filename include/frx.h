@@ -360,6 +360,31 @@ int frx_moe_prefill_umma_ex(const void* experts, size_t stride, int E, int n, in
 int frx_moe_prefill_stream_ex(const void* experts, size_t stride, int E, int n, int ff, const float* x, const int32_t* ids, int T,
                               int K, void* yd, void* ws, size_t ws_bytes, frx_stream_t stream, int block64, int yd_bf16);
 
+/* ---- expert-parallel prefill (tokens and experts both sharded over the GPUs of a node; the
+ * reference runs on one GPU and has no counterpart; the nearest single-GPU structure is
+ * arch/qwen4exp/moe_stream.cu:152-177) ----
+ * Every rank quantizes its own tokens (frx_quantize_q8: 2,304 bytes per token instead of 8,192),
+ * the ranks exchange the quantized tokens and the routing (all-gather), each rank runs
+ * frx_moe_prefill_q8_ep over all T tokens but only over the slots whose expert it holds, forms its
+ * part of every token's weighted sum (frx_moe_combine_partial), and a reduce-scatter of those rows
+ * gives every rank the outputs of its own tokens. Nothing here waits for the stream.
+ * e_map [E_all] int32 (device): the index of every expert among the E_local held by this rank
+ * (experts_local + index * stride), or -1: any placement of experts on ranks, e.g. hot experts
+ * dealt round-robin. xq [T][n] int8 and xd [T][n/32] float as frx_quantize_q8 writes them; ids [T][K]
+ * name experts of the whole layer. yd [T*K][n]: rows of slots held elsewhere are not written.
+ * form: 0 by size, 1 streaming, 2 tensor-memory. Workspace: frx_moe_prefill_workspace_bytes(T, K, n, ff, E_local). */
+int frx_moe_prefill_q8_ep(const void* experts_local, size_t stride, int E_local, const int32_t* e_map, int E_all, int n, int ff,
+                          const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, float* yd, void* ws, size_t ws_bytes,
+                          frx_stream_t stream, int form);
+/* The streaming form of frx_moe_prefill_q8_ep on its own (form = 1). */
+int frx_moe_prefill_stream_q8_ep(const void* experts_local, size_t stride, int E_local, const int32_t* e_map, int E_all, int n, int ff,
+                                 const int8_t* xq, const float* xd, const int32_t* ids, int T, int K, float* yd, void* ws, size_t ws_bytes,
+                                 frx_stream_t stream);
+/* out[t] = sum over the token's slots whose expert is held here (e_map[id] >= 0), in ascending
+ * expert id, of wts * yd; zeros for tokens with no such slot. out [T][n]. */
+int frx_moe_combine_partial(float* out, const float* yd, const float* wts, const int32_t* ids, const int32_t* e_map, int n, int K, int T,
+                            frx_stream_t stream);
+
 /* The join between layers of the chained expert-stack benchmark (a 48-layer stack walked by a
  * window of three tokens): x_next[t] = r / sqrt(mean(r^2) + 1e-6), r = x[t] + y[t], an RMS norm
  * with unit weight. No counterpart in the reference, whose MoE layers are joined by its attention

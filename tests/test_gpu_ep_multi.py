@@ -58,7 +58,10 @@ def _worker(rank, world, port_no, ret):
     # prefill form: this rank's half of the tokens
     Tl = T // world
     xs, ls = x[rank * Tl:(rank + 1) * Tl], lg[rank * Tl:(rank + 1) * Tl]
-    o2, i2, w2 = ep.moe_prefill_ep(ex.base + lo * ex.stride, ex.stride, E, n, ff, cuda(xs), cuda(ls), K)
+    pipe = ep.PrefillEp(ex.base + lo * ex.stride, ex.stride, E, n, ff, Tl, K, chunks=2)
+    o2, i2, w2 = pipe.run(cuda(xs), cuda(ls))
+    torch.cuda.synchronize()
+    pipe.status()
     ref = port.moe_layer(ex.routed_planar(), ex.blob_bytes, None, n, ff, xs, ids[rank * Tl:(rank + 1) * Tl], wts[rank * Tl:(rank + 1) * Tl])
     err_prefill = rel_max(o2.cpu().numpy(), ref)
     ids_ok = bool(np.array_equal(i2.cpu().numpy(), ids[rank * Tl:(rank + 1) * Tl]))
