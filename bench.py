@@ -49,7 +49,7 @@ sys.path.insert(0, ROOT)
 N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
-NCU_GU_TRAFFIC_PER_BLOB = 224.33e6 / 367   # DRAM bytes per distinct expert blob of one gate/up launch (ncu, profiles/)
+NCU_GU_TRAFFIC_PER_BLOB = 223.0e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
 UNIT = "layer-tokens/s"

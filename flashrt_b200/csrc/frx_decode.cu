@@ -19,6 +19,7 @@ namespace {
 #include "frx_group.cuh"
 
 constexpr int kMaxChunkTokens = 64;   // tokens grouped by one k_group launch
+constexpr int kNarrowTok = 4;         // items of at most this many tokens take the narrow form of the inner product (units_mma_narrow)
 
 // One unit of expert work: a tiled expert blob and up to 8 (token, expert) slots routed to it.
 // A slot is a row of the hidden and output buffers: t * K + k for the k-th expert of token t,
@@ -49,7 +50,7 @@ Layout make_layout(int T, int K, int n, int ff) {
         off += align_up(bytes);
         return o;
     };
-    L.max_items = Tc * K + (Tc + kTokPerItem - 1) / kTokPerItem;
+    L.max_items = Tc * K + (Tc + kNarrowTok - 1) / kNarrowTok;   // every routed slot its own item at worst; the shared expert in items of four tokens
     L.status = take(64);
     L.items = take(size_t(L.max_items) * sizeof(Item));
     L.order = take(size_t(Tc) * K * 4);
@@ -141,13 +142,23 @@ __device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, in
 __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
                                                       int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c,
                                                       const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi,
-                                                      int block64, const int32_t* __restrict__ e_map) {
+                                                      int block64, const int32_t* __restrict__ e_map,
+                                                      const int32_t* __restrict__ row_list, const int* __restrict__ row_count, int store_h) {
     pdl_wait();
     pdl_trigger();
-    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
-    const size_t blk = quad >> 3;
+    size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
+    size_t blk = quad >> 3;
     bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
-    if (live && slot_ids) {
+    if (row_list) {
+        // only the listed rows (the slots a grouping placed, in grouped order) are visited: the i-th
+        // row of blocks belongs to row row_list[i]; beyond row_count there is nothing to do
+        const size_t bpr = size_t(k / kQ8), i = blk / bpr;
+        live = live && i < size_t(*row_count);
+        if (live) {
+            blk = size_t(row_list[i]) * bpr + blk % bpr;
+            quad = blk * 8 + (quad & 7);
+        }
+    } else if (live && slot_ids) {
         const size_t r = blk / size_t(k / kQ8);
         if (r < size_t(routed_rows)) {
             const int e = slot_ids[r];
@@ -163,7 +174,7 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
         hv[1] = swiglu_ref(g0.z, g0.w);
         hv[2] = swiglu_ref(g1.x, g1.y);
         hv[3] = swiglu_ref(g1.z, g1.w);
-        *reinterpret_cast<float4*>(h + quad * 4) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+        if (store_h) *reinterpret_cast<float4*>(h + quad * 4) = make_float4(hv[0], hv[1], hv[2], hv[3]);
     }
     // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16
     float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
@@ -230,10 +241,13 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
 // reference's CPU path adds them, quant/q2_0/moe_cpu.cpp:70-79). One block of 1024 threads, no
 // atomics on data: the result does not depend on thread timing.
 // dyn: dynamic shared memory of E * 8 + T * K * 4 bytes.
+// tpi: tokens per item, 8 (the width of the MMA) or 4: with four every item takes the narrow form
+// of the inner product, so all items cost the same and the even split of tasks over the SMs is an
+// even split of time (an expert with more tokens is then read once from HBM and again from the L2).
 __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32_t* __restrict__ ids, int T, int K, int E, int e_lo,
                                             int e_hi, const uint8_t* __restrict__ experts, size_t stride,
                                             const uint8_t* __restrict__ shared, Item* __restrict__ items, int* __restrict__ status,
-                                            int32_t* __restrict__ order, int max_items) {
+                                            int32_t* __restrict__ order, int max_items, int tpi) {
     unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K]
     __shared__ int warp_tot[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -258,7 +272,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     __syncthreads();
     const int per = (E + 1023) / 1024, e0 = tid * per, e1 = min(E, e0 + per);
     int cnt = 0;
-    for (int e = e0; e < e1; ++e) cnt += (__popcll(mask[e]) + kTokPerItem - 1) / kTokPerItem;
+    for (int e = e0; e < e1; ++e) cnt += (__popcll(mask[e]) + tpi - 1) / tpi;
     int inc = cnt;   // inclusive scan over the block: within the warp, then over the warp totals
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -279,7 +293,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     __syncthreads();
     int at = inc - cnt + (warp ? warp_tot[warp - 1] : 0);
     const int routed_items = warp_tot[31];
-    const int shared_items = shared ? (T + kTokPerItem - 1) / kTokPerItem : 0;
+    const int shared_items = shared ? (T + tpi - 1) / tpi : 0;
     if (routed_items + shared_items > max_items) {
         if (tid == 0) {
             status[0] = kDevTooManyItems;
@@ -294,7 +308,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
             it.blob = experts + size_t(e - e_lo) * stride;
             it.expert = e;
             int m = 0;
-            while (bits && m < kTokPerItem) {
+            while (bits && m < tpi) {
                 const int t = __ffsll((long long)bits) - 1;
                 bits &= bits - 1;
                 int k = 0;
@@ -311,7 +325,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         Item it;
         it.blob = shared;
         it.expert = -1;
-        const int t0 = tid * kTokPerItem, m = min(kTokPerItem, T - t0);
+        const int t0 = tid * tpi, m = min(tpi, T - t0);
         it.n_tok = m;
         for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? T * K + t0 + j : 0;
         items[routed_items + tid] = it;
@@ -342,7 +356,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
                                                    size_t stride, const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                    int* __restrict__ status, int32_t* __restrict__ order, int max_items,
                                                    const float* __restrict__ x, int n, size_t n_blocks, int8_t* __restrict__ xq,
-                                                   float* __restrict__ xa, float* __restrict__ xc) {
+                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi) {
     extern __shared__ unsigned long long dyn[];
     pdl_wait();
     pdl_trigger();
@@ -358,7 +372,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
             route_warp<V>(logits + size_t(t) * E, E, K, lane, ids + size_t(t) * K, wts + size_t(t) * K, nullptr, nullptr);
     }
     cluster_sync_all();   // every block's ids are visible to block 0
-    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items);
+    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -387,6 +401,8 @@ struct StreamParams {
     const float* ac;
     const int32_t* slot_ids;   // expert parallel: the expert of every routed slot (else null), and the range held here
     int e_lo, e_hi;
+    const int32_t* row_list;   // the hidden-row quantizer visits only these rows, *row_count of them (prefill: the grouped slots)
+    const int* row_count;
     const int32_t* e_map;      // or, instead of a range: for every expert its index among those held here, -1 if elsewhere
     float2* gu;        // [slots][ff]   (gate x, up x) per hidden element, written by GATE_UP
     float* h;          // [slots][ff]   the hidden values silu(gate x) * up x, written by the quantizer of the hidden rows
@@ -512,7 +528,6 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uin
 // additions per (row, token) are those of units_mma: the results are the same bits.
 // The item buffer must have been built for the narrow form (see build in k_stream): zeros in token
 // columns 4..7 of the B fragments, scale and bias entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1.
-constexpr int kNarrowTok = 4;
 template <int UPC>
 __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
                                                  const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
@@ -673,21 +688,24 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     const int nseg = last_item - first_item + 1;
     const int ctid = threadIdx.x;
 
-    auto build = [&](int q) {
+    // btid / bthreads: this thread's index among the threads that share the build, and their number
+    // (the whole block in the steady state; half of it each for the first two items, which are
+    // built side by side so that their global-memory round trips overlap)
+    auto build = [&](int q, int btid, int bthreads) {
         const Item* it = p.items + first_item + q;
         const int buf = q % nbuf;
         uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.bfrag + buf * (nb * 512));
         float* daw = reinterpret_cast<float*>(smem + sp.da + buf * (nb * 64));
         float* ciw = reinterpret_cast<float*>(smem + sp.ci + buf * (nb * 128));
-        if (ctid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[ctid] = reinterpret_cast<const uint32_t*>(it)[ctid];
+        if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
         const int m = it->n_tok;
         const bool narrow = m <= kNarrowTok && p.narrow;   // see units_mma_narrow
         // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
-        constexpr int NT = NW * 32;
+        const int NT = bthreads;
         const int vpr = nb * 4;   // 16-byte vectors per row
         if (narrow)   // token columns 4..7 of every block hold zeros
-            for (int idx = ctid; idx < nb * 16; idx += NT) reinterpret_cast<uint4*>(bw)[(idx >> 4) * 32 + 16 + (idx & 15)] = make_uint4(0u, 0u, 0u, 0u);
-        for (int base = ctid; base < m * vpr; base += 4 * NT) {
+            for (int idx = btid; idx < nb * 16; idx += NT) reinterpret_cast<uint4*>(bw)[(idx >> 4) * 32 + 16 + (idx & 15)] = make_uint4(0u, 0u, 0u, 0u);
+        for (int base = btid; base < m * vpr; base += 4 * NT) {
             uint4 v[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -708,7 +726,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
                 }
             }
         }
-        for (int idx = ctid; idx < m * nb * 2; idx += NT) {
+        for (int idx = btid; idx < m * nb * 2; idx += NT) {
             const int g = idx / (nb * 2), r = idx % (nb * 2), b = r >> 1, s = r & 1;
             const int slot = it->slot[g];
             const size_t row = GATE_UP ? size_t(slot_token(slot, p.K, p.TK)) : size_t(slot);
@@ -753,10 +771,20 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     };
     const int ahead = nbuf - 1;
     if (!GATE_UP) pdl_wait();   // the first weight chunks are already in flight
-    for (int q = 0; q < ahead && q < nseg; ++q) {
-        build(q);
+    if (ahead == 2 && nseg >= 2) {   // the first two items side by side: one half of the warps each
+        constexpr int H = NW / 2;
+        build(warp < H ? 0 : 1, warp < H ? ctid : ctid - H * 32, warp < H ? H * 32 : (NW - H) * 32);
         __syncwarp();
-        if (lane == 0) mbar_arrive(ready + q % nbuf);
+        if (lane == 0) {   // every warp arrives at both barriers; they complete when the builders have
+            mbar_arrive(ready + 0);
+            mbar_arrive(ready + 1);
+        }
+    } else {
+        for (int q = 0; q < ahead && q < nseg; ++q) {
+            build(q, ctid, NW * 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready + q % nbuf);
+        }
     }
     for (int q = 0; q < nseg; ++q) {
         const int item = first_item + q, buf = q % nbuf;
@@ -858,7 +886,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         if (q + ahead < nseg) {
             const int nxt = (q + ahead) % nbuf;   // the buffer of item q - 1
             if (q >= 1) mbar_wait_bounded(done + nxt, uint32_t((q - 1) / nbuf) & 1u, abort, p.wait_ns);
-            build(q + ahead);
+            build(q + ahead, ctid, NW * 32);
             __syncwarp();
             if (lane == 0) mbar_arrive(ready + nxt);
         }
@@ -1302,7 +1330,7 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.ac = xb.c;
     FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map, p.row_list, p.row_count, p.row_list ? 0 : 1));
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -1365,7 +1393,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
             return launch_pdl_cluster(kernel, dim3(kHeadCluster + qblocks), dim3(1024), dyn, stream, kHeadCluster, logits ? logits + size_t(t0) * E : (const float*)nullptr,
                               ids + size_t(t0) * K, wts + size_t(t0) * K, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
                               static_cast<const uint8_t*>(shared), items, status, order, L.max_items, x + size_t(t0) * n, n, nblk, xb.q, xb.a,
-                              xb.c);
+                              xb.c, g_narrow ? kNarrowTok : kTokPerItem);
         };
         if (!logits)
             FRX_LAUNCH(kKPrologue, stream, head(k_prologue<0>));
@@ -1895,10 +1923,10 @@ int prefill_stream_impl(const void* experts, size_t stride, int E, const int32_t
     p.ff = ff;
     p.K = K;
     p.TK = S;
-    if (e_map) {   // the hidden-row quantizer skips the rows of slots held elsewhere
-        p.slot_ids = ids;
-        p.e_map = e_map;
-    }
+    // the hidden-row quantizer walks the grouped slots (with an expert map: only those held here)
+    // and does not keep the float hidden values, which nothing reads at these sizes
+    p.row_list = perm;
+    p.row_count = bounds + E;
     launch_ffn(p, xb, act_h(base, L), size_t(S), cfg, stream);
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;

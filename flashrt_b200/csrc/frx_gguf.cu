@@ -1,5 +1,7 @@
 // GGUF reader (format versions 2 and 3, single file) and the Q2_0 expert loader that fills the
-// device arena from it. Written from the published description of the container format: a header
+// device arena from it. The reader follows the reference's own (core/gguf.cpp:17-120: the same walk
+// over header, key/value pairs and tensor directory, here over an in-memory buffer with bounds
+// flags instead of a FILE* with exceptions) and the published description of the container: a header
 // (magic "GGUF", version, tensor count, key/value count), typed key/value pairs, a tensor
 // directory (name, dimensions with the fastest first, ggml type id, offset into the data section)
 // and the data section, which starts at the next multiple of general.alignment (32 by default).
