@@ -240,6 +240,8 @@ def run_frx(args):
         moe.check(moe.lib.frx_debug_set_consumer_warps(args.nw))
     if args.narrow is not None:
         moe.check(moe.lib.frx_debug_set_narrow_items(args.narrow))
+    if args.task4 is not None:
+        moe.check(moe.lib.frx_debug_set_four_group_tasks(args.task4))
     if args.gu_chunks:
         moe.check(moe.lib.frx_debug_set_gate_up_chunks(args.gu_chunks))
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
@@ -935,6 +937,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the decode_batches, prefill and verify_stack keys")
     ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16, 20)")
+    ap.add_argument("--task4", type=int, default=None, help="tuning: 0 keeps two row groups per task in the decode layer")
     ap.add_argument("--gu-chunks", type=int, default=0, help="tuning: K slices per gate/up task")
     ap.add_argument("--narrow", type=int, default=None, help="tuning: 0 sends every work item through the eight-token form")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"], help="decode = configs[1] (default), prefill = configs[2]")

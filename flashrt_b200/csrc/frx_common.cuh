@@ -258,6 +258,22 @@ __device__ __forceinline__ void mma_u8s8_chain2(uint64_t& lo, uint64_t& hi, uint
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c0), "r"(c1));
 }
 
+// Four MMAs chained into one accumulator (see mma_u8s8_chain2): D = sum_j A_j * B_j + C.
+__device__ __forceinline__ void mma_u8s8_chain4(uint64_t& lo, uint64_t& hi, const uint32_t (&a)[16], const uint32_t (&b)[8], int c0, int c1) {
+    asm volatile(
+        "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%18,%19}, {%26,%27,%26,%27};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%6,%7,%8,%9}, {%20,%21}, {d0,d1,d2,d3};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%10,%11,%12,%13}, {%22,%23}, {d0,d1,d2,d3};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%14,%15,%16,%17}, {%24,%25}, {d0,d1,d2,d3};\n\t"
+        "mov.b64 %0, {d0,d1};\n\t"
+        "mov.b64 %1, {d2,d3};\n\t}"
+        : "=l"(lo), "=l"(hi)
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]), "r"(a[10]), "r"(a[11]),
+          "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
+          "r"(c0), "r"(c1));
+}
+
 __device__ __forceinline__ void mma_u8s8_bias(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1, int c) {
     asm volatile(

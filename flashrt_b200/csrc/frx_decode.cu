@@ -573,9 +573,134 @@ __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ uni
     }
 }
 
+// Four row groups at once for items of one or two tokens: the B operand of group j carries the
+// tokens in columns 2j, 2j + 1 and zeros elsewhere, the four MMAs accumulate into one D, and lane
+// (g, t4) finishes group t4: a quarter of the float work of units_mma per row, all of it live.
+// `units` points at the first unit of group 0 of the chunk, group j follows at j * gstride. The item
+// buffer is in the narrow form (zeros in token column 4; scale and bias entries of tokens 0, 1 at
+// the quad of lanes t4 = 0). Same products, same scaling, same order of additions per (row, token).
+template <int UPC>
+__device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
+                                             const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
+                                             int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
+    const uint8_t* codes = units + lane * 16;
+    const uint8_t* scales = units + t4 * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
+    const uint4* bf_p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bf_p[j] = bfrag + b0 * 32 + ((g >> 1) == j ? (g & 1) : 4) * 4 + t4;   // column 4: zeros
+    const int4* ci_p = ci + b0 * 8;
+    const ulonglong2* da_p = da + b0 * 4;
+    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
+    const int n_units = UPC ? UPC : count;
+#pragma unroll(1)
+    for (int u = 0; u < n_units; ++u) {
+        uint4 c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4*>(codes + j * gstride + u * kUnitBytes);
+        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+            const int b = 2 * u + jj;
+            const int4 cq = ci_p[b * 8];
+            const ulonglong2 a = da_p[b * 4];
+            uint32_t a0[16], a1[16], bb0[8], bb1[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 bf = bf_p[j][b * 32];
+                bb0[2 * j] = bf.x;
+                bb0[2 * j + 1] = bf.y;
+                bb1[2 * j] = bf.z;
+                bb1[2 * j + 1] = bf.w;
+                const uint32_t w0 = jj ? c[j].y : c[j].x, w1 = jj ? c[j].w : c[j].z;
+                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
+                a0[4 * j] = w0 & M0;
+                a0[4 * j + 1] = w1 & M0;
+                a0[4 * j + 2] = v0 & M0;
+                a0[4 * j + 3] = v1 & M0;
+                a1[4 * j] = w0 & M1;
+                a1[4 * j + 1] = w1 & M1;
+                a1[4 * j + 2] = v0 & M1;
+                a1[4 * j + 3] = v1 & M1;
+            }
+            uint64_t lo0, hi0, lo1, hi1;
+            mma_u8s8_chain4(lo0, hi0, a0, bb0, cq.x, cq.y);
+            mma_u8s8_chain4(lo1, hi1, a1, bb1, cq.z, cq.w);
+            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
+            const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
+            const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
+            const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
+            const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+            float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
+            unpack2(sumi_lo, s0, s1);
+            unpack2(sumi_hi, s2, s3);
+            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
+            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+        }
+    }
+}
+
+// Four row groups as two pairs in the narrow form (items of three or four tokens): the activation
+// fragments, scales and biases of a block are loaded once and serve both pairs.
+template <int UPC>
+__device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
+                                               const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
+                                               int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
+    const uint8_t* codes = units + lane * 16;
+    const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // pair 0; pair 1 two groups on
+    const uint4* bf0_p = bfrag + b0 * 32 + g * 4 + t4;
+    const uint4* bf1_p = bfrag + b0 * 32 + ((g + 4) & 7) * 4 + t4;
+    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
+    const ulonglong2* da_p = da + b0 * 4 + t4;
+    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
+    const int n_units = UPC ? UPC : count;
+#pragma unroll(1)
+    for (int u = 0; u < n_units; ++u) {
+        uint4 c[4];
+        uint2 sc[2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4*>(codes + j * gstride + u * kUnitBytes);
+#pragma unroll
+        for (int pi = 0; pi < 2; ++pi) sc[pi] = *reinterpret_cast<const uint2*>(scales + 2 * pi * gstride + u * kUnitBytes);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+            const int b = 2 * u + jj;
+            const uint4 bfa = bf0_p[b * 32], bfb = bf1_p[b * 32];
+            const int4 cq = ci_p[b * 8];
+            const ulonglong2 a = da_p[b * 4];
+#pragma unroll
+            for (int pi = 0; pi < 2; ++pi) {
+                const uint4 c0 = c[2 * pi], c1 = c[2 * pi + 1];
+                const uint32_t w0 = jj ? c0.y : c0.x, w1 = jj ? c0.w : c0.z;
+                const uint32_t x0 = jj ? c1.y : c1.x, x1 = jj ? c1.w : c1.z;
+                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
+                uint64_t lo0, hi0, lo1, hi1;
+                mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq.x, cq.y);
+                mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq.z, cq.w);
+                const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[pi].x), s_hi = *reinterpret_cast<const __half2*>(&sc[pi].y);
+                const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
+                const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
+                const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
+                const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+                float s0, s1, s2, s3;
+                unpack2(sumi_lo, s0, s1);
+                unpack2(sumi_hi, s2, s3);
+                acc_lo[pi] = add2(acc_lo[pi], pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
+                acc_hi[pi] = add2(acc_hi[pi], pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+            }
+        }
+    }
+}
+
 // UPC: units per units_mma call when known at compile time (gate/up: units per chunk; down: units
 // per group), else 0.
-template <bool GATE_UP, int NW, int UPC>
+// TASK4 (decode, where grouping cuts items at four tokens): a task is four groups walked once over
+// K, a chunk the same K range of all four (four bulk copies on one barrier); items of one or two
+// tokens take units_mma_n2, items of three or four units_mma_n4x2.
+template <bool GATE_UP, int NW, int UPC, bool TASK4 = false>
 __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // Gate/up follows the kernel that makes the work items, so it waits for it at once. Down follows
@@ -588,11 +713,12 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
     const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
-    const uint32_t task_bytes = GATE_UP ? group_bytes * 2 : group_bytes * kDownGroups;
+    const uint32_t task_bytes = TASK4 ? group_bytes * 4 : GATE_UP ? group_bytes * 2 : group_bytes * kDownGroups;
     const int cpt = p.cpt, rpw = p.rpw;
     const uint32_t chunk_bytes = task_bytes / uint32_t(cpt);
-    const uint32_t half_bytes = chunk_bytes / 2;   // gate/up: one group's share of a chunk
-    const int tasks_per_expert = GATE_UP ? p.ff / 16 : p.n / 16 / kDownGroups;
+    const uint32_t half_bytes = chunk_bytes / 2;      // gate/up: one group's share of a chunk
+    const uint32_t quarter_bytes = chunk_bytes / 4;   // four-group tasks: one group's share of a chunk
+    const int tasks_per_expert = TASK4 ? (GATE_UP ? p.ff / 32 : p.n / 64) : GATE_UP ? p.ff / 16 : p.n / 16 / kDownGroups;
     const size_t section = GATE_UP ? 0 : size_t(p.ff / 8) * (size_t(p.n / kUnitK) * kUnitBytes);
     const int slots = NW * rpw;
     const int nbuf = p.nbuf;
@@ -633,6 +759,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     // ---- this warp's stream of chunks. Task i of the block (i = warp, warp + NW, ...) is fetched as
     // cpt chunks; chunk j of the warp goes to its ring slot j % rpw. Lane 0 issues the TMA copies:
     // the first rpw chunks up front, then chunk j + rpw into the slot that chunk j just left.
+    // (Handing tasks to whichever warp is free, from a shared counter, was measured and is slower.)
     const int first_item = int(lo / tasks_per_expert), last_item = int((hi - 1) / tasks_per_expert);
     int is_item = 0, is_task = 0, is_i = warp, is_c = 0, is_slot = 0;   // the next chunk to issue
     const uint8_t* is_blob = nullptr;
@@ -646,7 +773,11 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         if (is_i >= ntasks) return;
         mbar_expect_tx(full + is_slot, chunk_bytes);
         uint8_t* dst = ring + size_t(is_slot) * chunk_bytes;
-        if (GATE_UP) {   // the same K range of the task's two groups, one after the other
+        if (TASK4) {     // the same K range of the task's four groups
+            const uint8_t* src = is_blob + size_t(is_task) * task_bytes + size_t(is_c) * quarter_bytes;
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) bulk_g2s(dst + gq * quarter_bytes, src + size_t(gq) * group_bytes, quarter_bytes, full + is_slot);
+        } else if (GATE_UP) {   // the same K range of the task's two groups, one after the other
             const uint8_t* src = is_blob + size_t(is_task) * task_bytes + size_t(is_c) * half_bytes;
             bulk_g2s(dst, src, half_bytes, full + is_slot);
             bulk_g2s(dst + half_bytes, src + group_bytes, half_bytes, full + is_slot);
@@ -789,7 +920,6 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     for (int q = 0; q < nseg; ++q) {
         const int item = first_item + q, buf = q % nbuf;
         mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort, p.wait_ns);
-        const long long seg_lo = max(lo, (long long)item * tasks_per_expert);
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
         const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da + buf * (nb * 64));
@@ -800,10 +930,68 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         const bool narrow = m <= kNarrowTok && p.narrow;
         // the lane's two token columns, and in the narrow form the row group (of the pair) it finishes
         const int c0 = narrow ? 2 * (t4 & 1) : 2 * t4, c1 = c0 + 1, rn = t4 >> 1;
+        const long long seg_lo = max(lo, (long long)item * tasks_per_expert);
         const int i_lo = int(seg_lo - lo), first = i_lo + (warp - i_lo % NW + NW) % NW;
         for (long long tau = lo + first; tau < seg_hi; tau += NW) {
             const int task = int(tau % tasks_per_expert);
-            if (GATE_UP && narrow) {
+            if constexpr (TASK4) {
+                const int upc = units / cpt;
+                float* o0 = nullptr;
+                float* o1 = nullptr;
+                if (m <= 2) {   // lane (g, t4) finishes row group t4 for tokens 0 and 1
+                    uint64_t acc_lo = 0ull, acc_hi = 0ull;
+                    for (int c = 0; c < cpt; ++c) {
+                        const uint8_t* cp = chunk_wait();
+                        units_mma_n2<UPC>(cp, quarter_bytes, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
+                        chunk_done();
+                    }
+                    float sum[4];
+                    unpack2(acc_lo, sum[0], sum[1]);
+                    unpack2(acc_hi, sum[2], sum[3]);
+                    const int grp = task * 4 + t4;
+                    if (GATE_UP) {
+                        const int row = grp * 8 + g;
+                        p.gu[size_t(its->slot[0]) * p.ff + row] = make_float2(sum[0], sum[2]);
+                        if (m > 1) p.gu[size_t(its->slot[1]) * p.ff + row] = make_float2(sum[1], sum[3]);
+                    } else {
+                        const int row = grp * 16 + g;
+                        o0 = out_row(its->slot[0]);
+                        put2(o0, row, sum[0], sum[2]);
+                        if (m > 1) {
+                            o1 = out_row(its->slot[1]);
+                            put2(o1, row, sum[1], sum[3]);
+                        }
+                    }
+                } else {        // two pairs in the narrow form: lanes t4 = 0, 1 finish the first group of a pair, 2, 3 the second
+                    uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};
+                    for (int c = 0; c < cpt; ++c) {
+                        const uint8_t* cp = chunk_wait();
+                        units_mma_n4x2<UPC>(cp, quarter_bytes, upc, 2 * c * upc, bfrag, da, ci, lane, acc_lo, acc_hi);
+                        chunk_done();
+                    }
+                    const int t0 = 2 * (t4 & 1), t1 = t0 + 1;
+                    if (!GATE_UP) {
+                        if (t0 < m) o0 = out_row(its->slot[t0]);
+                        if (t1 < m) o1 = out_row(its->slot[t1]);
+                    }
+#pragma unroll
+                    for (int pi = 0; pi < 2; ++pi) {
+                        float sum[4];
+                        unpack2(acc_lo[pi], sum[0], sum[1]);
+                        unpack2(acc_hi[pi], sum[2], sum[3]);
+                        const int grp = task * 4 + 2 * pi + (t4 >> 1);
+                        if (GATE_UP) {
+                            const int row = grp * 8 + g;
+                            if (t0 < m) p.gu[size_t(its->slot[t0]) * p.ff + row] = make_float2(sum[0], sum[2]);
+                            if (t1 < m) p.gu[size_t(its->slot[t1]) * p.ff + row] = make_float2(sum[1], sum[3]);
+                        } else {
+                            const int row = grp * 16 + g;
+                            if (o0) put2(o0, row, sum[0], sum[2]);
+                            if (o1) put2(o1, row, sum[1], sum[3]);
+                        }
+                    }
+                }
+            } else if (GATE_UP && narrow) {
                 uint64_t acc_lo = 0ull, acc_hi = 0ull;   // {0.0f, 0.0f}
                 const int upc = units / cpt;
                 for (int c = 0; c < cpt; ++c) {
@@ -1223,8 +1411,12 @@ struct StreamCfg {
 // 0. With few items most warps of a 16-warp block would have no task at all while the busy ones
 // are limited by their two ring slots (a warp streams its task with only that much in flight):
 // blocks of 4 or 8 warps with deeper rings serve small batches better.
-int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
-    const int budget = max_smem_optin() - 1024;
+// decode, when every item has at most four tokens: bit 0 = gate/up, bit 1 = down take tasks of four row groups
+// (k_stream's TASK4 form). Measured at batch 64: down gains from it, gate/up does not.
+int g_task4 = 2;
+
+int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0, bool task4 = false) {
+    const int budget = max_smem_optin() - 2048;   // less the kernels' static shared memory
     if (budget <= 0) return fail(FRX_ERR_CUDA, "no CUDA device");
     // a task is fetched as `chunks` chunks; the preferred warp count is kept if
     // every warp can have at least two ring slots (up to four), else fewer warps are used
@@ -1233,7 +1425,7 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
     auto fit = [&](int kdim, uint32_t task_bytes, int chunks, long long max_tasks, int& nw, int& cpt, int& rpw, int& nbuf, uint32_t& bytes) {
         cpt = chunks;
         const uint32_t chunk = task_bytes / uint32_t(cpt);
-        int first = g_nw;
+        int first = task4 ? (g_nw >= 12 ? 16 : 8) : g_nw;
         if (max_tasks > 0 && max_tasks <= 4LL * sms) first = 4;
         else if (max_tasks > 0 && max_tasks <= 8LL * sms) first = 8;
         const int prefs[3] = {first, first > 16 ? 16 : first > 12 ? 12 : 8, 8};
@@ -1248,6 +1440,16 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0) {
         return false;
     };
     const int gu_units = n / kUnitK, dn_units = ff / kUnitK;
+    if (task4) {
+        // a task is four groups, a chunk two units (or one) of K of all four: 4,608 bytes at the usual shapes
+        const int gu_c = gu_units % 2 == 0 ? gu_units / 2 : gu_units, dn_c = dn_units % 2 == 0 ? dn_units / 2 : dn_units;
+        if (!fit(n, uint32_t(gu_units) * kUnitBytes * 4, gu_c, max_items * (ff / 32), c.nw_gu, c.cpt_gu, c.rpw_gu, c.nbuf_gu, c.smem_gu) ||
+            !fit(ff, uint32_t(dn_units) * kUnitBytes * 4, dn_c, max_items * (n / 64), c.nw_dn, c.cpt_dn, c.rpw_dn, c.nbuf_dn, c.smem_dn))
+            return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
+        auto round_nw = [](int nw) { return nw >= 12 ? 16 : nw >= 8 ? 8 : 4; };   // the forms that are built
+        if (round_nw(c.nw_gu) != c.nw_gu || round_nw(c.nw_dn) != c.nw_dn) return fail(FRX_ERR_SHAPE, "unsupported warp count for four-group tasks");
+        return FRX_OK;
+    }
     // gate/up: a task is two groups, fetched in K slices; down: kDownGroups groups in two chunks of whole groups
     int gu_chunks = gu_units % 4 == 0 ? 4 : gu_units % 2 == 0 ? 2 : 1;
     if (g_gu_chunks > 0 && gu_units % g_gu_chunks == 0) gu_chunks = g_gu_chunks;
@@ -1266,6 +1468,25 @@ void launch_stream_nw(const StreamParams& p, int upc, uint32_t smem, cudaStream_
         launch_pdl(k_stream<GATE_UP, NW, kFixed>, dim3(sms), dim3(NW * 32), smem, stream, p);
     else
         launch_pdl(k_stream<GATE_UP, NW, 0>, dim3(sms), dim3(NW * 32), smem, stream, p);   // any other split of K
+}
+
+template <bool GATE_UP>
+void launch_stream4(const StreamParams& p, int nw, int upc, uint32_t smem, cudaStream_t stream) {
+    const int sms = sm_count();
+    auto go = [&](auto kernel, int threads) { launch_pdl(kernel, dim3(sms), dim3(threads), smem, stream, p); };
+    if (upc == 2) {
+        switch (nw) {
+            case 4: go(k_stream<GATE_UP, 4, 2, true>, 128); break;
+            case 8: go(k_stream<GATE_UP, 8, 2, true>, 256); break;
+            default: go(k_stream<GATE_UP, 16, 2, true>, 512); break;
+        }
+    } else {
+        switch (nw) {
+            case 4: go(k_stream<GATE_UP, 4, 0, true>, 128); break;
+            case 8: go(k_stream<GATE_UP, 8, 0, true>, 256); break;
+            default: go(k_stream<GATE_UP, 16, 0, true>, 512); break;
+        }
+    }
 }
 
 template <bool GATE_UP>
@@ -1288,7 +1509,7 @@ int set_smem_attr() {
     FRX_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lk(mu);
     if (dev >= 0 && dev < 64 && done[dev]) return FRX_OK;
-    const int lim = max_smem_optin();
+    const int lim = max_smem_optin() - 2048;   // dynamic part only: the kernels also hold a little static shared memory
     const void* fns[] = {
         reinterpret_cast<const void*>(k_stream<true, 4, 4>),   reinterpret_cast<const void*>(k_stream<true, 4, 0>),
         reinterpret_cast<const void*>(k_stream<false, 4, 4>),  reinterpret_cast<const void*>(k_stream<false, 4, 0>),
@@ -1299,7 +1520,13 @@ int set_smem_attr() {
         reinterpret_cast<const void*>(k_stream<true, 16, 4>),  reinterpret_cast<const void*>(k_stream<true, 16, 0>),
         reinterpret_cast<const void*>(k_stream<false, 16, 4>), reinterpret_cast<const void*>(k_stream<false, 16, 0>),
         reinterpret_cast<const void*>(k_stream<true, 20, 4>),  reinterpret_cast<const void*>(k_stream<true, 20, 0>),
-        reinterpret_cast<const void*>(k_stream<false, 20, 4>), reinterpret_cast<const void*>(k_stream<false, 20, 0>)};
+        reinterpret_cast<const void*>(k_stream<false, 20, 4>), reinterpret_cast<const void*>(k_stream<false, 20, 0>),
+        reinterpret_cast<const void*>(k_stream<true, 4, 2, true>),   reinterpret_cast<const void*>(k_stream<true, 4, 0, true>),
+        reinterpret_cast<const void*>(k_stream<false, 4, 2, true>),  reinterpret_cast<const void*>(k_stream<false, 4, 0, true>),
+        reinterpret_cast<const void*>(k_stream<true, 8, 2, true>),   reinterpret_cast<const void*>(k_stream<true, 8, 0, true>),
+        reinterpret_cast<const void*>(k_stream<false, 8, 2, true>),  reinterpret_cast<const void*>(k_stream<false, 8, 0, true>),
+        reinterpret_cast<const void*>(k_stream<true, 16, 2, true>),  reinterpret_cast<const void*>(k_stream<true, 16, 0, true>),
+        reinterpret_cast<const void*>(k_stream<false, 16, 2, true>), reinterpret_cast<const void*>(k_stream<false, 16, 0, true>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
@@ -1319,7 +1546,8 @@ void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaSt
     FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c, block64));
 }
 
-void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream) {
+void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream,
+                bool task4_gu = false, bool task4_dn = false) {
     p.narrow = g_narrow;
     p.wait_ns = wait_limit_ns();
     p.cpt = cfg.cpt_gu;
@@ -1328,7 +1556,10 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.aq = xb.q;
     p.aa = xb.a;
     p.ac = xb.c;
-    FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
+    if (task4_gu)
+        FRX_LAUNCH(kKGateUp, stream, launch_stream4<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
+    else
+        FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     const size_t nblk = h_rows * (p.ff / kQ8);
     FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map, p.row_list, p.row_count, p.row_list ? 0 : 1));
     p.cpt = cfg.cpt_dn;
@@ -1337,7 +1568,10 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
     p.aq = hb.q;
     p.aa = hb.a;
     p.ac = hb.c;
-    FRX_LAUNCH(kKDown, stream, launch_stream<false>(p, cfg.nw_dn, p.ff / kUnitK, cfg.smem_dn, stream));
+    if (task4_dn)
+        FRX_LAUNCH(kKDown, stream, launch_stream4<false>(p, cfg.nw_dn, p.ff / kUnitK / cfg.cpt_dn, cfg.smem_dn, stream));
+    else
+        FRX_LAUNCH(kKDown, stream, launch_stream<false>(p, cfg.nw_dn, p.ff / kUnitK, cfg.smem_dn, stream));
 }
 
 template <class LayoutT>
@@ -1373,8 +1607,28 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
     if (T == 0) return FRX_OK;
     const Layout L = make_layout(T, K, n, ff);
     if (ws_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_decode: workspace %zu < %zu", ws_bytes, L.total);
+    // with items cut at four tokens either streaming kernel may take tasks of four row groups
+    const bool task4_gu = g_narrow && (g_task4 & 1), task4_dn = g_narrow && (g_task4 & 2);
     StreamCfg cfg;
-    if (int rc = stream_cfg(n, ff, cfg, L.max_items)) return rc;   // max_items: the most items a chunk of tokens can make
+    if (int rc = stream_cfg(n, ff, cfg, L.max_items, false)) return rc;   // max_items: the most items a chunk of tokens can make
+    if (task4_gu || task4_dn) {
+        StreamCfg c4;
+        if (int rc = stream_cfg(n, ff, c4, L.max_items, true)) return rc;
+        if (task4_gu) {
+            cfg.nw_gu = c4.nw_gu;
+            cfg.cpt_gu = c4.cpt_gu;
+            cfg.rpw_gu = c4.rpw_gu;
+            cfg.nbuf_gu = c4.nbuf_gu;
+            cfg.smem_gu = c4.smem_gu;
+        }
+        if (task4_dn) {
+            cfg.nw_dn = c4.nw_dn;
+            cfg.cpt_dn = c4.cpt_dn;
+            cfg.rpw_dn = c4.rpw_dn;
+            cfg.nbuf_dn = c4.nbuf_dn;
+            cfg.smem_dn = c4.smem_dn;
+        }
+    }
     if (int rc = set_smem_attr()) return rc;
     auto* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + L.status);
@@ -1419,7 +1673,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
             p.e_lo = e_lo;
             p.e_hi = e_hi;
         }
-        launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream);
+        launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream, task4_gu, task4_dn);
         if (ep)   // one chunk only (the caller checked T <= 64)
             FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_allreduce, dim3((n + 256 * kEpElems - 1) / (256 * kEpElems), Tc), dim3(256), 0, stream, out,
                                                             (const float*)p.y, (const float*)wts, (const int32_t*)order,
@@ -1748,6 +2002,10 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
 }
 
 // Tuning knobs for measurements (process-wide, not thread-safe: set them before any compute call).
+int frx_debug_set_four_group_tasks(int on) {
+    g_task4 = on & 3;
+    return FRX_OK;
+}
 int frx_debug_set_gate_up_chunks(int chunks) {
     if (chunks < 0 || chunks > 16) return FRX_ERR_ARG;
     g_gu_chunks = chunks;

@@ -80,6 +80,7 @@ SIGNATURES = {
     "frx_debug_set_consumer_warps": (_i, [_i]),
     "frx_debug_set_gate_up_chunks": (_i, [_i]),
     "frx_debug_set_narrow_items": (_i, [_i]),
+    "frx_debug_set_four_group_tasks": (_i, [_i]),
     "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),
     "frx_moe_decode_static_status": (_i, [_vp]),
     "frx_moe_layer_ep_allreduce": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -64,11 +64,15 @@ const char* frx_profile_class_name(int cls);
  * frx_debug_set_narrow_items: 1 (default) lets work items of at most four tokens take the narrow
  * form of the inner product (two row groups share one MMA accumulator, half the float work per row);
  * 0 sends every item through the eight-token form. Results are the same bits either way.
+ * frx_debug_set_four_group_tasks: which streaming kernels of the decode layer walk four row groups per task
+ * instead of two (needs narrow items): bit 0 gate/up, bit 1 down; default 2 (down only, the faster
+ * combination as measured). Same bits either way.
  * frx_debug_set_wait_limit_ns: the longest a kernel waits on a barrier, a flag or a peer before it
  * gives up and reports FRX_ERR_DEVICE through the workspace status (default 2 s; 0 restores it). */
 int frx_debug_set_consumer_warps(int nw);
 int frx_debug_set_gate_up_chunks(int chunks);
 int frx_debug_set_narrow_items(int on);
+int frx_debug_set_four_group_tasks(int on);
 int frx_debug_set_wait_limit_ns(unsigned long long ns);
 
 /* ---- Q2_0 storage (quant/q2_0/q2_0.hpp:27-56, quant/q2_0/q2_0.cpp:43-71) ---- */

@@ -274,8 +274,15 @@ def test_narrow_and_wide_item_forms_give_the_same_bits(port):
         out_w, ys_w = run_decode(ex, x, ids, wts, gate)
     finally:
         check(lib.frx_debug_set_narrow_items(1))
-    out_n, ys_n = run_decode(ex, x, ids, wts, gate)
+    out_n, ys_n = run_decode(ex, x, ids, wts, gate)                # narrow items, four row groups per task (the default)
     assert np.array_equal(ys_n, ys_w) and np.array_equal(out_n, out_w)
+    for forms in (0, 1, 3):                                        # two or four row groups per task, per kernel (default: 2)
+        try:
+            check(lib.frx_debug_set_four_group_tasks(forms))
+            out_2, ys_2 = run_decode(ex, x, ids, wts, gate)
+        finally:
+            check(lib.frx_debug_set_four_group_tasks(2))
+        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), forms
     ref_out, ref_ys, _ = port.moe_layer(ex.routed_planar(), ex.blob_bytes, ex.shared_planar, n, ff, x, ids, wts, gate, n_threads=8,
                                         want_slots=True)
     assert max(rel_max(ys_n[s], ref_ys[s]) for s in range(T * K)) < 1e-5
