@@ -49,6 +49,7 @@ sys.path.insert(0, ROOT)
 N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
+NCU_FFN_TRAFFIC_PER_BLOB = None            # the same for one launch of the fused kernel (k_ffn)
 NCU_GU_TRAFFIC_PER_BLOB = 223.0e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
@@ -240,6 +241,14 @@ def run_frx(args):
         moe.check(moe.lib.frx_debug_set_consumer_warps(args.nw))
     if args.narrow is not None:
         moe.check(moe.lib.frx_debug_set_narrow_items(args.narrow))
+    if args.fused is not None:
+        moe.check(moe.lib.frx_debug_set_fused_ffn(args.fused))
+    if args.down_weight is not None:
+        moe.check(moe.lib.frx_debug_set_down_task_weight(args.down_weight))
+    if args.fold is not None:
+        moe.check(moe.lib.frx_debug_set_fold_quant(args.fold))
+    if args.ffn_buffers:
+        moe.check(moe.lib.frx_debug_set_ffn_buffers(*[int(v) for v in args.ffn_buffers.split(",")]))
     if args.task4 is not None:
         moe.check(moe.lib.frx_debug_set_four_group_tasks(args.task4))
     if args.gu_chunks:
@@ -428,7 +437,7 @@ def run_frx(args):
     value = B * L / (ms * 1e-3)
 
     # ---- per-kernel device time: CUDA events around every launch, the same K steps without the graph
-    ncls = 8
+    ncls = 16
     pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
     moe.check(moe.lib.frx_profile_begin())
     for _ in range(args.steps):
@@ -438,26 +447,51 @@ def run_frx(args):
     names = [moe.lib.frx_profile_class_name(i).decode() for i in range(ncls)]
     kernels = {names[i]: {"launches": int(pn[i]), "ms_total": round(float(pms[i]), 4),
                           "us_per_launch": round(1e3 * float(pms[i]) / max(1, int(pn[i])), 3)} for i in range(ncls) if pn[i]}
-    gu_us = kernels["gate_up"]["us_per_launch"]
     peak, peak_src = peaks()
     mean_local = float(np.mean(local_distinct)) + (1.0 if rank == 0 or world == 1 else 0.0)
-    gu_alg_bytes = mean_local * GU_BYTES + B * (N_MODEL + N_MODEL // 32 * 8) + B * (K + 1) * FF * 4
+    fused = "ffn" in kernels   # gate/up, the hidden rows and down in one kernel (k_ffn), else k_stream<gate_up> is the dominant kernel
+    if fused:
+        # whole blobs, the quantized x in, (gate x, up x) pairs out and in again, the slots' output rows out
+        top_name, gu_us = "k_ffn", kernels["ffn"]["us_per_launch"]
+        gu_alg_bytes = (mean_local * EXPERT_BYTES + B * (N_MODEL + N_MODEL // 32 * 8) + 2 * B * (K + 1) * FF * 8
+                        + B * (K + 1) * N_MODEL * 4)
+        traffic_per_blob = NCU_FFN_TRAFFIC_PER_BLOB
+    else:
+        top_name, gu_us = "k_stream<gate_up>", kernels["gate_up"]["us_per_launch"]
+        gu_alg_bytes = mean_local * GU_BYTES + B * (N_MODEL + N_MODEL // 32 * 8) + B * (K + 1) * FF * 4
+        traffic_per_blob = NCU_GU_TRAFFIC_PER_BLOB
     achieved = gu_alg_bytes / (gu_us * 1e-6) / 1e9
 
     def layer_alg_bytes(dist_list, Bt):
         return float(np.mean([(d + 1) * EXPERT_BYTES for d in dist_list])) + Bt * (E * 4 + N_MODEL * 8) + Bt * K * 8
 
     layer_bytes = layer_alg_bytes(distinct, B)
-    roofline = {"bound": "hbm", "kernel": "k_stream<gate_up>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+    roofline = {"bound": "hbm", "kernel": top_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_source": peak_src,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture of a 2-layer
                 # case of the same kernel, scaled to this run by the distinct blobs a launch reads
-                "traffic": int(mean_local * NCU_GU_TRAFFIC_PER_BLOB), "traffic_source": "ncu capture of a 2-layer case, scaled by distinct expert blobs",
+                "traffic": int(mean_local * traffic_per_blob) if traffic_per_blob else None, "traffic_source": "ncu capture of a 2-layer case, scaled by distinct expert blobs",
                 "algorithmic_bytes_per_launch": int(gu_alg_bytes), "us_per_launch": gu_us,
                 "timing": "CUDA events around each launch, a separate pass of the same steps without the CUDA graph",
                 "layer": {"algorithmic_bytes": int(layer_bytes), "us": round(ms * 1e3 / L, 3),
                           "achieved_GBps": round(layer_bytes / world / (ms * 1e-3 / L) / 1e9, 1),
                           "frac_of_peak": round(layer_bytes / world / (ms * 1e-3 / L) / 1e9 / peak, 4)}}
+
+    # ---- expert parallel: where the fused all-reduce's time goes (SM cycle stamps of block 0 in the last
+    # layer call of the pass above, every rank's)
+    ep_allreduce = None
+    if comm is not None:
+        st = comm.stamps()
+        mine = torch.tensor([st[1] - st[0], st[2] - st[1], st[3] - st[2]], dtype=torch.float64, device=dev)
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        cyc = torch.stack(every).cpu().numpy()
+        ep_allreduce = {"unit": "SM cycles of block 0, last layer call, per rank",
+                        "own_partial_sums_stored": [int(v) for v in cyc[:, 0]],
+                        "waiting_for_peer_flags": [int(v) for v in cyc[:, 1]],
+                        "peer_parts_read_and_summed": [int(v) for v in cyc[:, 2]],
+                        "kernel_us_per_launch": kernels.get("combine", {}).get("us_per_launch"),
+                        "bytes_read_from_peers_per_rank": (world - 1) * B * N_MODEL * 4}
 
     # ---- e2e: host buffers through frx_moe_layers_host (one call per step, copies pipelined with
     # compute), every copy inside the timed region
@@ -643,6 +677,8 @@ def run_frx(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": sum(v["launches"] for v in kernels.values()), "kernels": kernels,
             "roofline": roofline, "cpu_baseline": cpu, "decode_batches": decode_batches, "prefill": prefill, "verify_stack": verify_stack,
         }
+        if ep_allreduce is not None:
+            line["ep_allreduce"] = ep_allreduce
         print(json.dumps(line))
     if comm is not None:
         comm.close()
@@ -770,7 +806,7 @@ def bench_prefill_extra(torch, dist, moe, synth, dev, rank, world, arena, e_lo, 
             tt = torch.tensor([ms], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             ms = float(tt.item())
-        ncls = 8
+        ncls = 16
         pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
         moe.check(moe.lib.frx_profile_begin())
         step()
@@ -893,7 +929,7 @@ def run_prefill(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ncls = 8
+    ncls = 16
     pms, pn = (C.c_float * ncls)(), (C.c_int * ncls)()
     moe.check(moe.lib.frx_profile_begin())
     for _ in range(args.steps):
@@ -937,6 +973,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the decode_batches, prefill and verify_stack keys")
     ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16, 20)")
+    ap.add_argument("--fused", type=int, default=None, help="tuning: 0 runs the decode FFN as three kernels instead of one")
+    ap.add_argument("--down-weight", type=int, default=None, help="tuning: weight (in 1/16) of a down task of a 3-4 token item in the split over blocks; 0 = even split")
+    ap.add_argument("--fold", type=int, default=None, help="tuning: 0 runs the hidden-row quantizer as its own kernel")
+    ap.add_argument("--ffn-buffers", default=None, help="tuning: item buffers of the fused FFN kernel, gate/up,down (e.g. 3,3)")
     ap.add_argument("--task4", type=int, default=None, help="tuning: 0 keeps two row groups per task in the decode layer")
     ap.add_argument("--gu-chunks", type=int, default=0, help="tuning: K slices per gate/up task")
     ap.add_argument("--narrow", type=int, default=None, help="tuning: 0 sends every work item through the eight-token form")

@@ -134,7 +134,7 @@ int frx_profile_end(float* ms, int* launches, int n_classes) {
 }
 
 const char* frx_profile_class_name(int cls) {
-    static const char* names[kNumKernelClasses] = {"route_topk", "quant_q8", "group", "gate_up", "down", "combine", "layout", "route_group_quant"};
+    static const char* names[kNumKernelClasses] = {"route_topk", "quant_q8", "group", "gate_up", "down", "combine", "layout", "route_group_quant", "ffn"};
     return cls >= 0 && cls < kNumKernelClasses ? names[cls] : "";
 }
 

@@ -47,7 +47,7 @@ int max_smem_optin();
 
 // Optional per-kernel timing (frx_profile_begin / frx_profile_end): when switched on, every
 // launch made through FRX_LAUNCH is bracketed by two CUDA events on its own stream.
-enum KernelClass : int { kKRoute = 0, kKQuant, kKGroup, kKGateUp, kKDown, kKCombine, kKLayout, kKPrologue, kNumKernelClasses };
+enum KernelClass : int { kKRoute = 0, kKQuant, kKGroup, kKGateUp, kKDown, kKCombine, kKLayout, kKPrologue, kKFfn, kNumKernelClasses };
 extern bool g_profile_on;
 void profile_mark(int cls, cudaStream_t stream, bool start);
 #define FRX_LAUNCH(cls, stream, ...)                                   \
@@ -202,6 +202,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// Counters in global memory that blocks of one grid raise and await.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // 1-D bulk copy global -> shared through the TMA unit, completion counted on an mbarrier.
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -241,28 +251,27 @@ __device__ __forceinline__ void mma_u8s8_c4(uint64_t& lo, uint64_t& hi, uint32_t
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w));
 }
 
-// Two MMAs chained into one accumulator: D = A0 * B0 + A1 * B1 + C, results packed as above. Used
-// with B operands that are zero in complementary token columns, so that the columns of D belong to
-// different row groups.
+// Two MMAs chained into one accumulator: D = A0 * B0 + A1 * B1 + C with every element of C equal
+// to `c`, results packed as above. Used with B operands that are zero in complementary token
+// columns, so that the columns of D belong to different row groups.
 __device__ __forceinline__ void mma_u8s8_chain2(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3,
-                                                uint32_t f0, uint32_t f1, int c0, int c1) {
-    // the accumulator input is {c0, c1} for the lane's two token columns, in both row halves
+                                                uint32_t f0, uint32_t f1, int c) {
     asm volatile(
         "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%14,%15,%14,%15};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%6,%7}, {%14,%14,%14,%14};\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%8,%9,%10,%11}, {%12,%13}, {d0,d1,d2,d3};\n\t"
         "mov.b64 %0, {d0,d1};\n\t"
         "mov.b64 %1, {d2,d3};\n\t}"
         : "=l"(lo), "=l"(hi)
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c0), "r"(c1));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(e0), "r"(e1), "r"(e2), "r"(e3), "r"(f0), "r"(f1), "r"(c));
 }
 
 // Four MMAs chained into one accumulator (see mma_u8s8_chain2): D = sum_j A_j * B_j + C.
-__device__ __forceinline__ void mma_u8s8_chain4(uint64_t& lo, uint64_t& hi, const uint32_t (&a)[16], const uint32_t (&b)[8], int c0, int c1) {
+__device__ __forceinline__ void mma_u8s8_chain4(uint64_t& lo, uint64_t& hi, const uint32_t (&a)[16], const uint32_t (&b)[8], int c) {
     asm volatile(
         "{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%18,%19}, {%26,%27,%26,%27};\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%2,%3,%4,%5}, {%18,%19}, {%26,%26,%26,%26};\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%6,%7,%8,%9}, {%20,%21}, {d0,d1,d2,d3};\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%10,%11,%12,%13}, {%22,%23}, {d0,d1,d2,d3};\n\t"
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {d0,d1,d2,d3}, {%14,%15,%16,%17}, {%24,%25}, {d0,d1,d2,d3};\n\t"
@@ -271,7 +280,18 @@ __device__ __forceinline__ void mma_u8s8_chain4(uint64_t& lo, uint64_t& hi, cons
         : "=l"(lo), "=l"(hi)
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]), "r"(a[10]), "r"(a[11]),
           "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]),
-          "r"(c0), "r"(c1));
+          "r"(c));
+}
+
+// A 16-byte load from shared memory that only the lanes with `on` perform; the others keep what
+// `v` held (a predicated instruction: lanes that are off cost no shared-memory bandwidth).
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, bool on) {   // addr: smem_u32() of the source
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.u32 q, %4, 0;\n\t"
+        "@q ld.shared.v4.u32 {%0,%1,%2,%3}, [%5];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(uint32_t(on)), "r"(addr));
 }
 
 __device__ __forceinline__ void mma_u8s8_bias(uint64_t& lo, uint64_t& hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

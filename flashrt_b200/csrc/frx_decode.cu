@@ -36,8 +36,12 @@ constexpr int kItemWords = sizeof(Item) / 4;
 __host__ __device__ inline int slot_token(int slot, int K, int TK) { return slot < TK ? slot / K : slot - TK; }
 
 // Workspace status words: [0] device error, [1] items of the current chunk, [2] detail, [3] cookie.
+// Behind the kStatusWords words, in the decode layout: one counter per item, the gate/up tasks of the
+// item that have been finished (zeroed by the grouping kernel, counted and awaited by k_ffn).
+constexpr int kStatusWords = 16;
+constexpr int kMaxStreamBlocks = 1024;   // the streaming kernels run one block per SM
 struct Layout {
-    size_t status, items, order, xq, xa, xc, gu, h, hq, ha, hc, y, ysh, total;
+    size_t status, ranges, items, order, xq, xa, xc, gu, h, hq, ha, hc, y, ysh, total;
     int max_items;
 };
 
@@ -51,7 +55,8 @@ Layout make_layout(int T, int K, int n, int ff) {
         return o;
     };
     L.max_items = Tc * K + (Tc + kNarrowTok - 1) / kNarrowTok;   // every routed slot its own item at worst; the shared expert in items of four tokens
-    L.status = take(64);
+    L.status = take(64 + size_t(L.max_items) * 4);   // 16 status words, then one counter per item (see k_ffn)
+    L.ranges = take((kMaxStreamBlocks + 1) * 4);   // the down kernel's tasks per block (see DownSplit)
     L.items = take(size_t(L.max_items) * sizeof(Item));
     L.order = take(size_t(Tc) * K * 4);
     L.xq = take(size_t(Tc) * n);
@@ -244,14 +249,28 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
 // tpi: tokens per item, 8 (the width of the MMA) or 4: with four every item takes the narrow form
 // of the inner product, so all items cost the same and the even split of tasks over the SMs is an
 // even split of time (an expert with more tokens is then read once from HBM and again from the L2).
+// `split` (decode): how the down kernel's tasks are shared out among its blocks. A down task of an
+// item of three or four tokens costs more than one of an item of one or two (two passes of float
+// work per block of K instead of one), so an even split of tasks is not an even split of time:
+// block b takes the tasks [ranges[b], ranges[b + 1]) (numbered item * tasks_per_expert + task),
+// boundaries placed so that every block gets the same weight, a task of a small item weighing 16
+// and one of a larger item `heavy`. dyn then has max_items more ints.
+struct DownSplit {
+    int* ranges;            // [blocks + 1], or null: no split is written
+    int blocks;             // blocks of the down kernel
+    int tasks_per_expert;
+    int heavy;              // weight of a task of an item of more than two tokens (16 = as light ones)
+};
 __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32_t* __restrict__ ids, int T, int K, int E, int e_lo,
                                             int e_hi, const uint8_t* __restrict__ experts, size_t stride,
                                             const uint8_t* __restrict__ shared, Item* __restrict__ items, int* __restrict__ status,
-                                            int32_t* __restrict__ order, int max_items, int tpi) {
-    unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K]
+                                            int32_t* __restrict__ order, int max_items, int tpi, bool zero_counters = false,
+                                            DownSplit split = DownSplit{nullptr, 0, 0, 16}) {
+    unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K], then the items' weights
     __shared__ int warp_tot[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int32_t* sid = reinterpret_cast<int32_t*>(mask + E);   // the ids, read many times below
+    int* wgt = sid + T * K;                                // with `split`: weight of a task of every item, then their running sums
     if (tid == 0 && status[3] != kCookie) {   // first use of this workspace
         status[0] = kDevOk;
         status[2] = 0;
@@ -271,8 +290,15 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     }
     __syncthreads();
     const int per = (E + 1023) / 1024, e0 = tid * per, e1 = min(E, e0 + per);
+    // one scan for two sums: the items in the low 12 bits, the weights of their tasks above (see DownSplit)
+    constexpr int kCntBits = 12, kCntMask = (1 << kCntBits) - 1;
+    auto weight_of = [&](int m) { return m <= 2 ? 16 : split.heavy; };
     int cnt = 0;
-    for (int e = e0; e < e1; ++e) cnt += (__popcll(mask[e]) + tpi - 1) / tpi;
+    for (int e = e0; e < e1; ++e) {
+        const int pc = __popcll(mask[e]), full = pc / tpi, rem = pc - full * tpi;
+        cnt += full + (rem ? 1 : 0);
+        if (split.ranges) cnt += (full * weight_of(tpi) + (rem ? weight_of(rem) : 0)) << kCntBits;
+    }
     int inc = cnt;   // inclusive scan over the block: within the warp, then over the warp totals
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -291,8 +317,9 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         warp_tot[lane] = w;
     }
     __syncthreads();
-    int at = inc - cnt + (warp ? warp_tot[warp - 1] : 0);
-    const int routed_items = warp_tot[31];
+    const int before = inc - cnt + (warp ? warp_tot[warp - 1] : 0);
+    int at = before & kCntMask, wat = before >> kCntBits;   // this thread's first item, and the weight in front of it
+    const int routed_items = warp_tot[31] & kCntMask, routed_weight = warp_tot[31] >> kCntBits;
     const int shared_items = shared ? (T + tpi - 1) / tpi : 0;
     if (routed_items + shared_items > max_items) {
         if (tid == 0) {
@@ -318,6 +345,10 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
             }
             it.n_tok = m;
             for (int j = m; j < kTokPerItem; ++j) it.slot[j] = 0;
+            if (split.ranges) {
+                wgt[at] = wat;   // the weight in front of this item
+                wat += weight_of(m);
+            }
             items[at++] = it;
         }
     }
@@ -328,9 +359,12 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         const int t0 = tid * tpi, m = min(tpi, T - t0);
         it.n_tok = m;
         for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? T * K + t0 + j : 0;
+        if (split.ranges) wgt[routed_items + tid] = routed_weight + tid * weight_of(tpi);   // (all but the last shared item are full)
         items[routed_items + tid] = it;
     }
     if (tid == 0) status[1] = routed_items + shared_items;
+    if (zero_counters)
+        for (int i = tid; i < routed_items + shared_items; i += 1024) status[kStatusWords + i] = 0;
     // Slots of a token by ascending expert id: slot s takes the place given by the number of the
     // token's slots that come before it (smaller id, or the same id and a smaller k).
     for (int s = tid; s < T * K; s += 1024) {
@@ -341,6 +375,29 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
             rank += (ej < e || (ej == e && j < k)) ? 1 : 0;
         }
         order[t * K + rank] = (e < e_lo || e >= e_hi) ? -1 - s : s;   // slots of experts held elsewhere take no part in this rank's sum
+    }
+    if (!split.ranges) return;
+    // every boundary by bisection over the running weights
+    const int n_items = routed_items + shared_items;
+    __syncthreads();
+    if (tid <= split.blocks && n_items > 0) {
+        const int tpe = split.tasks_per_expert;
+        const int last_w = shared_items ? weight_of(min(tpi, T - (shared_items - 1) * tpi)) : 0;
+        const unsigned total_w = unsigned(shared_items ? wgt[n_items - 1] + last_w : routed_weight);
+        if (tid == split.blocks) {
+            split.ranges[tid] = n_items * tpe;
+        } else {
+            const unsigned target = unsigned((unsigned long long)total_w * unsigned(tpe) * unsigned(tid) / unsigned(split.blocks));
+            int lo = 0, hi = n_items - 1;   // the last item whose tasks begin at or before the target
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (unsigned(wgt[mid]) * unsigned(tpe) <= target) lo = mid;
+                else hi = mid - 1;
+            }
+            const unsigned wi = (lo + 1 < n_items ? unsigned(wgt[lo + 1]) : total_w) - unsigned(wgt[lo]);   // the item's own weight
+            const int task = int((target - unsigned(wgt[lo]) * unsigned(tpe)) / wi);
+            split.ranges[tid] = lo * tpe + min(task, tpe - 1);
+        }
     }
 }
 
@@ -356,7 +413,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
                                                    size_t stride, const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                    int* __restrict__ status, int32_t* __restrict__ order, int max_items,
                                                    const float* __restrict__ x, int n, size_t n_blocks, int8_t* __restrict__ xq,
-                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi) {
+                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi, DownSplit split) {
     extern __shared__ unsigned long long dyn[];
     pdl_wait();
     pdl_trigger();
@@ -372,7 +429,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
             route_warp<V>(logits + size_t(t) * E, E, K, lane, ids + size_t(t) * K, wts + size_t(t) * K, nullptr, nullptr);
     }
     cluster_sync_all();   // every block's ids are visible to block 0
-    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi);
+    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi, true, split);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -416,6 +473,12 @@ struct StreamParams {
     int block64;       // hidden rows quantized with one scale per 64 values (moe_q2::run's block64 option)
     int y_bf16;        // down: y holds bf16 rows (moe_q2::run's yd_bf16 option)
     int narrow;        // items of at most kNarrowTok tokens take units_mma_narrow (results are the same bits either way)
+    unsigned long long* stamps;   // measurement aid (else null): per block four globaltimer values, see frx_debug_set_stream_stamps
+    const int* ranges; // down: block b takes the tasks [ranges[b], ranges[b + 1]) (else null: an even split)
+    int from_gu;       // down: item buffers are built from gu (SwiGLU and quantization on the way), there is no separate quantizer launch
+    int* cnt;          // k_ffn: per item, the gate/up tasks finished so far
+    int cpt_dn;        // k_ffn: chunks per down task (cpt: per gate/up task)
+    int nbuf_dn;       // k_ffn: item buffers of the down half (nbuf: of the gate/up half)
 };
 
 // Shared-memory plan of k_stream. The activation operand of an item (fragments, scales, biases,
@@ -528,7 +591,7 @@ __device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uin
 // additions per (row, token) are those of units_mma: the results are the same bits.
 // The item buffer must have been built for the narrow form (see build in k_stream): zeros in token
 // columns 4..7 of the B fragments, scale and bias entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1.
-template <int UPC>
+template <int UPC, int BS = 32>   // BS: 16-byte vectors per block of the B fragments (32: eight token columns; 16: four)
 __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
                                                  const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
                                                  const int4* __restrict__ ci, int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
@@ -536,10 +599,13 @@ __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ uni
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint8_t* codes = units + lane * 16;
     const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
-    const uint4* bf0_p = bfrag + b0 * 32 + g * 4 + t4;               // column g: token g, or zeros for g >= 4
-    const uint4* bf1_p = bfrag + b0 * 32 + ((g + 4) & 7) * 4 + t4;   // column g + 4 (mod 8): zeros for g < 4, else token g - 4
-    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
-    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
+    // B operand: lanes g < 4 carry token g for row group 0 and zeros for row group 1, lanes g >= 4
+    // zeros for group 0 and token g - 4 for group 1. The zeros never change, so each lane loads only
+    // its live fragment (a predicated load: half the shared-memory traffic of two full loads).
+    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 3) * 4 + t4);
+    const bool low = g < 4;
+    uint4 bfa = make_uint4(0u, 0u, 0u, 0u), bfb = bfa;
+    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + (b0 * 4 + t4) * 2);   // -(kMagic + sum of the codes), see build
     const ulonglong2* da_p = da + b0 * 4 + t4;
     const int n_units = UPC ? UPC : count;
 #pragma unroll(2)
@@ -550,20 +616,21 @@ __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ uni
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int b = 2 * u + j;
-            const uint4 bfa = bf0_p[b * 32], bfb = bf1_p[b * 32];
-            const int4 cq = ci_p[b * 8];   // {c0, c1} of the first half of the block, {c0, c1} of the second
+            lds128_if(bfa, bf_a + b * (BS * 16), low);
+            lds128_if(bfb, bf_a + b * (BS * 16), !low);
+            const ulonglong2 nm = nm_p[b * 8];   // {first half: columns c0, c1}, {second half}
             const ulonglong2 a = da_p[b * 4];
             const uint32_t w0 = j ? c0.y : c0.x, w1 = j ? c0.w : c0.z;   // group 0: rows g, g + 8
             const uint32_t x0 = j ? c1.y : c1.x, x1 = j ? c1.w : c1.z;   // group 1
             const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
             uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq.x, cq.y);
-            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq.z, cq.w);
+            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, kMagicBits);
+            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, kMagicBits);
             const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
             const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
             const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
-            const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
-            const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+            const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
+            const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
             float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
             unpack2(sumi_lo, s0, s1);
             unpack2(sumi_hi, s2, s3);
@@ -579,7 +646,7 @@ __device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ uni
 // `units` points at the first unit of group 0 of the chunk, group j follows at j * gstride. The item
 // buffer is in the narrow form (zeros in token column 4; scale and bias entries of tokens 0, 1 at
 // the quad of lanes t4 = 0). Same products, same scaling, same order of additions per (row, token).
-template <int UPC>
+template <int UPC, int BS = 32>
 __device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
                                              const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
                                              int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
@@ -587,12 +654,14 @@ __device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, 
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint8_t* codes = units + lane * 16;
     const uint8_t* scales = units + t4 * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
-    const uint4* bf_p[4];
+    // B operand of row group j: token g & 1 in the lanes with g >> 1 == j, zeros elsewhere; a lane loads
+    // only its live fragment, the zeros of the other three stay in registers
+    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 1) * 4 + t4);
+    uint4 bf[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) bf_p[j] = bfrag + b0 * 32 + ((g >> 1) == j ? (g & 1) : 4) * 4 + t4;   // column 4: zeros
-    const int4* ci_p = ci + b0 * 8;
+    for (int j = 0; j < 4; ++j) bf[j] = make_uint4(0u, 0u, 0u, 0u);
+    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + b0 * 8);
     const ulonglong2* da_p = da + b0 * 4;
-    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
     const int n_units = UPC ? UPC : count;
 #pragma unroll(1)
     for (int u = 0; u < n_units; ++u) {
@@ -603,16 +672,16 @@ __device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, 
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
             const int b = 2 * u + jj;
-            const int4 cq = ci_p[b * 8];
+            const ulonglong2 nm = nm_p[b * 8];
             const ulonglong2 a = da_p[b * 4];
             uint32_t a0[16], a1[16], bb0[8], bb1[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint4 bf = bf_p[j][b * 32];
-                bb0[2 * j] = bf.x;
-                bb0[2 * j + 1] = bf.y;
-                bb1[2 * j] = bf.z;
-                bb1[2 * j + 1] = bf.w;
+                lds128_if(bf[j], bf_a + b * (BS * 16), (g >> 1) == j);
+                bb0[2 * j] = bf[j].x;
+                bb0[2 * j + 1] = bf[j].y;
+                bb1[2 * j] = bf[j].z;
+                bb1[2 * j + 1] = bf[j].w;
                 const uint32_t w0 = jj ? c[j].y : c[j].x, w1 = jj ? c[j].w : c[j].z;
                 const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
                 a0[4 * j] = w0 & M0;
@@ -625,13 +694,13 @@ __device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, 
                 a1[4 * j + 3] = v1 & M1;
             }
             uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_chain4(lo0, hi0, a0, bb0, cq.x, cq.y);
-            mma_u8s8_chain4(lo1, hi1, a1, bb1, cq.z, cq.w);
+            mma_u8s8_chain4(lo0, hi0, a0, bb0, kMagicBits);
+            mma_u8s8_chain4(lo1, hi1, a1, bb1, kMagicBits);
             const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
             const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
             const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
-            const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
-            const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+            const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
+            const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
             float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
             unpack2(sumi_lo, s0, s1);
             unpack2(sumi_hi, s2, s3);
@@ -643,7 +712,7 @@ __device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, 
 
 // Four row groups as two pairs in the narrow form (items of three or four tokens): the activation
 // fragments, scales and biases of a block are loaded once and serve both pairs.
-template <int UPC>
+template <int UPC, int BS = 32>
 __device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
                                                const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
                                                int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
@@ -651,11 +720,11 @@ __device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units
     constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
     const uint8_t* codes = units + lane * 16;
     const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // pair 0; pair 1 two groups on
-    const uint4* bf0_p = bfrag + b0 * 32 + g * 4 + t4;
-    const uint4* bf1_p = bfrag + b0 * 32 + ((g + 4) & 7) * 4 + t4;
-    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
+    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 3) * 4 + t4);   // as in units_mma_narrow
+    const bool low = g < 4;
+    uint4 bfa = make_uint4(0u, 0u, 0u, 0u), bfb = bfa;
+    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + (b0 * 4 + t4) * 2);
     const ulonglong2* da_p = da + b0 * 4 + t4;
-    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
     const int n_units = UPC ? UPC : count;
 #pragma unroll(1)
     for (int u = 0; u < n_units; ++u) {
@@ -668,8 +737,9 @@ __device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
             const int b = 2 * u + jj;
-            const uint4 bfa = bf0_p[b * 32], bfb = bf1_p[b * 32];
-            const int4 cq = ci_p[b * 8];
+            lds128_if(bfa, bf_a + b * (BS * 16), low);
+            lds128_if(bfb, bf_a + b * (BS * 16), !low);
+            const ulonglong2 nm = nm_p[b * 8];
             const ulonglong2 a = da_p[b * 4];
 #pragma unroll
             for (int pi = 0; pi < 2; ++pi) {
@@ -678,18 +748,93 @@ __device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units
                 const uint32_t x0 = jj ? c1.y : c1.x, x1 = jj ? c1.w : c1.z;
                 const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
                 uint64_t lo0, hi0, lo1, hi1;
-                mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, cq.x, cq.y);
-                mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, cq.z, cq.w);
+                mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, kMagicBits);
+                mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, kMagicBits);
                 const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[pi].x), s_hi = *reinterpret_cast<const __half2*>(&sc[pi].y);
                 const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
                 const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
-                const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
-                const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
+                const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
+                const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
                 float s0, s1, s2, s3;
                 unpack2(sumi_lo, s0, s1);
                 unpack2(sumi_hi, s2, s3);
                 acc_lo[pi] = add2(acc_lo[pi], pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
                 acc_hi[pi] = add2(acc_hi[pi], pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
+            }
+        }
+    }
+}
+
+// The narrow forms start their accumulators at kMagicBits and add -(kMagic + sum of the codes) in
+// float (exact: both are integers below 2^24); `c` is the wide form's accumulator input,
+// kMagicBits - sum as an int32 behind a float pointer.
+__device__ __forceinline__ float narrow_bias(float c) { return -(kMagic + float(kMagicBits - __float_as_int(c))); }
+
+// The item buffer of a down item in the narrow form (B fragments of the item's at most kNarrowTok
+// tokens, BS 16-byte vectors per block; scales; -(kMagic + sum of the codes)) straight from the
+// (gate x, up x) pairs of the item's slots: h = silu(gate x) * up x is formed here and quantized as
+// k_quant_hidden does (quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id),
+// d through fp16). A thread owns four consecutive values, eight neighbouring lanes one 32-block;
+// thread btid of NT (whole warps) takes part. The pairs were written by other SMs, during this
+// kernel or the one before: they are read from the L2.
+template <int BS>
+__device__ __noinline__ void build_hidden_narrow(const float2* __restrict__ gu, int ff, const Item* __restrict__ it, uint32_t* bw,
+                                                    float* daw, float* ciw, int btid, int NT) {
+    const int m = min(it->n_tok, kNarrowTok);
+    const int qpr = ff / 4, total = m * qpr;   // quads per row (a multiple of 32: whole warps stay together)
+    constexpr int kBatch = 2;                  // loads of this many quads are in flight together
+    for (int base = 0; base < total; base += kBatch * NT) {
+        float4 g0[kBatch], g1[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const int idx = base + k * NT + btid;
+            if (idx < total) {
+                const int g = idx / qpr, rq = idx - g * qpr;
+                const float4* src = reinterpret_cast<const float4*>(gu + size_t(it->slot[g]) * ff + size_t(rq) * 4);
+                g0[k] = __ldcg(src);
+                g1[k] = __ldcg(src + 1);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            if (base + k * NT >= total) break;   // uniform for the warp
+            const int idx = base + k * NT + btid;
+            const bool live = idx < total;
+            const int g = live ? idx / qpr : 0, rq = live ? idx - g * qpr : 0;
+            float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (live) {
+                hv[0] = swiglu_ref(g0[k].x, g0[k].y);
+                hv[1] = swiglu_ref(g0[k].z, g0[k].w);
+                hv[2] = swiglu_ref(g1[k].x, g1[k].y);
+                hv[3] = swiglu_ref(g1[k].z, g1[k].w);
+            }
+            float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            const float d = __fdiv_rn(am, 127.0f);
+            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+            int code[4], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
+                sum += code[i];
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (live) {
+                const int rb = rq >> 3, j = rq & 7, b = rb >> 1, h = rb & 1, hi = j >> 2, t = j & 3;
+                bw[(b * BS + g * 4 + t) * 4 + h * 2 + hi] =
+                    uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
+                if (j == 0) {
+                    const float ds = __half2float(__float2half_rn(d));
+                    const float av = h ? ds * 0.0625f : ds, nv = -(kMagic + float(h ? 16 * sum : sum));
+                    const int dst = (b * 4 + (g >> 1)) * 4 + h * 2 + (g & 1);
+                    daw[dst] = av;
+                    daw[dst + 8] = av;
+                    const int cq = (b * 4 + (g >> 1)) * 8 + h * 2 + (g & 1);
+                    ciw[cq] = nv;
+                    ciw[cq + 16] = nv;
+                }
             }
         }
     }
@@ -707,9 +852,9 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     // the hidden-row quantizer, which itself started only after gate/up and therefore after the
     // items were complete: down reads the items and starts streaming its weights (constant data)
     // while the quantizer is still running, and waits for it only before it touches the hidden rows.
-    if (GATE_UP) pdl_wait();
-    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* stamp = p.stamps ? p.stamps + size_t(blockIdx.x) * 4 : nullptr;
+    if (stamp && threadIdx.x == 0) stamp[0] = global_ns();   // the block has started
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
     const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
@@ -729,12 +874,30 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;            // this warp's slots
     volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
 
+    if (threadIdx.x == 0) {   // (before the wait: this needs nothing from the kernels in front)
+        for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
+        for (int b = 0; b < kMaxItemBufs; ++b) {
+            mbar_init(ready + b, NW);
+            mbar_init(done + b, NW);
+        }
+        *abort = 0;
+        mbar_fence_init();
+    }
+    // The next kernel may be scheduled from here on. (Gate/up says so only after its own wait: what
+    // follows it, down included, then starts after the item list is complete. Letting every kernel of
+    // the chain say so first thing was measured: no gain at batch 64, a loss at small batches.)
+    if (GATE_UP) pdl_wait();
+    pdl_trigger();
     // (down, before its wait: the item list was complete and flushed to the L2 before the kernel in
     // front of this one began, but the same addresses are rewritten every layer, so the reads
     // bypass this SM's L1, which may still hold the previous layer's lines)
     const int n_items = GATE_UP ? p.status[1] : *reinterpret_cast<const volatile int*>(p.status + 1);
     const long long total = (long long)n_items * tasks_per_expert;
-    const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    if (!GATE_UP && p.ranges && n_items > 0) {   // a split by weight, made by the grouping kernel
+        lo = *reinterpret_cast<const volatile int*>(p.ranges + blockIdx.x);
+        hi = *reinterpret_cast<const volatile int*>(p.ranges + blockIdx.x + 1);
+    }
     const int ntasks = int(hi - lo);
     if (ntasks <= 0) {   // uniform for the block
         if (!GATE_UP) pdl_wait();   // keeps "this grid has ended" meaning "every kernel before it has ended"
@@ -745,15 +908,6 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         return *reinterpret_cast<const uint8_t* const volatile*>(&p.items[item].blob);
     };
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
-        for (int b = 0; b < kMaxItemBufs; ++b) {
-            mbar_init(ready + b, NW);
-            mbar_init(done + b, NW);
-        }
-        *abort = 0;
-        mbar_fence_init();
-    }
     __syncthreads();
 
     // ---- this warp's stream of chunks. Task i of the block (i = warp, warp + NW, ...) is fetched as
@@ -831,11 +985,13 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
         const int m = it->n_tok;
         const bool narrow = m <= kNarrowTok && p.narrow;   // see units_mma_narrow
-        // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
         const int NT = bthreads;
+        if (!GATE_UP && p.from_gu) {   // the hidden rows are made here (every item is narrow then)
+            build_hidden_narrow<32>(p.gu, p.ff, it, bw, daw, ciw, btid, NT);
+            return;
+        }
+        // column g of the B fragments, scales and biases <- activation row of the item's g-th slot
         const int vpr = nb * 4;   // 16-byte vectors per row
-        if (narrow)   // token columns 4..7 of every block hold zeros
-            for (int idx = btid; idx < nb * 16; idx += NT) reinterpret_cast<uint4*>(bw)[(idx >> 4) * 32 + 16 + (idx & 15)] = make_uint4(0u, 0u, 0u, 0u);
         for (int base = btid; base < m * vpr; base += 4 * NT) {
             uint4 v[4];
 #pragma unroll
@@ -867,11 +1023,14 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
             // the MMA's accumulator input of this block half: {c0, c1, c0, c1} for the lane's two token columns and both row halves
             const float cv = p.ac[row * (nb * 2) + r];
             if (narrow) {
-                // one quad per (block, t4): {c0, c1} of the first half, {c0, c1} of the second; lanes
-                // t4 = 2, 3 work on the same tokens as t4 = 0, 1 (for the second row group)
+                // one quad per (block, t4): -(kMagic + sum of the codes) for {c0, c1} of the first half and
+                // {c0, c1} of the second (the sum times 16 there): the accumulators start at kMagicBits and
+                // this is added to them as floats. Lanes t4 = 2, 3 work on the same tokens as t4 = 0, 1
+                // (for the second row group).
+                const float nv = narrow_bias(cv);
                 const int cq = (b * 4 + (g >> 1)) * 8 + s * 2 + (g & 1);
-                ciw[cq] = cv;
-                ciw[cq + 16] = cv;
+                ciw[cq] = nv;
+                ciw[cq + 16] = nv;
                 daw[dst + 8] = av;
             } else {
                 const int cq = ((b * 4 + (g >> 1)) * 2 + s) * 4 + (g & 1);
@@ -902,6 +1061,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     };
     const int ahead = nbuf - 1;
     if (!GATE_UP) pdl_wait();   // the first weight chunks are already in flight
+    if (stamp && threadIdx.x == 0) stamp[1] = global_ns();   // the kernels in front have ended, the first copies are issued
     if (ahead == 2 && nseg >= 2) {   // the first two items side by side: one half of the warps each
         constexpr int H = NW / 2;
         build(warp < H ? 0 : 1, warp < H ? ctid : ctid - H * 32, warp < H ? H * 32 : (NW - H) * 32);
@@ -920,6 +1080,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     for (int q = 0; q < nseg; ++q) {
         const int item = first_item + q, buf = q % nbuf;
         mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort, p.wait_ns);
+        if (stamp && q == 0 && threadIdx.x == 0) stamp[2] = global_ns();   // the first item buffer is built
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
         const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da + buf * (nb * 64));
@@ -1077,6 +1238,412 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
             build(q + ahead, ctid, NW * 32);
             __syncwarp();
             if (lane == 0) mbar_arrive(ready + nxt);
+        }
+    }
+    __syncthreads();
+    if (stamp && threadIdx.x == 0) stamp[3] = global_ns();   // every warp of the block has finished
+    if (*abort) {
+        // A wait ran out: report it, and give copies still in flight time to land before the
+        // block's shared memory is released.
+        if (threadIdx.x == 0) p.status[0] = kDevWaitTimeout;
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) {
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The decode FFN as one kernel (items of at most kNarrowTok tokens): gate/up, then SwiGLU and the
+// quantization of the hidden rows, then down, with one ring of weight chunks per warp that is never
+// drained in between.
+//   A block owns the same share of the gate/up tasks and of the down tasks (roughly the same
+//   items). Its warps take the block's tasks round-robin over the whole sequence: first the gate/up
+//   tasks in item order, then the down tasks. A gate/up task is two row groups in chunks of four
+//   units of K, a down task four row groups in chunks of two units: the same 8 units = 4,608 bytes.
+//   A warp that has finished its gate/up tasks of an item adds their number to the item's counter
+//   (release). The hidden rows of an item are complete when its counter has reached the number of
+//   gate/up tasks of an expert; whoever builds a down item waits for that (acquire, bounded), reads
+//   the (gate x, up x) pairs of the item's slots, forms silu(gate x) * up x, quantizes it like
+//   k_quant_hidden and writes codes, scales and accumulator inputs straight into the item buffer.
+//   (Letting one warp build a whole item buffer, the first to get there, instead of all warps in
+//   shares, was measured and is slower: the lone builder's global-memory round trips are serial.)
+//   A block walks its down items starting from its second one: the first is shared with the block
+//   before, which reaches it last in its own gate/up pass, the last is shared with the block after,
+//   which took it first.
+// Blocks wait for counters that other blocks raise, so every block must be resident: the grid is
+// one block per SM (checked on the host), and every wait is bounded.
+// Products, scaling and the order of additions are those of k_stream: the same bits.
+constexpr int kMaxItemBufs4 = 4;                 // item buffers per half, at most
+constexpr int kFfnBS = 16;                       // 16-byte vectors per block of the B fragments: token columns 0..3
+constexpr uint32_t kFfnBfragBlock = kFfnBS * 16;
+struct FfnPlan {
+    uint32_t ring, g_bfrag, g_da, g_ci, g_item, d_bfrag, d_da, d_ci, d_item, bars, abort, total;
+};
+__host__ __device__ inline FfnPlan ffn_plan(int n, int ff, uint32_t chunk_bytes, int slots, int nbuf_g, int nbuf_d) {
+    const uint32_t nbg = uint32_t(n / kQK), nbd = uint32_t(ff / kQK);
+    FfnPlan s{};
+    uint32_t off = 0;
+    s.ring = off;
+    off += uint32_t(slots) * chunk_bytes;
+    off = (off + 127u) & ~127u;
+    s.g_bfrag = off;
+    off += uint32_t(nbuf_g) * nbg * kFfnBfragBlock;
+    s.g_da = off;
+    off += uint32_t(nbuf_g) * nbg * 64;
+    s.g_ci = off;
+    off += uint32_t(nbuf_g) * nbg * 128;
+    s.g_item = off;
+    off += uint32_t(nbuf_g) * 64;
+    s.d_bfrag = off;
+    off += uint32_t(nbuf_d) * nbd * kFfnBfragBlock;
+    s.d_da = off;
+    off += uint32_t(nbuf_d) * nbd * 64;
+    s.d_ci = off;
+    off += uint32_t(nbuf_d) * nbd * 128;
+    s.d_item = off;
+    off += uint32_t(nbuf_d) * 64;
+    s.bars = off;          // `slots` ring barriers, then ready/done of the gate/up buffers, then of the down buffers
+    off += uint32_t(slots + 4 * kMaxItemBufs4) * 8;
+    off = (off + 15u) & ~15u;
+    s.abort = off;
+    off += 16;
+    s.total = off;
+    return s;
+}
+constexpr int kFfnUnitsGu = 4, kFfnUnitsDn = 2;   // units of K per chunk and row group
+constexpr uint32_t kFfnChunkBytes = 2 * kFfnUnitsGu * kUnitBytes;
+static_assert(kFfnChunkBytes == 4 * kFfnUnitsDn * kUnitBytes, "one ring slot serves both halves");
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 1) k_ffn(const StreamParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ctid = threadIdx.x;
+    const int nb_g = p.n / kQK, units_g = p.n / kUnitK, nb_d = p.ff / kQK, units_d = p.ff / kUnitK;
+    const uint32_t gbytes_g = uint32_t(units_g) * kUnitBytes, gbytes_d = uint32_t(units_d) * kUnitBytes;   // one row group
+    const int cpt_g = units_g / kFfnUnitsGu, cpt_d = units_d / kFfnUnitsDn, rpw = p.rpw;
+    constexpr uint32_t chunk_bytes = kFfnChunkBytes, half_bytes = chunk_bytes / 2, quarter_bytes = chunk_bytes / 4;
+    const int tpe_g = p.ff / 16, tpe_d = p.n / 64;   // tasks per expert
+    const size_t section_d = size_t(p.ff / 8) * gbytes_g;   // the down rows follow the gate/up groups in a blob
+    const int slots = NW * rpw, nbuf_g = p.nbuf, nbuf_d = p.nbuf_dn;
+    const FfnPlan sp = ffn_plan(p.n, p.ff, chunk_bytes, slots, nbuf_g, nbuf_d);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + sp.bars);
+    uint64_t* ready_g = bars + slots;
+    uint64_t* done_g = ready_g + kMaxItemBufs4;
+    uint64_t* ready_d = done_g + kMaxItemBufs4;
+    uint64_t* done_d = ready_d + kMaxItemBufs4;
+    uint64_t* full = bars + warp * rpw;                                   // this warp's ring barriers
+    uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;    // this warp's ring slots
+    volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < slots; ++s) mbar_init(bars + s, 1);
+        for (int b = 0; b < 4 * kMaxItemBufs4; ++b) mbar_init(ready_g + b, NW);
+        *abort = 0;
+        mbar_fence_init();
+    }
+    pdl_wait();   // the items, the counters (zeroed) and the quantized x are complete
+    pdl_trigger();
+
+    const int n_items = p.status[1];
+    const long long tot_g = (long long)n_items * tpe_g, tot_d = (long long)n_items * tpe_d;
+    const long long lo_g = tot_g * blockIdx.x / gridDim.x, hi_g = tot_g * (blockIdx.x + 1) / gridDim.x;
+    const long long lo_d = tot_d * blockIdx.x / gridDim.x, hi_d = tot_d * (blockIdx.x + 1) / gridDim.x;
+    const int nt_g = int(hi_g - lo_g), nt_d = int(hi_d - lo_d);
+    if (nt_g + nt_d <= 0) return;   // uniform for the block
+    // segments: runs of consecutive tasks of one item
+    const int fi_g = nt_g > 0 ? int(lo_g / tpe_g) : 0, nseg_g = nt_g > 0 ? int((hi_g - 1) / tpe_g) - fi_g + 1 : 0;
+    const int fi_d = nt_d > 0 ? int(lo_d / tpe_d) : 0, nseg_d = nt_d > 0 ? int((hi_d - 1) / tpe_d) - fi_d + 1 : 0;
+    const int rot_d = nseg_d > 1 ? 1 : 0;
+    const int ahead_g = nbuf_g - 1, ahead_d = nbuf_d - 1;
+    __syncthreads();
+    auto item_d = [&](int s) { return fi_d + (s + rot_d) % nseg_d; };   // the item of the s-th down segment in walking order
+    auto seg_g = [&](int s, long long& a, int& len) {
+        const long long it = fi_g + s;
+        a = max(lo_g, it * tpe_g);
+        len = int(min(hi_g, (it + 1) * tpe_g) - a);
+    };
+    auto seg_d = [&](int s, long long& a, int& len) {
+        const long long it = item_d(s);
+        a = max(lo_d, it * tpe_d);
+        len = int(min(hi_d, (it + 1) * tpe_d) - a);
+    };
+
+    // ---- this warp's stream of chunks (lane 0 issues). The block's tasks are numbered through both
+    // halves; task i belongs to warp i % NW. is_j: index of the task within its half.
+    int is_ph = 0, is_s = -1, is_off = 0, is_len = 0, is_j = warp, is_c = 0, is_slot = 0, is_task = 0;
+    long long is_a = 0;
+    const uint8_t* is_blob = nullptr;
+    auto is_seek = [&]() {   // to the segment that holds task is_j of half is_ph, or on to the next half; is_ph = 2: nothing left
+        while (is_ph < 2) {
+            if (is_s >= 0 && is_j < is_off + is_len) {
+                is_task = int((is_a + (is_j - is_off)) % (is_ph ? tpe_d : tpe_g));
+                return;
+            }
+            if (is_s + 1 < (is_ph ? nseg_d : nseg_g)) {
+                ++is_s;
+                is_off += is_len;
+                if (is_ph) seg_d(is_s, is_a, is_len);
+                else seg_g(is_s, is_a, is_len);
+                is_blob = p.items[is_ph ? item_d(is_s) : fi_g + is_s].blob + (is_ph ? section_d : size_t(0));
+            } else {
+                ++is_ph;
+                is_s = -1;
+                is_off = 0;
+                is_len = 0;
+                is_j = ((warp - nt_g) % NW + NW) % NW;   // the first down task of this warp
+            }
+        }
+    };
+    auto issue_next = [&]() {   // lane 0 only
+        if (is_ph >= 2) return;
+        mbar_expect_tx(full + is_slot, chunk_bytes);
+        uint8_t* dst = ring + size_t(is_slot) * chunk_bytes;
+        int cpt;
+        if (is_ph == 0) {   // the same K range of the task's two groups
+            const uint8_t* src = is_blob + size_t(is_task) * (2 * gbytes_g) + size_t(is_c) * half_bytes;
+            bulk_g2s(dst, src, half_bytes, full + is_slot);
+            bulk_g2s(dst + half_bytes, src + gbytes_g, half_bytes, full + is_slot);
+            cpt = cpt_g;
+        } else {            // of the task's four groups
+            const uint8_t* src = is_blob + size_t(is_task) * (4 * gbytes_d) + size_t(is_c) * quarter_bytes;
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) bulk_g2s(dst + gq * quarter_bytes, src + size_t(gq) * gbytes_d, quarter_bytes, full + is_slot);
+            cpt = cpt_d;
+        }
+        if (++is_slot == rpw) is_slot = 0;
+        if (++is_c == cpt) {
+            is_c = 0;
+            is_j += NW;
+            is_seek();
+        }
+    };
+    if (lane == 0) {
+        is_seek();
+        for (int k = 0; k < rpw; ++k) issue_next();
+    }
+    int cs_slot = 0;
+    uint32_t cs_phase = 0;
+    auto chunk_wait = [&]() -> const uint8_t* {
+        mbar_wait_bounded(full + cs_slot, cs_phase, abort, p.wait_ns);
+        return ring + size_t(cs_slot) * chunk_bytes;
+    };
+    auto chunk_done = [&]() {
+        __syncwarp();
+        if (lane == 0) issue_next();
+        if (++cs_slot == rpw) {
+            cs_slot = 0;
+            cs_phase ^= 1u;
+        }
+    };
+
+    // ---- item buffers. gate/up: column g of the B fragments, scales and accumulator inputs <- the
+    // quantized x row of the item's g-th token, in the narrow form (zeros in token columns 4..7, the
+    // entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1).
+    auto build_x = [&](int s, int btid, int NT) {
+        const Item* it = p.items + fi_g + s;
+        const int buf = s % nbuf_g;
+        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.g_bfrag + buf * (nb_g * kFfnBfragBlock));
+        float* daw = reinterpret_cast<float*>(smem + sp.g_da + buf * (nb_g * 64));
+        float* ciw = reinterpret_cast<float*>(smem + sp.g_ci + buf * (nb_g * 128));
+        if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.g_item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
+        const int m = min(it->n_tok, kNarrowTok);
+        const int vpr = nb_g * 4;   // 16-byte vectors per row
+        for (int base = btid; base < m * vpr; base += 4 * NT) {
+            uint4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = base + k * NT;
+                if (idx < m * vpr) {
+                    const int g = idx / vpr, r = idx % vpr;
+                    v[k] = reinterpret_cast<const uint4*>(p.aq + size_t(slot_token(it->slot[g], p.K, p.TK)) * p.n)[r];
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = base + k * NT;
+                if (idx < m * vpr) {
+                    const int g = idx / vpr, r = idx % vpr;
+                    reinterpret_cast<uint4*>(bw)[(r >> 2) * kFfnBS + g * 4 + (r & 3)] = v[k];
+                }
+            }
+        }
+        for (int idx = btid; idx < m * nb_g * 2; idx += NT) {
+            const int g = idx / (nb_g * 2), r = idx % (nb_g * 2), b = r >> 1, h = r & 1;
+            const size_t row = size_t(slot_token(it->slot[g], p.K, p.TK));
+            const float av = p.aa[row * (nb_g * 2) + r], cv = p.ac[row * (nb_g * 2) + r];
+            const int dst = (b * 4 + (g >> 1)) * 4 + h * 2 + (g & 1);
+            daw[dst] = av;
+            daw[dst + 8] = av;
+            const float nv = narrow_bias(cv);
+            const int cq = (b * 4 + (g >> 1)) * 8 + h * 2 + (g & 1);
+            ciw[cq] = nv;
+            ciw[cq + 16] = nv;
+        }
+    };
+    // down: the same form from the item's hidden rows, which are made here from the (gate x, up x)
+    // pairs. A thread owns four consecutive values, eight neighbouring lanes one 32-block.
+    auto build_h = [&](int s, int btid, int NT) {
+        const int item = item_d(s);
+        const Item* it = p.items + item;
+        const int buf = s % nbuf_d;
+        if (lane == 0) {   // every gate/up task of the item has been counted
+            const int* c = p.cnt + item;
+            if (ld_acquire_gpu(c) < tpe_g && !*abort) {
+                uint64_t t0 = 0;
+                for (uint32_t polls = 1;; ++polls) {
+                    if (ld_acquire_gpu(c) >= tpe_g) break;
+                    __nanosleep(polls > 16 ? 200 : 40);
+                    if ((polls & 31u) == 0) {
+                        if (*abort) break;
+                        const uint64_t now = global_ns();
+                        if (t0 == 0) {
+                            t0 = now;
+                        } else if (now - t0 > p.wait_ns) {
+                            *abort = 1;
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.d_bfrag + buf * (nb_d * kFfnBfragBlock));
+        float* daw = reinterpret_cast<float*>(smem + sp.d_da + buf * (nb_d * 64));
+        float* ciw = reinterpret_cast<float*>(smem + sp.d_ci + buf * (nb_d * 128));
+        if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.d_item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
+        build_hidden_narrow<kFfnBS>(p.gu, p.ff, it, bw, daw, ciw, btid, NT);
+    };
+
+    auto out_row = [&](int sl) -> float* { return sl >= p.TK ? p.ysh + size_t(sl - p.TK) * p.n : p.y + size_t(sl) * p.n; };
+    auto put2 = [&](float* o, int row, float v0, float v8) {
+        o[row] = v0;
+        o[row + 8] = v8;
+    };
+    const int g = lane >> 2, t4 = lane & 3;
+
+    // ---- gate/up
+    if (ahead_g == 2 && nseg_g >= 2) {   // the first two items side by side, one half of the warps each
+        constexpr int H = NW / 2;
+        build_x(warp < H ? 0 : 1, warp < H ? ctid : ctid - H * 32, warp < H ? H * 32 : (NW - H) * 32);
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(ready_g + 0);
+            mbar_arrive(ready_g + 1);
+        }
+    } else {
+        for (int q = 0; q < ahead_g && q < nseg_g; ++q) {
+            build_x(q, ctid, NW * 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready_g + q % nbuf_g);
+        }
+    }
+    int off = 0;
+    for (int s = 0; s < nseg_g; ++s) {
+        const int buf = s % nbuf_g;
+        mbar_wait_bounded(ready_g + buf, uint32_t(s / nbuf_g) & 1u, abort, p.wait_ns);
+        long long a;
+        int len;
+        seg_g(s, a, len);
+        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.g_bfrag + buf * (nb_g * kFfnBfragBlock));
+        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.g_da + buf * (nb_g * 64));
+        const int4* ci = reinterpret_cast<const int4*>(smem + sp.g_ci + buf * (nb_g * 128));
+        const Item* its = reinterpret_cast<const Item*>(smem + sp.g_item + buf * 64);
+        const int m = its->n_tok;
+        const int c0 = 2 * (t4 & 1), c1 = c0 + 1, rn = t4 >> 1;
+        int mine = 0;
+        for (int j = off + ((warp - off % NW) % NW + NW) % NW; j < off + len; j += NW) {
+            const int task = int((a + (j - off)) % tpe_g);
+            uint64_t acc_lo = 0ull, acc_hi = 0ull;
+            for (int c = 0; c < cpt_g; ++c) {
+                const uint8_t* cp = chunk_wait();
+                units_mma_narrow<kFfnUnitsGu, kFfnBS>(cp, half_bytes, kFfnUnitsGu, 2 * c * kFfnUnitsGu, bfrag, da, ci, lane, acc_lo, acc_hi);
+                chunk_done();
+            }
+            float sum[4];
+            unpack2(acc_lo, sum[0], sum[1]);
+            unpack2(acc_hi, sum[2], sum[3]);
+            const int row = (task * 2 + rn) * 8 + g;
+            if (c0 < m) p.gu[size_t(its->slot[c0]) * p.ff + row] = make_float2(sum[0], sum[2]);
+            if (c1 < m) p.gu[size_t(its->slot[c1]) * p.ff + row] = make_float2(sum[1], sum[3]);
+            ++mine;
+        }
+        off += len;
+        __syncwarp();
+        if (lane == 0) {
+            if (mine) red_release_gpu_add(p.cnt + fi_g + s, mine);   // this warp's rows of the item are written
+            mbar_arrive(done_g + buf);
+        }
+        if (s + ahead_g < nseg_g) {
+            const int nxt = (s + ahead_g) % nbuf_g;   // the buffer of segment s - 1
+            if (s >= 1) mbar_wait_bounded(done_g + nxt, uint32_t((s - 1) / nbuf_g) & 1u, abort, p.wait_ns);
+            build_x(s + ahead_g, ctid, NW * 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready_g + nxt);
+        }
+    }
+
+    // ---- down (this warp's weight chunks of it are already on their way)
+    for (int q = 0; q < ahead_d && q < nseg_d; ++q) {
+        build_h(q, ctid, NW * 32);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_d + q % nbuf_d);
+    }
+    off = 0;
+    for (int s = 0; s < nseg_d; ++s) {
+        const int buf = s % nbuf_d;
+        mbar_wait_bounded(ready_d + buf, uint32_t(s / nbuf_d) & 1u, abort, p.wait_ns);
+        long long a;
+        int len;
+        seg_d(s, a, len);
+        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.d_bfrag + buf * (nb_d * kFfnBfragBlock));
+        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.d_da + buf * (nb_d * 64));
+        const int4* ci = reinterpret_cast<const int4*>(smem + sp.d_ci + buf * (nb_d * 128));
+        const Item* its = reinterpret_cast<const Item*>(smem + sp.d_item + buf * 64);
+        const int m = its->n_tok;
+        for (int j = off + ((warp - (nt_g + off) % NW) % NW + NW) % NW; j < off + len; j += NW) {
+            const int task = int((a + (j - off)) % tpe_d);
+            if (m <= 2) {   // lane (g, t4) finishes row group t4 for tokens 0 and 1
+                uint64_t acc_lo = 0ull, acc_hi = 0ull;
+                for (int c = 0; c < cpt_d; ++c) {
+                    const uint8_t* cp = chunk_wait();
+                    units_mma_n2<kFfnUnitsDn, kFfnBS>(cp, quarter_bytes, kFfnUnitsDn, 2 * c * kFfnUnitsDn, bfrag, da, ci, lane, acc_lo, acc_hi);
+                    chunk_done();
+                }
+                float sum[4];
+                unpack2(acc_lo, sum[0], sum[1]);
+                unpack2(acc_hi, sum[2], sum[3]);
+                const int row = (task * 4 + t4) * 16 + g;
+                put2(out_row(its->slot[0]), row, sum[0], sum[2]);
+                if (m > 1) put2(out_row(its->slot[1]), row, sum[1], sum[3]);
+            } else {        // two pairs in the narrow form: lanes t4 = 0, 1 finish the first group of a pair, 2, 3 the second
+                uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};
+                for (int c = 0; c < cpt_d; ++c) {
+                    const uint8_t* cp = chunk_wait();
+                    units_mma_n4x2<kFfnUnitsDn, kFfnBS>(cp, quarter_bytes, kFfnUnitsDn, 2 * c * kFfnUnitsDn, bfrag, da, ci, lane, acc_lo, acc_hi);
+                    chunk_done();
+                }
+                const int t0 = 2 * (t4 & 1), t1 = t0 + 1;
+                float* o0 = t0 < m ? out_row(its->slot[t0]) : nullptr;
+                float* o1 = t1 < m ? out_row(its->slot[t1]) : nullptr;
+#pragma unroll
+                for (int pi = 0; pi < 2; ++pi) {
+                    float sum[4];
+                    unpack2(acc_lo[pi], sum[0], sum[1]);
+                    unpack2(acc_hi[pi], sum[2], sum[3]);
+                    const int row = (task * 4 + 2 * pi + (t4 >> 1)) * 16 + g;
+                    if (o0) put2(o0, row, sum[0], sum[2]);
+                    if (o1) put2(o1, row, sum[1], sum[3]);
+                }
+            }
+        }
+        off += len;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(done_d + buf);
+        if (s + ahead_d < nseg_d) {
+            const int nxt = (s + ahead_d) % nbuf_d;
+            if (s >= 1) mbar_wait_bounded(done_d + nxt, uint32_t((s - 1) / nbuf_d) & 1u, abort, p.wait_ns);
+            build_h(s + ahead_d, ctid, NW * 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ready_d + nxt);
         }
     }
     __syncthreads();
@@ -1414,6 +1981,15 @@ struct StreamCfg {
 // decode, when every item has at most four tokens: bit 0 = gate/up, bit 1 = down take tasks of four row groups
 // (k_stream's TASK4 form). Measured at batch 64: down gains from it, gate/up does not.
 int g_task4 = 2;
+int g_down_heavy = 22;  // decode: weight of a down task of an item of three or four tokens when the tasks are shared out (16 = as one of a smaller item, 0 = even split by count)
+// decode: the hidden rows are formed and quantized inside down's item-buffer build (no k_quant_hidden launch)
+// from this many tokens on. Measured (148 SMs, hidden 2048, 512 experts top-10): a gain of 2 to 3 us per layer
+// at 4, 16 and 64 tokens, a loss of 3 to 4 us at 1 and 3 tokens, where the separate kernel's work runs on
+// all SMs at once while down's weights are already on their way.
+int g_fold_quant = 1, g_fold_min_tokens = 4;
+// the weighted split of down's tasks costs the grouping kernel about 1 us: it pays from about 16 tokens on
+constexpr int kSplitMinTokens = 16;
+unsigned long long* g_stream_stamps = nullptr;   // measurement aid: see frx_debug_set_stream_stamps
 
 int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0, bool task4 = false) {
     const int budget = max_smem_optin() - 2048;   // less the kernels' static shared memory
@@ -1458,6 +2034,36 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0, bool task4 
              c.smem_dn))
         return fail(FRX_ERR_SHAPE, "n %d / ff %d: tiles do not fit in shared memory", n, ff);
     return FRX_OK;
+}
+
+// The fused form (k_ffn): warps per block, ring slots per warp and item buffers that fit.
+// Off by default: measured at batch 64 (148 SMs) the one kernel takes as long as the three it
+// replaces (102 us against 57 + 9 + 39), and the chain of three overlaps better with its neighbours.
+int g_fused = 0;
+int g_ffn_nbuf_g = 0, g_ffn_nbuf_d = 0;   // > 0: that many item buffers (2 .. kMaxItemBufs4) instead of up to kMaxItemBufs, as fit
+struct FfnCfg {
+    int nw = 16, rpw = 2, nbuf_g = 2, nbuf_d = 2;
+    uint32_t smem = 0;
+};
+bool ffn_cfg(int n, int ff, long long max_items, FfnCfg& c) {
+    const int ug = n / kUnitK, ud = ff / kUnitK;
+    if (ug % kFfnUnitsGu || ud % kFfnUnitsDn) return false;
+    const int budget = max_smem_optin() - 2048, sms = sm_count();
+    const long long max_tasks = max_items * (ff / 16);
+    int first = g_nw >= 12 ? 16 : 8;
+    if (max_tasks > 0 && max_tasks <= 4LL * sms) first = 4;
+    else if (max_tasks > 0 && max_tasks <= 8LL * sms) first = 8;
+    const int prefs[3] = {first, first > 8 ? 8 : first, 4};
+    for (int k = 0; k < 3; ++k) {
+        c.nw = prefs[k];
+        for (c.nbuf_g = g_ffn_nbuf_g ? g_ffn_nbuf_g : kMaxItemBufs; c.nbuf_g >= 2; --c.nbuf_g)
+            for (c.nbuf_d = g_ffn_nbuf_d ? g_ffn_nbuf_d : kMaxItemBufs; c.nbuf_d >= 2; --c.nbuf_d)
+                for (c.rpw = c.nw <= 4 ? 8 : 4; c.rpw >= 2; --c.rpw) {
+                    c.smem = ffn_plan(n, ff, kFfnChunkBytes, c.nw * c.rpw, c.nbuf_g, c.nbuf_d).total;
+                    if (int(c.smem) <= budget) return true;
+                }
+    }
+    return false;
 }
 
 template <bool GATE_UP, int NW>
@@ -1526,7 +2132,8 @@ int set_smem_attr() {
         reinterpret_cast<const void*>(k_stream<true, 8, 2, true>),   reinterpret_cast<const void*>(k_stream<true, 8, 0, true>),
         reinterpret_cast<const void*>(k_stream<false, 8, 2, true>),  reinterpret_cast<const void*>(k_stream<false, 8, 0, true>),
         reinterpret_cast<const void*>(k_stream<true, 16, 2, true>),  reinterpret_cast<const void*>(k_stream<true, 16, 0, true>),
-        reinterpret_cast<const void*>(k_stream<false, 16, 2, true>), reinterpret_cast<const void*>(k_stream<false, 16, 0, true>)};
+        reinterpret_cast<const void*>(k_stream<false, 16, 2, true>), reinterpret_cast<const void*>(k_stream<false, 16, 0, true>),
+        reinterpret_cast<const void*>(k_ffn<4>), reinterpret_cast<const void*>(k_ffn<8>), reinterpret_cast<const void*>(k_ffn<16>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
@@ -1547,9 +2154,26 @@ void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaSt
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream,
-                bool task4_gu = false, bool task4_dn = false) {
+                bool task4_gu = false, bool task4_dn = false, const FfnCfg* fused = nullptr, bool fold_quant = false) {
     p.narrow = g_narrow;
     p.wait_ns = wait_limit_ns();
+    p.stamps = g_stream_stamps;
+    if (fused) {   // one kernel for gate/up, the hidden rows and down (items of at most four tokens)
+        p.aq = xb.q;
+        p.aa = xb.a;
+        p.ac = xb.c;
+        p.rpw = fused->rpw;
+        p.nbuf = fused->nbuf_g;
+        p.nbuf_dn = fused->nbuf_d;
+        p.cnt = p.status + kStatusWords;
+        const dim3 grid(sm_count());
+        switch (fused->nw) {
+            case 4: FRX_LAUNCH(kKFfn, stream, launch_pdl(k_ffn<4>, grid, dim3(128), fused->smem, stream, p)); break;
+            case 8: FRX_LAUNCH(kKFfn, stream, launch_pdl(k_ffn<8>, grid, dim3(256), fused->smem, stream, p)); break;
+            default: FRX_LAUNCH(kKFfn, stream, launch_pdl(k_ffn<16>, grid, dim3(512), fused->smem, stream, p)); break;
+        }
+        return;
+    }
     p.cpt = cfg.cpt_gu;
     p.rpw = cfg.rpw_gu;
     p.nbuf = cfg.nbuf_gu;
@@ -1560,8 +2184,12 @@ void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_r
         FRX_LAUNCH(kKGateUp, stream, launch_stream4<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
     else
         FRX_LAUNCH(kKGateUp, stream, launch_stream<true>(p, cfg.nw_gu, p.n / kUnitK / cfg.cpt_gu, cfg.smem_gu, stream));
+    // decode with items of at most four tokens: down makes the hidden rows itself, from gu
+    p.from_gu = fold_quant && g_narrow && task4_dn && !p.row_list && !p.block64 ? 1 : 0;
     const size_t nblk = h_rows * (p.ff / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map, p.row_list, p.row_count, p.row_list ? 0 : 1));
+    if (!p.from_gu)
+        FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_hidden, dim3(unsigned((nblk + 31) / 32)), dim3(256), 0, stream, (const float2*)p.gu, p.ff, nblk, p.h, hb.q, hb.a, hb.c, p.slot_ids, p.TK, p.e_lo, p.e_hi, p.block64, p.e_map, p.row_list, p.row_count, p.row_list ? 0 : 1));
+    if (p.stamps) p.stamps += size_t(sm_count()) * 4;   // down's stamps follow gate/up's
     p.cpt = cfg.cpt_dn;
     p.rpw = cfg.rpw_dn;
     p.nbuf = cfg.nbuf_dn;
@@ -1630,6 +2258,8 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         }
     }
     if (int rc = set_smem_attr()) return rc;
+    FfnCfg fcfg;
+    const bool fused = g_fused && g_narrow && ffn_cfg(n, ff, L.max_items, fcfg);
     auto* base = static_cast<uint8_t*>(ws);
     int* status = reinterpret_cast<int*>(base + L.status);
     Item* items = reinterpret_cast<Item*>(base + L.items);
@@ -1642,12 +2272,15 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         const size_t nblk = size_t(Tc) * (n / kQ8);
         const unsigned want = unsigned(std::min<size_t>((nblk + 31) / 32, size_t(sms)));
         const unsigned qblocks = (want + kHeadCluster - 1) / kHeadCluster * kHeadCluster;
-        const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4;
+        // the down kernel's tasks are shared out by weight when every item is narrow (see DownSplit)
+        DownSplit split{nullptr, sms, n / 64, g_down_heavy};
+        if (g_narrow && g_down_heavy > 0 && Tc >= kSplitMinTokens && L.max_items <= 1024 && sms <= kMaxStreamBlocks) split.ranges = reinterpret_cast<int*>(base + L.ranges);
+        const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4 + (split.ranges ? size_t(L.max_items) * 4 : 0);
         auto head = [&](auto kernel) {
             return launch_pdl_cluster(kernel, dim3(kHeadCluster + qblocks), dim3(1024), dyn, stream, kHeadCluster, logits ? logits + size_t(t0) * E : (const float*)nullptr,
                               ids + size_t(t0) * K, wts + size_t(t0) * K, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
                               static_cast<const uint8_t*>(shared), items, status, order, L.max_items, x + size_t(t0) * n, n, nblk, xb.q, xb.a,
-                              xb.c, g_narrow ? kNarrowTok : kTokPerItem);
+                              xb.c, g_narrow ? kNarrowTok : kTokPerItem, split);
         };
         if (!logits)
             FRX_LAUNCH(kKPrologue, stream, head(k_prologue<0>));
@@ -1668,12 +2301,13 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         p.ff = ff;
         p.K = K;
         p.TK = Tc * K;
+        p.ranges = split.ranges;
         if (e_lo > 0 || e_hi < E) {
             p.slot_ids = ids + size_t(t0) * K;
             p.e_lo = e_lo;
             p.e_hi = e_hi;
         }
-        launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream, task4_gu, task4_dn);
+        launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream, task4_gu, task4_dn, fused ? &fcfg : nullptr, g_fold_quant && Tc >= g_fold_min_tokens);
         if (ep)   // one chunk only (the caller checked T <= 64)
             FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_allreduce, dim3((n + 256 * kEpElems - 1) / (256 * kEpElems), Tc), dim3(256), 0, stream, out,
                                                             (const float*)p.y, (const float*)wts, (const int32_t*)order,
@@ -2002,6 +2636,30 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
 }
 
 // Tuning knobs for measurements (process-wide, not thread-safe: set them before any compute call).
+int frx_debug_set_down_task_weight(int sixteenths) {
+    if (sixteenths < 0 || sixteenths > 64) return fail(FRX_ERR_ARG, "frx_debug_set_down_task_weight: 0 .. 64");
+    g_down_heavy = sixteenths;
+    return FRX_OK;
+}
+int frx_debug_set_fold_quant(int on) {
+    g_fold_quant = on ? 1 : 0;
+    return FRX_OK;
+}
+int frx_debug_set_stream_stamps(void* device_buffer) {
+    g_stream_stamps = static_cast<unsigned long long*>(device_buffer);
+    return FRX_OK;
+}
+int frx_debug_set_fused_ffn(int on) {
+    g_fused = on ? 1 : 0;
+    return FRX_OK;
+}
+int frx_debug_set_ffn_buffers(int gate_up, int down) {
+    if (gate_up < 0 || gate_up > kMaxItemBufs4 || gate_up == 1 || down < 0 || down > kMaxItemBufs4 || down == 1)
+        return fail(FRX_ERR_ARG, "frx_debug_set_ffn_buffers: 0 or 2 .. %d", kMaxItemBufs4);
+    g_ffn_nbuf_g = gate_up;
+    g_ffn_nbuf_d = down;
+    return FRX_OK;
+}
 int frx_debug_set_four_group_tasks(int on) {
     g_task4 = on & 3;
     return FRX_OK;

@@ -81,6 +81,11 @@ SIGNATURES = {
     "frx_debug_set_gate_up_chunks": (_i, [_i]),
     "frx_debug_set_narrow_items": (_i, [_i]),
     "frx_debug_set_four_group_tasks": (_i, [_i]),
+    "frx_debug_set_fused_ffn": (_i, [_i]),
+    "frx_debug_set_fold_quant": (_i, [_i]),
+    "frx_debug_set_down_task_weight": (_i, [_i]),
+    "frx_debug_set_stream_stamps": (_i, [_vp]),
+    "frx_debug_set_ffn_buffers": (_i, [_i, _i]),
     "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),
     "frx_moe_decode_static_status": (_i, [_vp]),
     "frx_moe_layer_ep_allreduce": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -64,6 +64,10 @@ const char* frx_profile_class_name(int cls);
  * frx_debug_set_narrow_items: 1 (default) lets work items of at most four tokens take the narrow
  * form of the inner product (two row groups share one MMA accumulator, half the float work per row);
  * 0 sends every item through the eight-token form. Results are the same bits either way.
+ * frx_debug_set_fused_ffn: 1 runs the expert FFN of the decode layer (gate/up, the hidden rows, down) as one
+ * kernel when items have at most four tokens and the shape allows; 0 (default, the faster as measured) keeps
+ * the three kernels. frx_debug_set_ffn_buffers: item buffers per half of that kernel (0 = as many as fit,
+ * at most three). Same bits either way.
  * frx_debug_set_four_group_tasks: which streaming kernels of the decode layer walk four row groups per task
  * instead of two (needs narrow items): bit 0 gate/up, bit 1 down; default 2 (down only, the faster
  * combination as measured). Same bits either way.
@@ -73,6 +77,21 @@ int frx_debug_set_consumer_warps(int nw);
 int frx_debug_set_gate_up_chunks(int chunks);
 int frx_debug_set_narrow_items(int on);
 int frx_debug_set_four_group_tasks(int on);
+int frx_debug_set_fused_ffn(int on);
+/* 1 (default): in the decode layer the down kernel forms and quantizes the hidden rows while it builds its
+ * item buffers (needs narrow items and four-group tasks in down); 0: a separate quantizer kernel writes them
+ * to the workspace first (where frx_decode_workspace_view can read them). Same bits either way. */
+int frx_debug_set_fold_quant(int on);
+/* Decode layer: the down kernel's tasks are shared out among its blocks by weight, a task of an item of three
+ * or four tokens weighing `sixteenths` / 16 of one of a smaller item (default 22; 16 = equal; 0 = an even
+ * split by count, made by the kernel itself). Same bits whatever the split. */
+int frx_debug_set_down_task_weight(int sixteenths);
+/* Measurement aid: with a device buffer of 2 * SMs * 4 * 8 bytes set, every launch of the decode layer's two
+ * streaming kernels (three-kernel form) writes four globaltimer stamps per block there, gate/up's blocks first,
+ * then down's: [0] block started, [1] the kernels in front have ended, [2] first item buffer built, [3] block
+ * finished. NULL (default) switches it off. */
+int frx_debug_set_stream_stamps(void* device_buffer);
+int frx_debug_set_ffn_buffers(int gate_up, int down);
 int frx_debug_set_wait_limit_ns(unsigned long long ns);
 
 /* ---- Q2_0 storage (quant/q2_0/q2_0.hpp:27-56, quant/q2_0/q2_0.cpp:43-71) ---- */

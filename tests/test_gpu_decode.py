@@ -59,7 +59,20 @@ def test_layer_config_shape(port, T):
     x = synth.activations(T, n)
     ids, wts, _ = port.route(synth.router_logits(T, E), K)
     gate = np.random.default_rng(3).standard_normal(T).astype(np.float32)
-    out, ys, ws = run_decode(ex, x, ids, wts, gate, want_ws=True)
+    from flashrt_b200.lib import check, lib
+    out_d, ys_d = run_decode(ex, x, ids, wts, gate)            # the default: down forms and quantizes the hidden rows itself
+    try:                                                       # with the separate quantizer the hidden rows pass through the workspace
+        check(lib.frx_debug_set_fold_quant(0))
+        out, ys, ws = run_decode(ex, x, ids, wts, gate, want_ws=True)
+    finally:
+        check(lib.frx_debug_set_fold_quant(1))
+    assert np.array_equal(ys_d, ys) and np.array_equal(out_d, out)
+    try:                                                       # the FFN as one kernel: the hidden rows stay on chip
+        check(lib.frx_debug_set_fused_ffn(1))
+        out_f, ys_f = run_decode(ex, x, ids, wts, gate)
+    finally:
+        check(lib.frx_debug_set_fused_ffn(0))
+    assert np.array_equal(ys_f, ys) and np.array_equal(out_f, out)
     ref_out, ref_ys, ref_sh = port.moe_layer(ex.routed_planar(), ex.blob_bytes, ex.shared_planar, n, ff, x, ids, wts, gate,
                                              n_threads=8, want_slots=True)
     # hidden activations: Q8 codes bit-exact for a sample of slots
@@ -274,15 +287,33 @@ def test_narrow_and_wide_item_forms_give_the_same_bits(port):
         out_w, ys_w = run_decode(ex, x, ids, wts, gate)
     finally:
         check(lib.frx_debug_set_narrow_items(1))
-    out_n, ys_n = run_decode(ex, x, ids, wts, gate)                # narrow items, four row groups per task (the default)
+    out_n, ys_n = run_decode(ex, x, ids, wts, gate)                # narrow items (the default)
     assert np.array_equal(ys_n, ys_w) and np.array_equal(out_n, out_w)
-    for forms in (0, 1, 3):                                        # two or four row groups per task, per kernel (default: 2)
-        try:
+    for forms, fold in ((0, 1), (1, 1), (3, 1), (2, 0), (3, 0)):   # two or four row groups per task, per kernel (default: 2);
+        try:                                                       # hidden rows made by down itself or by the separate quantizer
             check(lib.frx_debug_set_four_group_tasks(forms))
+            check(lib.frx_debug_set_fold_quant(fold))
             out_2, ys_2 = run_decode(ex, x, ids, wts, gate)
         finally:
             check(lib.frx_debug_set_four_group_tasks(2))
-        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), forms
+            check(lib.frx_debug_set_fold_quant(1))
+        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), (forms, fold)
+    for weight in (0, 16, 40):                                     # how down's tasks are shared out among its blocks (default: 22)
+        try:
+            check(lib.frx_debug_set_down_task_weight(weight))
+            out_2, ys_2 = run_decode(ex, x, ids, wts, gate)
+        finally:
+            check(lib.frx_debug_set_down_task_weight(22))
+        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), weight
+    for bufs in ((0, 0), (2, 2), (4, 3)):                          # the FFN as one kernel, with different numbers of item buffers
+        try:
+            check(lib.frx_debug_set_fused_ffn(1))
+            check(lib.frx_debug_set_ffn_buffers(*bufs))
+            out_f, ys_f = run_decode(ex, x, ids, wts, gate)
+        finally:
+            check(lib.frx_debug_set_ffn_buffers(0, 0))
+            check(lib.frx_debug_set_fused_ffn(0))
+        assert np.array_equal(ys_f, ys_w) and np.array_equal(out_f, out_w), bufs
     ref_out, ref_ys, _ = port.moe_layer(ex.routed_planar(), ex.blob_bytes, ex.shared_planar, n, ff, x, ids, wts, gate, n_threads=8,
                                         want_slots=True)
     assert max(rel_max(ys_n[s], ref_ys[s]) for s in range(T * K)) < 1e-5

@@ -70,7 +70,7 @@ def _worker(rank, world, port_no, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_expert_parallel_layers(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
