@@ -50,7 +50,7 @@ N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
 NCU_FFN_TRAFFIC_PER_BLOB = None            # the same for one launch of the fused kernel (k_ffn)
-NCU_GU_TRAFFIC_PER_BLOB = 223.0e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
+NCU_GU_TRAFFIC_PER_BLOB = 224.1e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
 UNIT = "layer-tokens/s"
@@ -321,12 +321,13 @@ def run_frx(args):
             moe.moe_layer(arena.blob(l, 0), arena.stride, E, arena.blob(l, e_local), N_MODEL, FF, xin, lin, gin, K,
                           out=o, ids_out=ids_l, wts_out=wts_l, ws=ws_)
             return
-        shared_blob = arena.blob(l, e_local) if rank == 0 else None
-        if comm is not None:
-            ep.moe_layer_ep_fused(comm, arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o,
-                                  ids_l, wts_l, ws_)
-        else:
-            ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, shared_blob, N_MODEL, FF, xin, lin, gin, K, o, ids_l, wts_l, ws_)
+        if comm is not None:   # every rank holds the shared expert and applies it to its share of the tokens
+            ep.moe_layer_ep_fused(comm, arena.blob(l, 0), arena.stride, E, e_lo, e_hi, arena.blob(l, e_local), N_MODEL, FF, xin, lin, gin, K, o,
+                                  ids_l, wts_l, ws_, shared_tokens=ep.shared_token_range(rank, world, xin.shape[0]) if args.deal_shared else
+                                  ((0, xin.shape[0]) if rank == 0 else (0, 0)))
+            return
+        ep.moe_layer_ep(arena.blob(l, 0), arena.stride, E, e_lo, e_hi, arena.blob(l, e_local) if rank == 0 else None, N_MODEL, FF, xin, lin, gin, K,
+                        o, ids_l, wts_l, ws_)
 
     def ep_layer(l: int, xin, lin, gin, o):
         layer(l, xin, lin, gin, o, ids[l], wts[l], ws)
@@ -974,6 +975,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the decode_batches, prefill and verify_stack keys")
     ap.add_argument("--nw", type=int, default=0, help="tuning: consumer warps of the streaming kernel (8, 12, 16, 20)")
     ap.add_argument("--fused", type=int, default=None, help="tuning: 0 runs the decode FFN as three kernels instead of one")
+    ap.add_argument("--deal-shared", type=int, default=1, help="expert parallel: 1 deals the shared expert's tokens among the ranks, 0 leaves them all to rank 0")
     ap.add_argument("--down-weight", type=int, default=None, help="tuning: weight (in 1/16) of a down task of a 3-4 token item in the split over blocks; 0 = even split")
     ap.add_argument("--fold", type=int, default=None, help="tuning: 0 runs the hidden-row quantizer as its own kernel")
     ap.add_argument("--ffn-buffers", default=None, help="tuning: item buffers of the fused FFN kernel, gate/up,down (e.g. 3,3)")

@@ -265,7 +265,10 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
                                             int e_hi, const uint8_t* __restrict__ experts, size_t stride,
                                             const uint8_t* __restrict__ shared, Item* __restrict__ items, int* __restrict__ status,
                                             int32_t* __restrict__ order, int max_items, int tpi, bool zero_counters = false,
-                                            DownSplit split = DownSplit{nullptr, 0, 0, 16}) {
+                                            DownSplit split = DownSplit{nullptr, 0, 0, 16}, int sh_lo = 0, int sh_hi = 1 << 30) {
+    // the shared expert is applied to tokens [sh_lo, sh_hi) (all of them unless the caller deals them among ranks)
+    sh_lo = max(sh_lo, 0);
+    sh_hi = max(min(sh_hi, T), sh_lo);
     unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K], then the items' weights
     __shared__ int warp_tot[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -320,7 +323,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     const int before = inc - cnt + (warp ? warp_tot[warp - 1] : 0);
     int at = before & kCntMask, wat = before >> kCntBits;   // this thread's first item, and the weight in front of it
     const int routed_items = warp_tot[31] & kCntMask, routed_weight = warp_tot[31] >> kCntBits;
-    const int shared_items = shared ? (T + tpi - 1) / tpi : 0;
+    const int shared_items = shared ? (sh_hi - sh_lo + tpi - 1) / tpi : 0;
     if (routed_items + shared_items > max_items) {
         if (tid == 0) {
             status[0] = kDevTooManyItems;
@@ -356,7 +359,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         Item it;
         it.blob = shared;
         it.expert = -1;
-        const int t0 = tid * tpi, m = min(tpi, T - t0);
+        const int t0 = sh_lo + tid * tpi, m = min(tpi, sh_hi - t0);
         it.n_tok = m;
         for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? T * K + t0 + j : 0;
         if (split.ranges) wgt[routed_items + tid] = routed_weight + tid * weight_of(tpi);   // (all but the last shared item are full)
@@ -382,7 +385,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     __syncthreads();
     if (tid <= split.blocks && n_items > 0) {
         const int tpe = split.tasks_per_expert;
-        const int last_w = shared_items ? weight_of(min(tpi, T - (shared_items - 1) * tpi)) : 0;
+        const int last_w = shared_items ? weight_of(min(tpi, sh_hi - sh_lo - (shared_items - 1) * tpi)) : 0;
         const unsigned total_w = unsigned(shared_items ? wgt[n_items - 1] + last_w : routed_weight);
         if (tid == split.blocks) {
             split.ranges[tid] = n_items * tpe;
@@ -413,7 +416,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
                                                    size_t stride, const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                    int* __restrict__ status, int32_t* __restrict__ order, int max_items,
                                                    const float* __restrict__ x, int n, size_t n_blocks, int8_t* __restrict__ xq,
-                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi, DownSplit split) {
+                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi, DownSplit split, int sh_lo, int sh_hi) {
     extern __shared__ unsigned long long dyn[];
     pdl_wait();
     pdl_trigger();
@@ -429,7 +432,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
             route_warp<V>(logits + size_t(t) * E, E, K, lane, ids + size_t(t) * K, wts + size_t(t) * K, nullptr, nullptr);
     }
     cluster_sync_all();   // every block's ids are visible to block 0
-    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi, true, split);
+    if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi, true, split, sh_lo, sh_hi);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1660,7 +1663,8 @@ __global__ void __launch_bounds__(NW * 32, 1) k_ffn(const StreamParams p) {
 // out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate)
 __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out, const float* __restrict__ y,
                                                          const float* __restrict__ wts, const int32_t* __restrict__ order,
-                                                         const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K) {
+                                                         const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
+                                                         int sh_lo, int sh_hi) {   // the shared expert's rows exist for tokens [sh_lo, sh_hi)
     pdl_wait();
     pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
@@ -1670,7 +1674,7 @@ __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out
         const int s = order[t * K + k];
         if (s >= 0) acc = __fadd_rn(acc, __fmul_rn(wts[s], y[size_t(s) * n + i]));
     }
-    if (ysh) {
+    if (ysh && t >= sh_lo && t < sh_hi) {
         const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
         acc = __fadd_rn(acc, __fmul_rn(ysh[size_t(t) * n + i], g));
     }
@@ -1701,6 +1705,7 @@ struct EpParams {
     uint32_t* state;                       // local: [0] calls completed so far, [1] ticket, [8..15] cycle stamps
     size_t slot_floats;
     unsigned long long wait_ns;
+    int sh_lo, sh_hi;                      // this rank adds the shared expert's rows of tokens [sh_lo, sh_hi)
 };
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
@@ -1757,7 +1762,7 @@ __global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ o
                 acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
             }
         }
-        if (ysh) {
+        if (ysh && t >= ep.sh_lo && t < ep.sh_hi) {
             const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
             const float4 v = *reinterpret_cast<const float4*>(ysh + size_t(t) * n + i);
             acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
@@ -2223,7 +2228,7 @@ int check_moe_shape(const char* who, int n, int ff, int K) {
 // and weights are outputs, else inputs.
 int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int n, int ff, const float* x,
                  const float* logits, int32_t* ids, float* wts, const float* gate_logit, int T, int K, float* out, float* yslot, void* ws,
-                 size_t ws_bytes, cudaStream_t stream, const EpParams* ep = nullptr) {
+                 size_t ws_bytes, cudaStream_t stream, const EpParams* ep = nullptr, int shared_t0 = 0, int shared_t1 = 1 << 30) {
     if (!experts || !x || !ids || !wts || !out || !ws) return fail(FRX_ERR_ARG, "frx_moe_decode: null pointer");
     if (T < 0 || E < 1 || E > 4096) return fail(FRX_ERR_ARG, "frx_moe_decode: T %d, E %d", T, E);
     if (e_lo < 0 || e_hi > E || e_lo > e_hi) return fail(FRX_ERR_ARG, "frx_moe_decode: expert range [%d, %d) outside [0, %d)", e_lo, e_hi, E);
@@ -2269,6 +2274,8 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
     for (int t0 = 0; t0 < T; t0 += kMaxChunkTokens) {
         const int Tc = T - t0 < kMaxChunkTokens ? T - t0 : kMaxChunkTokens;
         const ActBufs xb = act_x(base, L);
+        // the tokens of this chunk that get the shared expert here
+        const int sh_lo = std::min(std::max(shared_t0 - t0, 0), Tc), sh_hi = std::max(std::min(shared_t1 - t0, Tc), sh_lo);
         const size_t nblk = size_t(Tc) * (n / kQ8);
         const unsigned want = unsigned(std::min<size_t>((nblk + 31) / 32, size_t(sms)));
         const unsigned qblocks = (want + kHeadCluster - 1) / kHeadCluster * kHeadCluster;
@@ -2280,7 +2287,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
             return launch_pdl_cluster(kernel, dim3(kHeadCluster + qblocks), dim3(1024), dyn, stream, kHeadCluster, logits ? logits + size_t(t0) * E : (const float*)nullptr,
                               ids + size_t(t0) * K, wts + size_t(t0) * K, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
                               static_cast<const uint8_t*>(shared), items, status, order, L.max_items, x + size_t(t0) * n, n, nblk, xb.q, xb.a,
-                              xb.c, g_narrow ? kNarrowTok : kTokPerItem, split);
+                              xb.c, g_narrow ? kNarrowTok : kTokPerItem, split, sh_lo, sh_hi);
         };
         if (!logits)
             FRX_LAUNCH(kKPrologue, stream, head(k_prologue<0>));
@@ -2308,14 +2315,17 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
             p.e_hi = e_hi;
         }
         launch_ffn(p, xb, act_h(base, L), size_t(Tc) * K + (shared ? Tc : 0), cfg, stream, task4_gu, task4_dn, fused ? &fcfg : nullptr, g_fold_quant && Tc >= g_fold_min_tokens);
-        if (ep)   // one chunk only (the caller checked T <= 64)
+        if (ep) {   // one chunk only (the caller checked T <= 64)
+            EpParams epc = *ep;
+            epc.sh_lo = sh_lo;
+            epc.sh_hi = sh_hi;
             FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_allreduce, dim3((n + 256 * kEpElems - 1) / (256 * kEpElems), Tc), dim3(256), 0, stream, out,
                                                             (const float*)p.y, (const float*)wts, (const int32_t*)order,
-                                                            (const float*)(shared ? p.ysh : nullptr), gate_logit, n, K, *ep, status));
-        else
+                                                            (const float*)(shared ? p.ysh : nullptr), gate_logit, n, K, epc, status));
+        } else
             FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
                                                             (const float*)(wts + size_t(t0) * K), (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
-                                                            gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K));
+                                                            gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K, sh_lo, sh_hi));
     }
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
@@ -2440,7 +2450,17 @@ int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_
                                const float* x, const float* logits, const float* gate_logit, int T, int K, float* out,
                                int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
                                frx_stream_t stream) {
+    return frx_moe_layer_ep_allreduce_dealt(experts, stride, E, e_lo, e_hi, shared, 0, T, n, ff, x, logits, gate_logit, T, K, out, ids_out, wts_out,
+                                            comm, ws, ws_bytes, stream);
+}
+
+int frx_moe_layer_ep_allreduce_dealt(const void* experts, size_t stride, int E, int e_lo, int e_hi, const void* shared, int shared_t0,
+                                     int shared_t1, int n, int ff, const float* x, const float* logits, const float* gate_logit, int T, int K,
+                                     float* out, int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
+                                     frx_stream_t stream) {
     if (!logits || !ws || !comm) return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: null pointer");
+    if (shared && (shared_t0 < 0 || shared_t1 > T || shared_t0 > shared_t1))
+        return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: shared-expert tokens [%d, %d) outside [0, %d)", shared_t0, shared_t1, T);
     if (comm->world < 1 || comm->world > FRX_EP_MAX_RANKS || comm->rank < 0 || comm->rank >= comm->world)
         return fail(FRX_ERR_ARG, "frx_moe_layer_ep_allreduce: rank %d of %d", comm->rank, comm->world);
     if (T < 0 || T > kMaxChunkTokens || T > comm->max_T || n != comm->n)
@@ -2470,7 +2490,8 @@ int frx_moe_layer_ep_allreduce(const void* experts, size_t stride, int E, int e_
     auto* base = static_cast<uint8_t*>(ws);
     int32_t* ids = ids_out ? ids_out : reinterpret_cast<int32_t*>(base + d);
     float* wts = wts_out ? wts_out : reinterpret_cast<float*>(base + d + r);
-    return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream, &ep);
+    return decode_steps(experts, stride, E, e_lo, e_hi, shared, n, ff, x, logits, ids, wts, gate_logit, T, K, out, nullptr, ws, d, stream, &ep,
+                        shared_t0, shared_t1);
 }
 
 int frx_ep_debug_stamps(const void* own_buffer, int max_T, int n, long long* cycles4) {

@@ -119,17 +119,30 @@ class EpComm:
         return list(out)
 
 
+def shared_token_range(rank: int, world: int, T: int, step: int = 4) -> tuple[int, int]:
+    """The tokens whose shared-expert rows rank `rank` computes when the shared expert's work is
+    dealt among the ranks: contiguous ranges of whole work items (`step` tokens) that partition [0, T)."""
+    items = (T + step - 1) // step
+    lo, hi = items * rank // world, items * (rank + 1) // world
+    return min(lo * step, T), min(hi * step, T)
+
+
 def moe_layer_ep_fused(comm: EpComm, experts_local: int, stride: int, E: int, e_lo: int, e_hi: int, shared: int | None, n: int, ff: int,
                        x: torch.Tensor, logits: torch.Tensor, gate_logit: torch.Tensor | None, K: int, out: torch.Tensor,
-                       ids_out: torch.Tensor, wts_out: torch.Tensor, ws: torch.Tensor, stream=None) -> torch.Tensor:
+                       ids_out: torch.Tensor, wts_out: torch.Tensor, ws: torch.Tensor, stream=None,
+                       shared_tokens: tuple[int, int] | None = None) -> torch.Tensor:
     """Router on every rank, local experts, and the all-reduce inside the layer's last kernel (peer
     loads over NVLink, partial sums added in rank order on every rank). `out` is the complete layer
-    output on every rank. Every rank must make the same sequence of calls."""
+    output on every rank. Every rank must make the same sequence of calls.
+    `shared`: the shared expert's blob on the one rank that applies it to all tokens, or, with
+    `shared_tokens` = (t0, t1), on every rank, each applying it to its own tokens (shared_token_range)."""
     T = x.shape[0]
     wp, wb = moe._ws_ptr(ws)
-    check(lib.frx_moe_layer_ep_allreduce(C.c_void_p(experts_local), stride, E, e_lo, e_hi, C.c_void_p(shared) if shared else None, n, ff,
-                                         moe._ptr(x), moe._ptr(logits), moe._ptr(gate_logit) if shared else None, T, K, moe._ptr(out),
-                                         moe._ptr(ids_out), moe._ptr(wts_out), C.byref(comm.struct), wp, wb, moe._stream(stream)))
+    t0, t1 = shared_tokens if shared_tokens is not None else (0, T)
+    check(lib.frx_moe_layer_ep_allreduce_dealt(C.c_void_p(experts_local), stride, E, e_lo, e_hi, C.c_void_p(shared) if shared else None, t0, t1,
+                                               n, ff, moe._ptr(x), moe._ptr(logits), moe._ptr(gate_logit) if shared else None, T, K,
+                                               moe._ptr(out), moe._ptr(ids_out), moe._ptr(wts_out), C.byref(comm.struct), wp, wb,
+                                               moe._stream(stream)))
     return out
 
 

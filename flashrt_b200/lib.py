@@ -89,6 +89,7 @@ SIGNATURES = {
     "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),
     "frx_moe_decode_static_status": (_i, [_vp]),
     "frx_moe_layer_ep_allreduce": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "frx_moe_layer_ep_allreduce_dealt": (_i, [_vp, _sz, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "frx_moe_layer_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "frx_moe_layer_host": (_i, [_vp, _sz, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "frx_moe_layers_host_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -307,6 +307,16 @@ int frx_moe_layer_ep_allreduce(const void* experts_local, size_t stride, int E, 
                                int32_t* ids_out, float* wts_out, const frx_ep_comm* comm, void* ws, size_t ws_bytes,
                                frx_stream_t stream);
 
+/* The same with the shared expert's work dealt among the ranks: every rank holds a copy of the shared
+ * expert and applies it to the tokens [shared_t0, shared_t1) (an empty range: none); the ranges of the
+ * ranks must partition [0, T). With the plain entry the one rank that passes `shared` does all T
+ * tokens and is the last to arrive at every exchange. Ranges that are multiples of four tokens keep
+ * the work items full. */
+int frx_moe_layer_ep_allreduce_dealt(const void* experts_local, size_t stride, int E, int e_lo, int e_hi, const void* shared,
+                                     int shared_t0, int shared_t1, int n, int ff, const float* x, const float* logits,
+                                     const float* gate_logit, int T, int K, float* out, int32_t* ids_out, float* wts_out,
+                                     const frx_ep_comm* comm, void* ws, size_t ws_bytes, frx_stream_t stream);
+
 /* The same with host buffers: x_host [T][n], logits_host [T][E], gate_logit_host [T] or null are
  * copied to the device, the layer runs, out_host [T][n] is copied back, and the call returns after
  * the stream has drained. `ws` is a device workspace of frx_moe_layer_host_workspace_bytes. */

@@ -46,8 +46,12 @@ def _worker(rank, world, port_no, ret):
         xi = synth.activations(T, n, seed=50 + it)
         want = moe.moe_decode(ex.base, ex.stride, E, ex.shared_ptr, n, ff, cuda(xi), cuda(ids), cuda(wts), None)
         got = torch.empty(T, n, device="cuda")
-        ep.moe_layer_ep_fused(comm, ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr if rank == 0 else None, n, ff, cuda(xi),
-                              cuda(lg), None, K, got, ids_o, wts_o, ws)
+        if it == 1:   # the shared expert's tokens dealt among the ranks (every rank holds a copy of it)
+            ep.moe_layer_ep_fused(comm, ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr, n, ff, cuda(xi), cuda(lg), None, K, got,
+                                  ids_o, wts_o, ws, shared_tokens=ep.shared_token_range(rank, world, T))
+        else:         # all of them on rank 0
+            ep.moe_layer_ep_fused(comm, ex.base + lo * ex.stride, ex.stride, E, lo, hi, ex.shared_ptr if rank == 0 else None, n, ff, cuda(xi),
+                                  cuda(lg), None, K, got, ids_o, wts_o, ws)
         torch.cuda.synchronize()
         moe.workspace_status(ws)
         err_fused = max(err_fused, rel_max(got.cpu().numpy(), want.cpu().numpy()))
