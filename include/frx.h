@@ -153,7 +153,11 @@ int frx_arena_load_planar(frx_arena* a, int layer, int expert0, int count, const
  * Softmax over E <= 1024 logits per token, the k <= 32 most probable experts in descending
  * probability with ties to the lower index, weights p / max(sum of the selected p, 6.103515625e-5).
  * ids, wts [T][k]. counts [E] (may be null): each selection adds 1. tail_counts [E] (may be null):
- * rows t >= tail_from also add 1 there. */
+ * rows t >= tail_from also add 1 there.
+ * The ranking is done on the logits (the softmax is monotonic; -0.0 and +0.0 tie). One corner differs
+ * from the reference, which ranks on the float probabilities: two distinct logits whose probabilities
+ * round to the same float, or both underflow to zero (a logit more than about 103 below the row's
+ * maximum), tie there and go to the lower index, while here the larger logit wins. */
 int frx_route_topk(frx_stream_t stream, const float* logits, int T, int E, int k, int32_t* ids, float* wts,
                    uint32_t* counts, uint32_t* tail_counts, int tail_from);
 
