@@ -202,6 +202,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// Touches the line at p without using it: the address translation (and the line in the L2) is there
+// by the time a dependent access needs it. Used before griddepcontrol.wait, on buffers whose
+// first access would otherwise pay a translation miss in the middle of a latency chain.
+__device__ __forceinline__ void touch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Counters in global memory that blocks of one grid raise and await.
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
@@ -214,6 +219,21 @@ __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
 
 // 1-D bulk copy global -> shared through the TMA unit, completion counted on an mbarrier.
 // dst, src 16-byte aligned; bytes a multiple of 16.
+// The same with an L2 eviction policy for the lines the copy brings in (see l2_policy_evict_first).
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+// Policy for data that is read once (a decode step's expert weights: 326 MB per layer through a
+// 126 MB L2): its lines are the first to go, so the stream does not push out what is read again
+// (the next kernels' code, item lists, activations).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))

@@ -269,7 +269,7 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
     // the shared expert is applied to tokens [sh_lo, sh_hi) (all of them unless the caller deals them among ranks)
     sh_lo = max(sh_lo, 0);
     sh_hi = max(min(sh_hi, T), sh_lo);
-    unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K], then the items' weights
+    unsigned long long* mask = dyn;   // [E] tokens routed to each expert, then the ids [T * K], the items' weights (with `split`: max_items), [E] ints
     __shared__ int warp_tot[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int32_t* sid = reinterpret_cast<int32_t*>(mask + E);   // the ids, read many times below
@@ -331,28 +331,39 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         }
         return;
     }
+    // every expert's first item and the weight in front of it, for the pass over the slots below
+    int* ebase = wgt + (split.ranges ? max_items : 0);   // [E]: item index in the low 12 bits, weight above
+    // the items are put together in shared memory and copied out in whole 16-byte vectors: scattered
+    // 4-byte stores to global memory from this one block cost several microseconds
+    Item* items_s = reinterpret_cast<Item*>(reinterpret_cast<uintptr_t>(ebase + E + 3) & ~uintptr_t(15));
     for (int e = e0; e < e1; ++e) {
-        unsigned long long bits = mask[e];
-        while (bits) {
-            Item it;
-            it.blob = experts + size_t(e - e_lo) * stride;
-            it.expert = e;
-            int m = 0;
-            while (bits && m < tpi) {
-                const int t = __ffsll((long long)bits) - 1;
-                bits &= bits - 1;
-                int k = 0;
-                while (k < K - 1 && sid[t * K + k] != e) ++k;
-                it.slot[m] = t * K + k;
-                ++m;
-            }
-            it.n_tok = m;
-            for (int j = m; j < kTokPerItem; ++j) it.slot[j] = 0;
-            if (split.ranges) {
-                wgt[at] = wat;   // the weight in front of this item
-                wat += weight_of(m);
-            }
-            items[at++] = it;
+        const int pc = __popcll(mask[e]), full = pc / tpi, rem = pc - full * tpi;
+        ebase[e] = at | (wat << kCntBits);
+        at += full + (rem ? 1 : 0);
+        wat += full * weight_of(tpi) + (rem ? weight_of(rem) : 0);
+    }
+    __syncthreads();
+    // One thread per slot: the slot's place among its expert's tokens (token order) gives its item
+    // and its position there; the thread of an item's first slot also writes the item's header. Of
+    // several slots of one token that name the same expert only the first is computed.
+    for (int s = tid; s < T * K; s += 1024) {
+        const int e = sid[s], t = s / K, k = s - t * K;
+        if (e < e_lo || e >= e_hi || e < 0 || e >= E) continue;
+        bool first = true;
+        for (int j = 0; j < k; ++j) first = first && sid[t * K + j] != e;
+        if (!first) continue;
+        const unsigned long long mk = mask[e];
+        const int idx = __popcll(mk & ((1ull << t) - 1ull)), pc = __popcll(mk);
+        const int j = idx / tpi, pos = idx - j * tpi, eb = ebase[e];
+        Item* it = items_s + (eb & kCntMask) + j;
+        it->slot[pos] = s;
+        if (pos == 0) {
+            const int m = min(tpi, pc - j * tpi);
+            it->blob = experts + size_t(e - e_lo) * stride;
+            it->n_tok = m;
+            it->expert = e;
+            for (int z = m; z < kTokPerItem; ++z) it->slot[z] = 0;
+            if (split.ranges) wgt[(eb & kCntMask) + j] = (eb >> kCntBits) + j * weight_of(tpi);   // the expert's items in front are full
         }
     }
     if (tid < shared_items) {
@@ -363,8 +374,11 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         it.n_tok = m;
         for (int j = 0; j < kTokPerItem; ++j) it.slot[j] = j < m ? T * K + t0 + j : 0;
         if (split.ranges) wgt[routed_items + tid] = routed_weight + tid * weight_of(tpi);   // (all but the last shared item are full)
-        items[routed_items + tid] = it;
+        items_s[routed_items + tid] = it;
     }
+    __syncthreads();
+    for (int i = tid; i < (routed_items + shared_items) * int(sizeof(Item) / 16); i += 1024)
+        reinterpret_cast<uint4*>(items)[i] = reinterpret_cast<const uint4*>(items_s)[i];
     if (tid == 0) status[1] = routed_items + shared_items;
     if (zero_counters)
         for (int i = tid; i < routed_items + shared_items; i += 1024) status[kStatusWords + i] = 0;
@@ -416,10 +430,31 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
                                                    size_t stride, const uint8_t* __restrict__ shared, Item* __restrict__ items,
                                                    int* __restrict__ status, int32_t* __restrict__ order, int max_items,
                                                    const float* __restrict__ x, int n, size_t n_blocks, int8_t* __restrict__ xq,
-                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi, DownSplit split, int sh_lo, int sh_hi) {
+                                                   float* __restrict__ xa, float* __restrict__ xc, int tpi, DownSplit split, int sh_lo, int sh_hi,
+                                                   unsigned long long* stamps) {   // measurement aid (else null): four globaltimer values of block 0
     extern __shared__ unsigned long long dyn[];
+    if (threadIdx.x == 0) {   // while the kernels in front still run: the translations of what this block will touch
+        if (blockIdx.x < kHeadCluster) {
+            const int t = blockIdx.x < T ? blockIdx.x : 0;
+            if (logits) touch_l2(logits + size_t(t) * E);
+            touch_l2(ids + size_t(t) * K);
+            touch_l2(wts + size_t(t) * K);
+            if (blockIdx.x == 0) {
+                touch_l2(items);
+                touch_l2(status);
+                touch_l2(order);
+                if (split.ranges) touch_l2(split.ranges);
+            }
+        } else {
+            touch_l2(x);
+            touch_l2(xq);
+            touch_l2(xa);
+            touch_l2(xc);
+        }
+    }
     pdl_wait();
     pdl_trigger();
+    if (stamps && blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_ns();   // the kernels in front have ended
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (blockIdx.x >= kHeadCluster) {
         const size_t qb = blockIdx.x - kHeadCluster, nqb = gridDim.x - kHeadCluster;
@@ -431,8 +466,14 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
         for (int t = warp * kHeadCluster + rank; t < T; t += 32 * kHeadCluster)
             route_warp<V>(logits + size_t(t) * E, E, K, lane, ids + size_t(t) * K, wts + size_t(t) * K, nullptr, nullptr);
     }
+    if (stamps && blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_ns();   // block 0's tokens are routed
     cluster_sync_all();   // every block's ids are visible to block 0
+    if (stamps && blockIdx.x == 0 && threadIdx.x == 0) stamps[2] = global_ns();   // all tokens are routed
     if (rank == 0) group_block(dyn, ids, T, K, E, e_lo, e_hi, experts, stride, shared, items, status, order, max_items, tpi, true, split, sh_lo, sh_hi);
+    if (stamps && blockIdx.x == 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) stamps[3] = global_ns();   // the work items are written
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -478,6 +519,7 @@ struct StreamParams {
     int narrow;        // items of at most kNarrowTok tokens take units_mma_narrow (results are the same bits either way)
     unsigned long long* stamps;   // measurement aid (else null): per block four globaltimer values, see frx_debug_set_stream_stamps
     const int* ranges; // down: block b takes the tasks [ranges[b], ranges[b + 1]) (else null: an even split)
+    int stream_once;   // the expert weights are read once per launch (decode): their L2 lines are marked evict-first
     int from_gu;       // down: item buffers are built from gu (SwiGLU and quantization on the way), there is no separate quantizer launch
     int* cnt;          // k_ffn: per item, the gate/up tasks finished so far
     int cpt_dn;        // k_ffn: chunks per down task (cpt: per gate/up task)
@@ -877,6 +919,19 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;            // this warp's slots
     volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
 
+    if (threadIdx.x == 32) {   // the translations of what this block will touch after its wait
+        touch_l2(p.items);
+        touch_l2(p.status);
+        touch_l2(p.aq);
+        touch_l2(p.aa);
+        touch_l2(p.ac);
+        touch_l2(p.gu);
+        if (!GATE_UP) {
+            touch_l2(p.y);
+            if (p.ysh) touch_l2(p.ysh);
+            if (p.ranges) touch_l2(p.ranges);
+        }
+    }
     if (threadIdx.x == 0) {   // (before the wait: this needs nothing from the kernels in front)
         for (int s = 0; s < slots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + sp.bars) + s, 1);
         for (int b = 0; b < kMaxItemBufs; ++b) {
@@ -926,6 +981,12 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         is_task = int(tau % tasks_per_expert);
         if (is_i < ntasks) is_blob = item_blob(is_item) + section;
     }
+    const uint64_t l2pol = l2_policy_evict_first();   // used when the weights are read once (decode): see l2_policy_evict_first
+    const bool once = p.stream_once != 0;
+    auto copy = [&](void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+        if (once) bulk_g2s_hint(dst, src, bytes, bar, l2pol);
+        else bulk_g2s(dst, src, bytes, bar);
+    };
     auto issue_next = [&]() {   // lane 0 only
         if (is_i >= ntasks) return;
         mbar_expect_tx(full + is_slot, chunk_bytes);
@@ -933,13 +994,13 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         if (TASK4) {     // the same K range of the task's four groups
             const uint8_t* src = is_blob + size_t(is_task) * task_bytes + size_t(is_c) * quarter_bytes;
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq) bulk_g2s(dst + gq * quarter_bytes, src + size_t(gq) * group_bytes, quarter_bytes, full + is_slot);
+            for (int gq = 0; gq < 4; ++gq) copy(dst + gq * quarter_bytes, src + size_t(gq) * group_bytes, quarter_bytes, full + is_slot);
         } else if (GATE_UP) {   // the same K range of the task's two groups, one after the other
             const uint8_t* src = is_blob + size_t(is_task) * task_bytes + size_t(is_c) * half_bytes;
-            bulk_g2s(dst, src, half_bytes, full + is_slot);
-            bulk_g2s(dst + half_bytes, src + group_bytes, half_bytes, full + is_slot);
+            copy(dst, src, half_bytes, full + is_slot);
+            copy(dst + half_bytes, src + group_bytes, half_bytes, full + is_slot);
         } else {
-            bulk_g2s(dst, is_blob + size_t(is_task) * task_bytes + size_t(is_c) * chunk_bytes, chunk_bytes, full + is_slot);
+            copy(dst, is_blob + size_t(is_task) * task_bytes + size_t(is_c) * chunk_bytes, chunk_bytes, full + is_slot);
         }
         if (++is_slot == rpw) is_slot = 0;
         if (++is_c == cpt) {
@@ -1665,6 +1726,13 @@ __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out
                                                          const float* __restrict__ wts, const int32_t* __restrict__ order,
                                                          const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
                                                          int sh_lo, int sh_hi) {   // the shared expert's rows exist for tokens [sh_lo, sh_hi)
+    if (threadIdx.x == 0) {
+        touch_l2(order + size_t(blockIdx.y) * K);
+        touch_l2(wts);
+        touch_l2(y);
+        touch_l2(out + size_t(blockIdx.y) * n);
+        if (ysh) touch_l2(ysh + size_t(blockIdx.y) * n);
+    }
     pdl_wait();
     pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
@@ -1986,6 +2054,7 @@ struct StreamCfg {
 // decode, when every item has at most four tokens: bit 0 = gate/up, bit 1 = down take tasks of four row groups
 // (k_stream's TASK4 form). Measured at batch 64: down gains from it, gate/up does not.
 int g_task4 = 2;
+int g_evict_first = 1;  // decode: the weight copies carry an evict-first L2 policy (see l2_policy_evict_first)
 int g_down_heavy = 22;  // decode: weight of a down task of an item of three or four tokens when the tasks are shared out (16 = as one of a smaller item, 0 = even split by count)
 // decode: the hidden rows are formed and quantized inside down's item-buffer build (no k_quant_hidden launch)
 // from this many tokens on. Measured (148 SMs, hidden 2048, 512 experts top-10): a gain of 2 to 3 us per layer
@@ -2140,6 +2209,10 @@ int set_smem_attr() {
         reinterpret_cast<const void*>(k_stream<false, 16, 2, true>), reinterpret_cast<const void*>(k_stream<false, 16, 0, true>),
         reinterpret_cast<const void*>(k_ffn<4>), reinterpret_cast<const void*>(k_ffn<8>), reinterpret_cast<const void*>(k_ffn<16>)};
     for (const void* f : fns) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    // the head kernel's grouping tables: 12 bytes per expert, 4 per slot, 52 per item (at most 4096 experts, 64 x 32 slots, 2064 items)
+    const void* heads[] = {reinterpret_cast<const void*>(k_prologue<0>), reinterpret_cast<const void*>(k_prologue<4>),
+                           reinterpret_cast<const void*>(k_prologue<16>), reinterpret_cast<const void*>(k_prologue<32>)};
+    for (const void* f : heads) FRX_CUDA(cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 168 * 1024));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return FRX_OK;
 }
@@ -2282,12 +2355,14 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         // the down kernel's tasks are shared out by weight when every item is narrow (see DownSplit)
         DownSplit split{nullptr, sms, n / 64, g_down_heavy};
         if (g_narrow && g_down_heavy > 0 && Tc >= kSplitMinTokens && L.max_items <= 1024 && sms <= kMaxStreamBlocks) split.ranges = reinterpret_cast<int*>(base + L.ranges);
-        const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4 + (split.ranges ? size_t(L.max_items) * 4 : 0);
+        const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4 + (split.ranges ? size_t(L.max_items) * 4 : 0) + size_t(E) * 4 + 16 +
+                           size_t(L.max_items) * sizeof(Item);
         auto head = [&](auto kernel) {
             return launch_pdl_cluster(kernel, dim3(kHeadCluster + qblocks), dim3(1024), dyn, stream, kHeadCluster, logits ? logits + size_t(t0) * E : (const float*)nullptr,
                               ids + size_t(t0) * K, wts + size_t(t0) * K, Tc, K, E, e_lo, e_hi, static_cast<const uint8_t*>(experts), stride,
                               static_cast<const uint8_t*>(shared), items, status, order, L.max_items, x + size_t(t0) * n, n, nblk, xb.q, xb.a,
-                              xb.c, g_narrow ? kNarrowTok : kTokPerItem, split, sh_lo, sh_hi);
+                              xb.c, g_narrow ? kNarrowTok : kTokPerItem, split, sh_lo, sh_hi,
+                              g_stream_stamps ? g_stream_stamps + size_t(sms) * 8 : (unsigned long long*)nullptr);
         };
         if (!logits)
             FRX_LAUNCH(kKPrologue, stream, head(k_prologue<0>));
@@ -2309,6 +2384,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         p.K = K;
         p.TK = Tc * K;
         p.ranges = split.ranges;
+        p.stream_once = g_evict_first;
         if (e_lo > 0 || e_hi < E) {
             p.slot_ids = ids + size_t(t0) * K;
             p.e_lo = e_lo;
@@ -2660,6 +2736,10 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
 int frx_debug_set_down_task_weight(int sixteenths) {
     if (sixteenths < 0 || sixteenths > 64) return fail(FRX_ERR_ARG, "frx_debug_set_down_task_weight: 0 .. 64");
     g_down_heavy = sixteenths;
+    return FRX_OK;
+}
+int frx_debug_set_evict_first(int on) {
+    g_evict_first = on ? 1 : 0;
     return FRX_OK;
 }
 int frx_debug_set_fold_quant(int on) {

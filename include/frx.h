@@ -82,14 +82,19 @@ int frx_debug_set_fused_ffn(int on);
  * item buffers (needs narrow items and four-group tasks in down); 0: a separate quantizer kernel writes them
  * to the workspace first (where frx_decode_workspace_view can read them). Same bits either way. */
 int frx_debug_set_fold_quant(int on);
+/* 1 (default): the decode layer's weight copies mark their L2 lines evict-first (a layer's 326 MB of experts pass
+ * once through a 126 MB L2 and would otherwise push out the kernels' code and the small buffers that are read
+ * again); 0: default policy. */
+int frx_debug_set_evict_first(int on);
 /* Decode layer: the down kernel's tasks are shared out among its blocks by weight, a task of an item of three
  * or four tokens weighing `sixteenths` / 16 of one of a smaller item (default 22; 16 = equal; 0 = an even
  * split by count, made by the kernel itself). Same bits whatever the split. */
 int frx_debug_set_down_task_weight(int sixteenths);
-/* Measurement aid: with a device buffer of 2 * SMs * 4 * 8 bytes set, every launch of the decode layer's two
+/* Measurement aid: with a device buffer of (2 * SMs + 1) * 4 * 8 bytes set, every launch of the decode layer's two
  * streaming kernels (three-kernel form) writes four globaltimer stamps per block there, gate/up's blocks first,
  * then down's: [0] block started, [1] the kernels in front have ended, [2] first item buffer built, [3] block
- * finished. NULL (default) switches it off. */
+ * finished; and block 0 of the layer's first kernel four more behind them: [0] the kernels in front have ended,
+ * [1] its own tokens routed, [2] all tokens routed, [3] work items written. NULL (default) switches it off. */
 int frx_debug_set_stream_stamps(void* device_buffer);
 int frx_debug_set_ffn_buffers(int gate_up, int down);
 int frx_debug_set_wait_limit_ns(unsigned long long ns);
