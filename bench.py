@@ -247,6 +247,8 @@ def run_frx(args):
         moe.check(moe.lib.frx_debug_set_down_task_weight(args.down_weight))
     if args.evict_first is not None:
         moe.check(moe.lib.frx_debug_set_evict_first(args.evict_first))
+    if args.down_item_weight is not None:
+        moe.check(moe.lib.frx_debug_set_down_item_weight(args.down_item_weight))
     if args.fold is not None:
         moe.check(moe.lib.frx_debug_set_fold_quant(args.fold))
     if args.ffn_buffers:
@@ -980,6 +982,7 @@ def main():
     ap.add_argument("--deal-shared", type=int, default=1, help="expert parallel: 1 deals the shared expert's tokens among the ranks, 0 leaves them all to rank 0")
     ap.add_argument("--down-weight", type=int, default=None, help="tuning: weight (in 1/16) of a down task of a 3-4 token item in the split over blocks; 0 = even split")
     ap.add_argument("--evict-first", type=int, default=None, help="tuning: 0 copies the decode layer's weights with the default L2 policy")
+    ap.add_argument("--down-item-weight", type=int, default=None, help="tuning: weight (in 1/16 of a task) of an item's buffer in down's split over blocks")
     ap.add_argument("--fold", type=int, default=None, help="tuning: 0 runs the hidden-row quantizer as its own kernel")
     ap.add_argument("--ffn-buffers", default=None, help="tuning: item buffers of the fused FFN kernel, gate/up,down (e.g. 3,3)")
     ap.add_argument("--task4", type=int, default=None, help="tuning: 0 keeps two row groups per task in the decode layer")

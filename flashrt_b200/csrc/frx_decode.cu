@@ -260,12 +260,13 @@ struct DownSplit {
     int blocks;             // blocks of the down kernel
     int tasks_per_expert;
     int heavy;              // weight of a task of an item of more than two tokens (16 = as light ones)
+    int per_item;           // weight of building an item's buffer, paid by every block that has tasks of the item
 };
 __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32_t* __restrict__ ids, int T, int K, int E, int e_lo,
                                             int e_hi, const uint8_t* __restrict__ experts, size_t stride,
                                             const uint8_t* __restrict__ shared, Item* __restrict__ items, int* __restrict__ status,
                                             int32_t* __restrict__ order, int max_items, int tpi, bool zero_counters = false,
-                                            DownSplit split = DownSplit{nullptr, 0, 0, 16}, int sh_lo = 0, int sh_hi = 1 << 30) {
+                                            DownSplit split = DownSplit{nullptr, 0, 0, 16, 0}, int sh_lo = 0, int sh_hi = 1 << 30) {
     // the shared expert is applied to tokens [sh_lo, sh_hi) (all of them unless the caller deals them among ranks)
     sh_lo = max(sh_lo, 0);
     sh_hi = max(min(sh_hi, T), sh_lo);
@@ -401,18 +402,23 @@ __device__ __forceinline__ void group_block(unsigned long long* dyn, const int32
         const int tpe = split.tasks_per_expert;
         const int last_w = shared_items ? weight_of(min(tpi, sh_hi - sh_lo - (shared_items - 1) * tpi)) : 0;
         const unsigned total_w = unsigned(shared_items ? wgt[n_items - 1] + last_w : routed_weight);
+        // an item also costs every block that touches it one item buffer: `per_item`, in the same units, in front of its tasks
+        const unsigned per_item = unsigned(split.per_item);
+        auto begins = [&](int i) { return unsigned(wgt[i]) * unsigned(tpe) + unsigned(i) * per_item; };   // weight in front of item i
         if (tid == split.blocks) {
             split.ranges[tid] = n_items * tpe;
         } else {
-            const unsigned target = unsigned((unsigned long long)total_w * unsigned(tpe) * unsigned(tid) / unsigned(split.blocks));
-            int lo = 0, hi = n_items - 1;   // the last item whose tasks begin at or before the target
+            const unsigned all = total_w * unsigned(tpe) + unsigned(n_items) * per_item;
+            const unsigned target = unsigned((unsigned long long)all * unsigned(tid) / unsigned(split.blocks));
+            int lo = 0, hi = n_items - 1;   // the last item that begins at or before the target
             while (lo < hi) {
                 const int mid = (lo + hi + 1) >> 1;
-                if (unsigned(wgt[mid]) * unsigned(tpe) <= target) lo = mid;
+                if (begins(mid) <= target) lo = mid;
                 else hi = mid - 1;
             }
-            const unsigned wi = (lo + 1 < n_items ? unsigned(wgt[lo + 1]) : total_w) - unsigned(wgt[lo]);   // the item's own weight
-            const int task = int((target - unsigned(wgt[lo]) * unsigned(tpe)) / wi);
+            const unsigned wi = (lo + 1 < n_items ? unsigned(wgt[lo + 1]) : total_w) - unsigned(wgt[lo]);   // weight of one task of the item
+            const unsigned into = target - begins(lo);
+            const int task = into <= per_item ? 0 : int((into - per_item) / wi);
             split.ranges[tid] = lo * tpe + min(task, tpe - 1);
         }
     }
@@ -2055,6 +2061,7 @@ struct StreamCfg {
 // (k_stream's TASK4 form). Measured at batch 64: down gains from it, gate/up does not.
 int g_task4 = 2;
 int g_evict_first = 1;  // decode: the weight copies carry an evict-first L2 policy (see l2_policy_evict_first)
+int g_down_per_item = 256;   // weight of an item's buffer in down's split, in 1/16 of a task (measured best near 16 tasks: 102.4 us per layer against 103.5 with 0 and 106.5 with 1024)
 int g_down_heavy = 22;  // decode: weight of a down task of an item of three or four tokens when the tasks are shared out (16 = as one of a smaller item, 0 = even split by count)
 // decode: the hidden rows are formed and quantized inside down's item-buffer build (no k_quant_hidden launch)
 // from this many tokens on. Measured (148 SMs, hidden 2048, 512 experts top-10): a gain of 2 to 3 us per layer
@@ -2353,7 +2360,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         const unsigned want = unsigned(std::min<size_t>((nblk + 31) / 32, size_t(sms)));
         const unsigned qblocks = (want + kHeadCluster - 1) / kHeadCluster * kHeadCluster;
         // the down kernel's tasks are shared out by weight when every item is narrow (see DownSplit)
-        DownSplit split{nullptr, sms, n / 64, g_down_heavy};
+        DownSplit split{nullptr, sms, n / 64, g_down_heavy, g_down_per_item};
         if (g_narrow && g_down_heavy > 0 && Tc >= kSplitMinTokens && L.max_items <= 1024 && sms <= kMaxStreamBlocks) split.ranges = reinterpret_cast<int*>(base + L.ranges);
         const size_t dyn = size_t(E) * 8 + size_t(Tc) * K * 4 + (split.ranges ? size_t(L.max_items) * 4 : 0) + size_t(E) * 4 + 16 +
                            size_t(L.max_items) * sizeof(Item);
@@ -2736,6 +2743,11 @@ int frx_moe_combine(float* out, const float* yh, const float* w, const int32_t* 
 int frx_debug_set_down_task_weight(int sixteenths) {
     if (sixteenths < 0 || sixteenths > 64) return fail(FRX_ERR_ARG, "frx_debug_set_down_task_weight: 0 .. 64");
     g_down_heavy = sixteenths;
+    return FRX_OK;
+}
+int frx_debug_set_down_item_weight(int sixteenths) {
+    if (sixteenths < 0 || sixteenths > 4096) return fail(FRX_ERR_ARG, "frx_debug_set_down_item_weight: 0 .. 4096");
+    g_down_per_item = sixteenths;
     return FRX_OK;
 }
 int frx_debug_set_evict_first(int on) {

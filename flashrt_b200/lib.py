@@ -85,6 +85,7 @@ SIGNATURES = {
     "frx_debug_set_fold_quant": (_i, [_i]),
     "frx_debug_set_evict_first": (_i, [_i]),
     "frx_debug_set_down_task_weight": (_i, [_i]),
+    "frx_debug_set_down_item_weight": (_i, [_i]),
     "frx_debug_set_stream_stamps": (_i, [_vp]),
     "frx_debug_set_ffn_buffers": (_i, [_i, _i]),
     "frx_debug_set_wait_limit_ns": (_i, [C.c_ulonglong]),

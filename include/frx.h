@@ -90,6 +90,9 @@ int frx_debug_set_evict_first(int on);
  * or four tokens weighing `sixteenths` / 16 of one of a smaller item (default 22; 16 = equal; 0 = an even
  * split by count, made by the kernel itself). Same bits whatever the split. */
 int frx_debug_set_down_task_weight(int sixteenths);
+/* ... and every item weighs `sixteenths` / 16 tasks more (its item buffer, built by every block that has tasks
+ * of it); default 256. */
+int frx_debug_set_down_item_weight(int sixteenths);
 /* Measurement aid: with a device buffer of (2 * SMs + 1) * 4 * 8 bytes set, every launch of the decode layer's two
  * streaming kernels (three-kernel form) writes four globaltimer stamps per block there, gate/up's blocks first,
  * then down's: [0] block started, [1] the kernels in front have ended, [2] first item buffer built, [3] block

@@ -51,7 +51,7 @@ def test_fixture_from_reference():
     assert np.array_equal(xq, g["xq"]) and np.array_equal(xd, g["xd"])
 
 
-@pytest.mark.parametrize("T", [1, 4, 16, 64])
+@pytest.mark.parametrize("T", [1, 3, 4, 16, 64])
 def test_layer_config_shape(port, T):
     # the benchmark's layer shape with fewer experts (the CPU oracle has to finish in seconds)
     n, ff, E, K = 2048, 512, 48, 10
@@ -298,13 +298,15 @@ def test_narrow_and_wide_item_forms_give_the_same_bits(port):
             check(lib.frx_debug_set_four_group_tasks(2))
             check(lib.frx_debug_set_fold_quant(1))
         assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), (forms, fold)
-    for weight in (0, 16, 40):                                     # how down's tasks are shared out among its blocks (default: 22)
+    for weight, per_item in ((0, 256), (16, 0), (40, 1024)):       # how down's tasks are shared out among its blocks (default: 22, 256)
         try:
             check(lib.frx_debug_set_down_task_weight(weight))
+            check(lib.frx_debug_set_down_item_weight(per_item))
             out_2, ys_2 = run_decode(ex, x, ids, wts, gate)
         finally:
             check(lib.frx_debug_set_down_task_weight(22))
-        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), weight
+            check(lib.frx_debug_set_down_item_weight(256))
+        assert np.array_equal(ys_2, ys_w) and np.array_equal(out_2, out_w), (weight, per_item)
     for bufs in ((0, 0), (2, 2), (4, 3)):                          # the FFN as one kernel, with different numbers of item buffers
         try:
             check(lib.frx_debug_set_fused_ffn(1))
