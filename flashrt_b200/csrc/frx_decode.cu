@@ -1727,32 +1727,58 @@ __global__ void __launch_bounds__(NW * 32, 1) k_ffn(const StreamParams p) {
     }
 }
 
-// out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate)
+// out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate).
+// A thread owns four consecutive elements of one token. The order entries, the weights and the rows
+// of eight slots at a time are loaded before the first addition (the loads do not depend on one
+// another, the additions keep their order), so the kernel is three round trips to memory long
+// instead of two per slot.
+constexpr int kCombineElems = 4, kCombineBatch = 8;
 __global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out, const float* __restrict__ y,
                                                          const float* __restrict__ wts, const int32_t* __restrict__ order,
                                                          const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
                                                          int sh_lo, int sh_hi) {   // the shared expert's rows exist for tokens [sh_lo, sh_hi)
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * kCombineElems, t = blockIdx.y;   // n is a multiple of 128: four elements are all inside or all outside
     if (threadIdx.x == 0) {
-        touch_l2(order + size_t(blockIdx.y) * K);
+        touch_l2(order + size_t(t) * K);
         touch_l2(wts);
         touch_l2(y);
-        touch_l2(out + size_t(blockIdx.y) * n);
-        if (ysh) touch_l2(ysh + size_t(blockIdx.y) * n);
+        touch_l2(out + size_t(t) * n);
+        if (ysh) touch_l2(ysh + size_t(t) * n);
     }
     pdl_wait();
     pdl_trigger();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (i >= n) return;
-    float acc = 0.0f;
-    for (int k = 0; k < K; ++k) {
-        const int s = order[t * K + k];
-        if (s >= 0) acc = __fadd_rn(acc, __fmul_rn(wts[s], y[size_t(s) * n + i]));
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int k0 = 0; k0 < K; k0 += kCombineBatch) {
+        int s[kCombineBatch];
+        float w[kCombineBatch];
+        float4 v[kCombineBatch];
+#pragma unroll
+        for (int j = 0; j < kCombineBatch; ++j) s[j] = k0 + j < K ? order[t * K + k0 + j] : -1;
+#pragma unroll
+        for (int j = 0; j < kCombineBatch; ++j)
+            if (s[j] >= 0) {
+                w[j] = wts[s[j]];
+                v[j] = *reinterpret_cast<const float4*>(y + size_t(s[j]) * n + i);
+            }
+#pragma unroll
+        for (int j = 0; j < kCombineBatch; ++j)
+            if (s[j] >= 0) {
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w[j], v[j].x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(w[j], v[j].y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w[j], v[j].z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(w[j], v[j].w));
+            }
     }
     if (ysh && t >= sh_lo && t < sh_hi) {
         const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
-        acc = __fadd_rn(acc, __fmul_rn(ysh[size_t(t) * n + i], g));
+        const float4 v = *reinterpret_cast<const float4*>(ysh + size_t(t) * n + i);
+        acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, g));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, g));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, g));
     }
-    out[size_t(t) * n + i] = acc;
+    *reinterpret_cast<float4*>(out + size_t(t) * n + i) = acc;
 }
 
 // ---- combine fused with the expert-parallel all-reduce over peer memory
@@ -2316,6 +2342,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
     if (logits && (E > 1024 || K > E)) return fail(FRX_ERR_SHAPE, "frx_moe_layer: unsupported router shape E %d, k %d", E, K);
     if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
+    if ((uintptr_t(out) | uintptr_t(yslot)) % 16) return fail(FRX_ERR_ARG, "frx_moe_decode: out and the per-slot output must be 16-byte aligned");
     if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_decode: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
     if (T == 0) return FRX_OK;
     const Layout L = make_layout(T, K, n, ff);
@@ -2406,7 +2433,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
                                                             (const float*)p.y, (const float*)wts, (const int32_t*)order,
                                                             (const float*)(shared ? p.ysh : nullptr), gate_logit, n, K, epc, status));
         } else
-            FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 255) / 256, Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
+            FRX_LAUNCH(kKCombine, stream, launch_pdl(k_combine_ordered, dim3((n + 256 * kCombineElems - 1) / (256 * kCombineElems), Tc), dim3(256), 0, stream, out + size_t(t0) * n, (const float*)p.y,
                                                             (const float*)(wts + size_t(t0) * K), (const int32_t*)order, (const float*)(shared ? p.ysh : nullptr),
                                                             gate_logit ? gate_logit + t0 : (const float*)nullptr, n, K, sh_lo, sh_hi));
     }

@@ -183,7 +183,8 @@ int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q
  * experts: tiled blobs at experts + e * stride, e < E. shared: one tiled blob or null.
  * gate_logit [T] or null (weight 1). ids, wts [T][K] as frx_route_topk writes them.
  * yslot (may be null): per-slot expert outputs [T*K][n], slot t*K+k, the moe_q2::run / moe_hits
- * output contract. n % 128 == 0, ff % 128 == 0, K <= 32, n <= 8192, ff <= 8192. */
+ * output contract. n % 128 == 0, ff % 128 == 0, K <= 32, n <= 8192, ff <= 8192; out and yslot
+ * 16-byte aligned. */
 size_t frx_moe_decode_workspace_bytes(int T, int K, int n, int ff);
 int frx_moe_decode(const void* experts, size_t stride, int E, const void* shared, int n, int ff, const float* x,
                    const int32_t* ids, const float* wts, const float* gate_logit, int T, int K, float* out, float* yslot,
