@@ -904,8 +904,11 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     // items were complete: down reads the items and starts streaming its weights (constant data)
     // while the quantizer is still running, and waits for it only before it touches the hidden rows.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned long long* stamp = p.stamps ? p.stamps + size_t(blockIdx.x) * 4 : nullptr;
-    if (stamp && threadIdx.x == 0) stamp[0] = global_ns();   // the block has started
+    // (measurement aid: nothing is kept in a register for it, the pointer is a launch parameter)
+    auto stamp_now = [&](int i) {
+        if (p.stamps && threadIdx.x == 0) p.stamps[size_t(blockIdx.x) * 4 + i] = global_ns();
+    };
+    stamp_now(0);   // the block has started
     const int kdim = GATE_UP ? p.n : p.ff;
     const int nb = kdim / kQK, units = kdim / kUnitK;
     const uint32_t group_bytes = uint32_t(units) * kUnitBytes;
@@ -987,12 +990,9 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         is_task = int(tau % tasks_per_expert);
         if (is_i < ntasks) is_blob = item_blob(is_item) + section;
     }
-    const uint64_t l2pol = l2_policy_evict_first();   // used when the weights are read once (decode): see l2_policy_evict_first
-    const bool once = p.stream_once != 0;
-    auto copy = [&](void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-        if (once) bulk_g2s_hint(dst, src, bytes, bar, l2pol);
-        else bulk_g2s(dst, src, bytes, bar);
-    };
+    // weights that are read once (decode) are marked evict-first in the L2: see l2_policy_evict_first
+    const uint64_t l2pol = p.stream_once ? l2_policy_evict_first() : l2_policy_evict_normal();
+    auto copy = [&](void* dst, const void* src, uint32_t bytes, uint64_t* bar) { bulk_g2s_hint(dst, src, bytes, bar, l2pol); };
     auto issue_next = [&]() {   // lane 0 only
         if (is_i >= ntasks) return;
         mbar_expect_tx(full + is_slot, chunk_bytes);
@@ -1131,7 +1131,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     };
     const int ahead = nbuf - 1;
     if (!GATE_UP) pdl_wait();   // the first weight chunks are already in flight
-    if (stamp && threadIdx.x == 0) stamp[1] = global_ns();   // the kernels in front have ended, the first copies are issued
+    stamp_now(1);   // the kernels in front have ended, the first copies are issued
     if (ahead == 2 && nseg >= 2) {   // the first two items side by side: one half of the warps each
         constexpr int H = NW / 2;
         build(warp < H ? 0 : 1, warp < H ? ctid : ctid - H * 32, warp < H ? H * 32 : (NW - H) * 32);
@@ -1150,7 +1150,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     for (int q = 0; q < nseg; ++q) {
         const int item = first_item + q, buf = q % nbuf;
         mbar_wait_bounded(ready + buf, uint32_t(q / nbuf) & 1u, abort, p.wait_ns);
-        if (stamp && q == 0 && threadIdx.x == 0) stamp[2] = global_ns();   // the first item buffer is built
+        if (q == 0) stamp_now(2);   // the first item buffer is built
         const long long seg_hi = min(hi, (long long)(item + 1) * tasks_per_expert);
         const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.bfrag + buf * (nb * 512));
         const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.da + buf * (nb * 64));
@@ -1311,7 +1311,7 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
         }
     }
     __syncthreads();
-    if (stamp && threadIdx.x == 0) stamp[3] = global_ns();   // every warp of the block has finished
+    stamp_now(3);   // every warp of the block has finished
     if (*abort) {
         // A wait ran out: report it, and give copies still in flight time to land before the
         // block's shared memory is released.
