@@ -50,7 +50,7 @@ N_MODEL, FF, E, K, LAYERS = 2048, 512, 512, 10, 48
 EXPERT_BYTES = 884736
 GU_BYTES = 589824          # gate + up of one expert
 NCU_FFN_TRAFFIC_PER_BLOB = None            # the same for one launch of the fused kernel (k_ffn)
-NCU_GU_TRAFFIC_PER_BLOB = 224.1e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
+NCU_GU_TRAFFIC_PER_BLOB = 223.7e6 / 367    # DRAM read + write bytes per distinct expert blob of one gate/up launch (an ncu capture of a 2-layer case)
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "q2_0_moe_layer_tokens_per_s"
 UNIT = "layer-tokens/s"
