@@ -66,3 +66,15 @@ def test_expert_ranges_partition_every_count():
             r = [expert_range(k, world, E) for k in range(world)]
             assert r[0][0] == 0 and r[-1][1] == E
             assert all(r[i][1] == r[i + 1][0] for i in range(world - 1))
+
+
+def test_shared_expert_token_ranges_partition_the_tokens_in_whole_items():
+    # with the shared expert dealt among the ranks, every token is taken by exactly one rank and the
+    # cuts fall on work-item boundaries (four tokens)
+    from flashrt_b200.ep import shared_token_range
+    for T in (64, 63, 5, 3, 1):
+        for world in (1, 2, 4, 8):
+            r = [shared_token_range(k, world, T) for k in range(world)]
+            assert r[0][0] == 0 and r[-1][1] == T
+            assert all(r[i][1] == r[i + 1][0] for i in range(world - 1))
+            assert all(lo % 4 == 0 and (hi % 4 == 0 or hi == T) for lo, hi in r)

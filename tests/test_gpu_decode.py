@@ -351,3 +351,30 @@ def test_full_layer_shape_on_a_slot_sample(port, T):
         want = port.moe_layer(np.ascontiguousarray(ex.planar[ids[t][by_id]]), ex.blob_bytes, ex.shared_planar, n, ff, x[t:t + 1],
                               np.arange(K, dtype=np.int32)[None], wts[t:t + 1][:, by_id], gate[t:t + 1])
         assert rel_max(got[t:t + 1], want) < 1e-5
+
+
+def test_stream_stamps_are_written_and_ordered(port):
+    # the measurement aid: four time stamps per block of the two streaming kernels, four of the head
+    from flashrt_b200.lib import check, lib
+    import ctypes as C
+    n, ff, E, K, T = 1024, 256, 96, 6, 40
+    ex = Experts(port, n, ff, E, direct=True)
+    x = synth.activations(T, n)
+    ids, wts, _ = port.route(synth.router_logits(T, E), K)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    st = torch.zeros((2 * sms + 1) * 4, dtype=torch.int64, device="cuda")
+    want, _ = run_decode(ex, x, ids, wts, None)
+    try:
+        check(lib.frx_debug_set_stream_stamps(C.c_void_p(st.data_ptr())))
+        got, _ = run_decode(ex, x, ids, wts, None)
+    finally:
+        check(lib.frx_debug_set_stream_stamps(None))
+    assert np.array_equal(got, want)
+    s = st.cpu().numpy()
+    gu, dn, head = s[:sms * 4].reshape(sms, 4), s[sms * 4:2 * sms * 4].reshape(sms, 4), s[2 * sms * 4:]
+    busy = gu[:, 3] > 0                                   # blocks that had tasks
+    assert busy.any() and (np.diff(gu[busy], axis=1) >= 0).all()
+    busy = dn[:, 3] > 0
+    assert busy.any() and (np.diff(dn[busy], axis=1) >= 0).all()
+    assert (np.diff(head) >= 0).all() and head[0] > 0
+    assert head[3] <= gu[gu[:, 1] > 0, 1].min()           # gate/up's wait returns after the head has written the items
