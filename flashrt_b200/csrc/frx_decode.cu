@@ -120,23 +120,40 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
 //                  through a float pointer: the value an MMA accumulator starts from, so that it
 //                  ends as kMagicBits + sum((q - 1) * code), which read as a float is kMagic plus
 //                  that sum, exactly.
-__device__ __forceinline__ void quant_frag_value(float v, int k, size_t blk, int lane, int8_t* __restrict__ q, float* __restrict__ a,
-                                                 float* __restrict__ c, float partner = 0.0f) {
-    float d;
-    int sum;
-    const int code = q8_block(v, d, sum, partner);
-    const int bpr = k / kQ8;
+// A thread owns four consecutive values (one 16-byte load, one word of codes out), eight
+// neighbouring lanes one 32-block: `quad` is the index of the thread's four values, all lanes of a
+// warp call it together, `live` is false beyond the end. With `block64` the scale is shared by the
+// two 32-blocks of a 64-block (moe_q2::run's block64 option, kernels/cuda/moe_q2.cu:58-77).
+__device__ __forceinline__ void quant_frag_quad(const float* __restrict__ x, int k, size_t quad, bool live, int8_t* __restrict__ q,
+                                                float* __restrict__ a, float* __restrict__ c, bool block64 = false) {
+    const float4 v = live ? reinterpret_cast<const float4*>(x)[quad] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float hv[4] = {v.x, v.y, v.z, v.w};
+    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if (block64) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));   // sixteen lanes hold one 64-block
+    const float d = __fdiv_rn(am, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int code[4], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
+        sum += code[i];
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (!live) return;
+    const size_t blk = quad >> 3;
+    const int bpr = k / kQ8, j = int(quad & 7);
     const size_t row = blk / bpr;
-    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
-    q[row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
-    if (lane == 0) {
-        a[blk] = s ? d * 0.0625f : d;
+    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = j >> 2, t = j & 3;
+    reinterpret_cast<uint32_t*>(q + row * k)[(b * 4 + t) * 4 + s * 2 + hi] =
+        uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
+    if (j == 0) {
+        const float ds = __half2float(__float2half_rn(d));
+        a[blk] = s ? ds * 0.0625f : ds;
         c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
     }
-}
-__device__ __forceinline__ void quant_frag_block(const float* __restrict__ x, int k, size_t blk, int lane, int8_t* __restrict__ q,
-                                                 float* __restrict__ a, float* __restrict__ c, bool block64 = false) {
-    quant_frag_value(x[blk * kQ8 + lane], k, blk, lane, q, a, c, block64 ? x[(blk ^ 1) * kQ8 + lane] : 0.0f);
 }
 // The hidden rows: gu holds (gate x, up x) pairs; h = silu(gate x) * up x is formed here, where
 // there are thousands of independent threads to hide the latency of the exponential, stored, and
@@ -210,21 +227,24 @@ __global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__
 }
 // Activations that arrive already quantized (natural order: codes [rows][k] int8, block scales
 // [rows][k/32] float, as frx_quantize_q8 writes them) into the fragment form above: a permutation
-// of the codes, the scale table, and the accumulator inputs from the block sums of the codes.
+// of the code words, the scale table, and the accumulator inputs from the block sums of the codes.
+// A thread owns four consecutive codes (one word in, one word out), eight neighbouring lanes one
+// 32-block.
 __global__ void __launch_bounds__(256) k_q8_to_frag(const int8_t* __restrict__ xq, const float* __restrict__ xd, int k, size_t n_blocks,
                                                     int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (blk >= n_blocks) return;
-    const int code = xq[blk * kQ8 + lane];
-    int sum = code;
+    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;
+    const size_t blk = quad >> 3;
+    const bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
+    const uint32_t w = live ? reinterpret_cast<const uint32_t*>(xq)[quad] : 0u;
+    int sum = __dp4a(int(w), 0x01010101, 0);   // the four signed codes added up
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const int bpr = k / kQ8;
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (!live) return;
+    const int bpr = k / kQ8, j = int(quad & 7);
     const size_t row = blk / bpr;
-    const int rb = int(blk % bpr), b = rb >> 1, sh = rb & 1, hi = lane >> 4, t = (lane >> 2) & 3;
-    q[row * k + ((b * 4 + t) * 4 + sh * 2 + hi) * 4 + (lane & 3)] = int8_t(code);
-    if (lane == 0) {
+    const int rb = int(blk % bpr), b = rb >> 1, sh = rb & 1, hi = j >> 2, t = j & 3;
+    reinterpret_cast<uint32_t*>(q + row * k)[(b * 4 + t) * 4 + sh * 2 + hi] = w;
+    if (j == 0) {
         const float d = xd[blk];
         a[blk] = sh ? d * 0.0625f : d;
         c[blk] = __int_as_float(kMagicBits - (sh ? 16 * sum : sum));
@@ -235,8 +255,8 @@ __global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x,
                                                     float* __restrict__ a, float* __restrict__ c, int block64) {
     pdl_wait();
     pdl_trigger();
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (blk < n_blocks) quant_frag_block(x, k, blk, threadIdx.x & 31, q, a, c, block64 != 0);
+    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // (the number of blocks is a multiple of four: warps are live as a whole)
+    quant_frag_quad(x, k, quad, quad < n_blocks * 8, q, a, c, block64 != 0);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -464,7 +484,7 @@ __global__ void __launch_bounds__(1024) k_prologue(const float* __restrict__ log
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (blockIdx.x >= kHeadCluster) {
         const size_t qb = blockIdx.x - kHeadCluster, nqb = gridDim.x - kHeadCluster;
-        for (size_t blk = qb * 32 + warp; blk < n_blocks; blk += nqb * 32) quant_frag_block(x, n, blk, lane, xq, xa, xc);
+        for (size_t quad = qb * 1024 + threadIdx.x; quad < n_blocks * 8; quad += nqb * 1024) quant_frag_quad(x, n, quad, true, xq, xa, xc);
         return;
     }
     const int rank = int(cluster_ctarank());   // cluster 0 is blocks 0 .. kHeadCluster - 1
@@ -2261,7 +2281,7 @@ struct ActBufs {
 // (The grouping kernel that fills p.items may be enqueued before or after the first quantizer.)
 void launch_quant_x(const float* x, int x_rows, int n, const ActBufs& xb, cudaStream_t stream, int block64 = 0) {
     const size_t nblk = size_t(x_rows) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk + 7) / 8)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c, block64));
+    FRX_LAUNCH(kKQuant, stream, launch_pdl(k_quant_frag, dim3(unsigned((nblk * 8 + 255) / 256)), dim3(256), 0, stream, x, n, nblk, xb.q, xb.a, xb.c, block64));
 }
 
 void launch_ffn(StreamParams p, const ActBufs& xb, const ActBufs& hb, size_t h_rows, const StreamCfg& cfg, cudaStream_t stream,
@@ -2342,7 +2362,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
     if (logits && (E > 1024 || K > E)) return fail(FRX_ERR_SHAPE, "frx_moe_layer: unsupported router shape E %d, k %d", E, K);
     if ((uintptr_t(experts) | uintptr_t(shared) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_decode: experts, shared and stride must be 16-byte aligned, ws 256-byte aligned");
-    if ((uintptr_t(out) | uintptr_t(yslot)) % 16) return fail(FRX_ERR_ARG, "frx_moe_decode: out and the per-slot output must be 16-byte aligned");
+    if ((uintptr_t(out) | uintptr_t(yslot) | uintptr_t(x)) % 16) return fail(FRX_ERR_ARG, "frx_moe_decode: x, out and the per-slot output must be 16-byte aligned");
     if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_decode: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
     if (T == 0) return FRX_OK;
     const Layout L = make_layout(T, K, n, ff);
@@ -2384,7 +2404,7 @@ int decode_steps(const void* experts, size_t stride, int E, int e_lo, int e_hi, 
         // the tokens of this chunk that get the shared expert here
         const int sh_lo = std::min(std::max(shared_t0 - t0, 0), Tc), sh_hi = std::max(std::min(shared_t1 - t0, Tc), sh_lo);
         const size_t nblk = size_t(Tc) * (n / kQ8);
-        const unsigned want = unsigned(std::min<size_t>((nblk + 31) / 32, size_t(sms)));
+        const unsigned want = unsigned(std::min<size_t>((nblk + 127) / 128, size_t(sms)));   // a block of 1024 threads quantizes 128 blocks of 32 values per pass
         const unsigned qblocks = (want + kHeadCluster - 1) / kHeadCluster * kHeadCluster;
         // the down kernel's tasks are shared out by weight when every item is narrow (see DownSplit)
         DownSplit split{nullptr, sms, n / 64, g_down_heavy, g_down_per_item};
@@ -2868,7 +2888,7 @@ int frx_moe_hits(const uint8_t* const* hit_ptr, const int32_t* hit_n, int K, con
     if (!hit_ptr || !hit_n || !x || !scratch || !yh) return fail(FRX_ERR_ARG, "frx_moe_hits: null pointer");
     if (int rc = check_moe_shape("frx_moe_hits", n, ff, K)) return rc;
     if (T < 1 || T * K > 1024) return fail(FRX_ERR_SHAPE, "frx_moe_hits: unsupported window T %d x K %d (T * K <= 1024)", T, K);
-    if (uintptr_t(scratch) % kAlign) return fail(FRX_ERR_ARG, "frx_moe_hits: scratch must be 256-byte aligned");
+    if (uintptr_t(scratch) % kAlign || uintptr_t(x) % 16) return fail(FRX_ERR_ARG, "frx_moe_hits: scratch must be 256-byte aligned, x 16-byte aligned");
     const HitsLayout L = hits_layout(K, n, ff, T);
     if (scratch_bytes < L.total) return fail(FRX_ERR_WORKSPACE, "frx_moe_hits: scratch %zu < %zu", scratch_bytes, L.total);
     StreamCfg cfg;
@@ -2937,6 +2957,7 @@ int prefill_stream_impl(const void* experts, size_t stride, int E, const int32_t
     if (int rc = check_moe_shape("frx_moe_prefill", n, ff, K)) return rc;
     if (T < 0 || E < 1 || E > 4096 || E_all < E || E_all > 4096 || size_t(T) * K > (size_t(1) << 30))
         return fail(FRX_ERR_SHAPE, "frx_moe_prefill: unsupported T %d, E %d (of %d)", T, E, E_all);
+    if ((uintptr_t(x) % 16) || (uintptr_t(xq) % 4)) return fail(FRX_ERR_ARG, "frx_moe_prefill: x must be 16-byte aligned, xq 4-byte aligned");
     if ((uintptr_t(experts) | stride) % 16 || uintptr_t(ws) % kAlign)
         return fail(FRX_ERR_ARG, "frx_moe_prefill: experts and stride must be 16-byte aligned, ws 256-byte aligned");
     if (stride < frx_q2_expert_bytes(n, ff)) return fail(FRX_ERR_ARG, "frx_moe_prefill: stride %zu < blob %zu", stride, frx_q2_expert_bytes(n, ff));
@@ -2957,7 +2978,7 @@ int prefill_stream_impl(const void* experts, size_t stride, int E, const int32_t
     const ActBufs xb = act_x(base, L);
     if (xq) {
         const size_t nblk = size_t(T) * (n / kQ8);
-        FRX_LAUNCH(kKQuant, stream, k_q8_to_frag<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(xq, xd, n, nblk, xb.q, xb.a, xb.c));
+        FRX_LAUNCH(kKQuant, stream, k_q8_to_frag<<<unsigned((nblk * 8 + 255) / 256), 256, 0, stream>>>(xq, xd, n, nblk, xb.q, xb.a, xb.c));
     } else {
         launch_quant_x(x, T, n, xb, stream, block64);
     }

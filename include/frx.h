@@ -10,6 +10,9 @@
  *   - every pointer is a device pointer unless its name ends in _host;
  *   - row-major, token-major layouts; the caller owns inputs, outputs and workspaces and asks
  *     the *_bytes functions for sizes; nothing is allocated by a compute call;
+ *   - activation and output buffers ([T][n] float rows, per-slot rows) are 16-byte aligned, int8
+ *     code buffers 4-byte aligned (n is a multiple of 128, so every row is when the base is);
+ *     a misaligned pointer is refused with FRX_ERR_ARG;
  *   - work is enqueued on the caller's stream, with no host synchronisation;
  *   - a call returns FRX_OK or an error code and never throws; frx_last_error() gives the text
  *     of the calling thread's last error.
