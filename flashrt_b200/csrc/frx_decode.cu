@@ -109,6 +109,27 @@ __global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, s
     }
 }
 
+// The same with a thread owning four consecutive values (x 16-byte aligned, q 4-byte aligned): one
+// 16-byte load and one word of codes per thread, eight neighbouring lanes one block.
+__global__ void __launch_bounds__(256) k_quant_q8_quads(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ q,
+                                                        float* __restrict__ d) {
+    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;
+    const bool live = quad < n_blocks * 8;   // no early exit: the shuffles need the whole warp
+    const float4 v = live ? reinterpret_cast<const float4*>(x)[quad] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float hv[4] = {v.x, v.y, v.z, v.w};
+    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float dd = __fdiv_rn(am, 127.0f);
+    const float id = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) word |= uint32_t(int(round_half_away(__fmul_rn(hv[i], id))) & 0xff) << (8 * i);
+    if (!live) return;
+    reinterpret_cast<uint32_t*>(q)[quad] = word;
+    if ((quad & 7) == 0) d[quad >> 3] = __half2float(__float2half_rn(dd));
+}
+
 // Activations in the form the expert kernel consumes, one row per token (x) or per slot (h):
 //   q [row][k]     int8 codes in MMA-B fragment order: the four bytes of element group
 //                  (b, s, hi, t) -- elements 64b + 32s + 16hi + 4t .. +3 -- are word
@@ -2473,7 +2494,10 @@ int frx_quantize_q8(frx_stream_t stream, const float* x, int T, int n, int8_t* q
     if (T == 0) return FRX_OK;   // an empty batch: nothing to do, pointers may be null
     if (!x || !q || !d) return fail(FRX_ERR_ARG, "frx_quantize_q8: null pointer");
     const size_t nblk = size_t(T) * (n / kQ8);
-    FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr));
+    if (uintptr_t(x) % 16 == 0 && uintptr_t(q) % 4 == 0)
+        FRX_LAUNCH(kKQuant, stream, k_quant_q8_quads<<<unsigned((nblk * 8 + 255) / 256), 256, 0, stream>>>(x, nblk, q, d));
+    else
+        FRX_LAUNCH(kKQuant, stream, k_quant_q8<<<unsigned((nblk + 7) / 8), 256, 0, stream>>>(x, nblk, q, d, nullptr));
     FRX_CUDA(cudaGetLastError());
     return FRX_OK;
 }

@@ -73,6 +73,13 @@ def test_quantize_q8_bit_exact(port):
     assert np.array_equal(q.cpu().numpy(), oq)
     assert np.array_equal(d.cpu().numpy(), od)
     assert list(oq[5, :4]) == [127, 3, -3, 1]
+    # the same rows from a buffer that is only 4-byte aligned (the one-value-per-lane form of the kernel)
+    buf = torch.empty(x.size + 1, device="cuda")
+    shifted = buf[1:].view(x.shape)
+    shifted.copy_(cuda(x))
+    assert shifted.data_ptr() % 16 == 4
+    q2, d2 = moe.quantize_q8(shifted)
+    assert torch.equal(q2, q) and torch.equal(d2, d)
 
 
 def test_quantize_q8_empty_and_bad_shape():
