@@ -73,212 +73,7 @@ Layout make_layout(int T, int K, int n, int ff) {
     return L;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Q8 quantization of 32 values held one per lane: returns the code; lane 0 gets scale and sum.
-// quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16.
-// `partner`: with activation blocks of 64 (moe_q2::run's block64 option, kernels/cuda/moe_q2.cu:58-77)
-// the value at the same place of the other half of the 64-block, which shares the scale; else 0.
-__device__ __forceinline__ int q8_block(float v, float& d_out, int& sum_out, float partner = 0.0f) {
-    float am = fmaxf(fabsf(v), fabsf(partner));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    const float d = __fdiv_rn(am, 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    const int q = int(round_half_away(__fmul_rn(v, id)));
-    int s = q;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    d_out = __half2float(__float2half_rn(d));
-    sum_out = s;
-    return q;
-}
-
-// x [T][n] -> q [T][n], d [T][n/32], and (optionally) the block sums of the codes.
-__global__ void __launch_bounds__(256) k_quant_q8(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ q,
-                                                  float* __restrict__ d, int32_t* __restrict__ sums) {
-    const size_t blk = size_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (blk >= n_blocks) return;
-    float dd;
-    int ss;
-    const int c = q8_block(x[blk * kQ8 + lane], dd, ss);
-    q[blk * kQ8 + lane] = int8_t(c);
-    if (lane == 0) {
-        d[blk] = dd;
-        if (sums) sums[blk] = ss;
-    }
-}
-
-// The same with a thread owning four consecutive values (x 16-byte aligned, q 4-byte aligned): one
-// 16-byte load and one word of codes per thread, eight neighbouring lanes one block.
-__global__ void __launch_bounds__(256) k_quant_q8_quads(const float* __restrict__ x, size_t n_blocks, int8_t* __restrict__ q,
-                                                        float* __restrict__ d) {
-    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;
-    const bool live = quad < n_blocks * 8;   // no early exit: the shuffles need the whole warp
-    const float4 v = live ? reinterpret_cast<const float4*>(x)[quad] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const float hv[4] = {v.x, v.y, v.z, v.w};
-    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    const float dd = __fdiv_rn(am, 127.0f);
-    const float id = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
-    uint32_t word = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) word |= uint32_t(int(round_half_away(__fmul_rn(hv[i], id))) & 0xff) << (8 * i);
-    if (!live) return;
-    reinterpret_cast<uint32_t*>(q)[quad] = word;
-    if ((quad & 7) == 0) d[quad >> 3] = __half2float(__float2half_rn(dd));
-}
-
-// Activations in the form the expert kernel consumes, one row per token (x) or per slot (h):
-//   q [row][k]     int8 codes in MMA-B fragment order: the four bytes of element group
-//                  (b, s, hi, t) -- elements 64b + 32s + 16hi + 4t .. +3 -- are word
-//                  (b * 4 + t) * 4 + s * 2 + hi, so lane (g, t) of a warp finds the B fragments of
-//                  block b for its token in one 16-byte load;
-//   a [row][k/32]  the block scale d (through fp16), divided by 16 for the second half of a
-//                  64-block (see group_mma);
-//   c [row][k/32]  the int32 kMagicBits - sum(codes) (the sum times 16 for the second half), stored
-//                  through a float pointer: the value an MMA accumulator starts from, so that it
-//                  ends as kMagicBits + sum((q - 1) * code), which read as a float is kMagic plus
-//                  that sum, exactly.
-// A thread owns four consecutive values (one 16-byte load, one word of codes out), eight
-// neighbouring lanes one 32-block: `quad` is the index of the thread's four values, all lanes of a
-// warp call it together, `live` is false beyond the end. With `block64` the scale is shared by the
-// two 32-blocks of a 64-block (moe_q2::run's block64 option, kernels/cuda/moe_q2.cu:58-77).
-__device__ __forceinline__ void quant_frag_quad(const float* __restrict__ x, int k, size_t quad, bool live, int8_t* __restrict__ q,
-                                                float* __restrict__ a, float* __restrict__ c, bool block64 = false) {
-    const float4 v = live ? reinterpret_cast<const float4*>(x)[quad] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const float hv[4] = {v.x, v.y, v.z, v.w};
-    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    if (block64) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));   // sixteen lanes hold one 64-block
-    const float d = __fdiv_rn(am, 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    int code[4], sum = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
-        sum += code[i];
-    }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (!live) return;
-    const size_t blk = quad >> 3;
-    const int bpr = k / kQ8, j = int(quad & 7);
-    const size_t row = blk / bpr;
-    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = j >> 2, t = j & 3;
-    reinterpret_cast<uint32_t*>(q + row * k)[(b * 4 + t) * 4 + s * 2 + hi] =
-        uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
-    if (j == 0) {
-        const float ds = __half2float(__float2half_rn(d));
-        a[blk] = s ? ds * 0.0625f : ds;
-        c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
-    }
-}
-// The hidden rows: gu holds (gate x, up x) pairs; h = silu(gate x) * up x is formed here, where
-// there are thousands of independent threads to hide the latency of the exponential, stored, and
-// quantized like x. A thread owns four consecutive values (one word of codes in fragment order),
-// eight neighbouring lanes one 32-block.
-// With `slot_ids` (expert parallel), routed rows whose expert lies outside [e_lo, e_hi) are skipped:
-// another rank computes them, and nothing here reads their hidden values.
-__global__ void __launch_bounds__(256) k_quant_hidden(const float2* __restrict__ gu, int k, size_t n_blocks, float* __restrict__ h,
-                                                      int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c,
-                                                      const int32_t* __restrict__ slot_ids, int routed_rows, int e_lo, int e_hi,
-                                                      int block64, const int32_t* __restrict__ e_map,
-                                                      const int32_t* __restrict__ row_list, const int* __restrict__ row_count, int store_h) {
-    pdl_wait();
-    pdl_trigger();
-    size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // four values each
-    size_t blk = quad >> 3;
-    bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
-    if (row_list) {
-        // only the listed rows (the slots a grouping placed, in grouped order) are visited: the i-th
-        // row of blocks belongs to row row_list[i]; beyond row_count there is nothing to do
-        const size_t bpr = size_t(k / kQ8), i = blk / bpr;
-        live = live && i < size_t(*row_count);
-        if (live) {
-            blk = size_t(row_list[i]) * bpr + blk % bpr;
-            quad = blk * 8 + (quad & 7);
-        }
-    } else if (live && slot_ids) {
-        const size_t r = blk / size_t(k / kQ8);
-        if (r < size_t(routed_rows)) {
-            const int e = slot_ids[r];
-            live = e_map ? e_map[e] >= 0 : (e >= e_lo && e < e_hi);   // (ids were range-checked by the grouping kernels)
-        }
-    }
-    const int j = int(quad & 7);        // values 4 j .. 4 j + 3 of the block
-    float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (live) {
-        const float4* src = reinterpret_cast<const float4*>(gu + quad * 4);
-        const float4 g0 = src[0], g1 = src[1];
-        hv[0] = swiglu_ref(g0.x, g0.y);
-        hv[1] = swiglu_ref(g0.z, g0.w);
-        hv[2] = swiglu_ref(g1.x, g1.y);
-        hv[3] = swiglu_ref(g1.z, g1.w);
-        if (store_h) *reinterpret_cast<float4*>(h + quad * 4) = make_float4(hv[0], hv[1], hv[2], hv[3]);
-    }
-    // quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id), d through fp16
-    float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    if (block64) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));   // sixteen lanes hold one 64-block
-    const float d = __fdiv_rn(am, 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    int code[4], sum = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
-        sum += code[i];
-    }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (!live) return;
-    const int bpr = k / kQ8;
-    const size_t row = blk / bpr;
-    const int rb = int(blk % bpr), b = rb >> 1, s = rb & 1, hi = j >> 2, t = j & 3;
-    const uint32_t word = uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
-    *reinterpret_cast<uint32_t*>(q + row * k + ((b * 4 + t) * 4 + s * 2 + hi) * 4) = word;
-    if (j == 0) {
-        const float ds = __half2float(__float2half_rn(d));
-        a[blk] = s ? ds * 0.0625f : ds;
-        c[blk] = __int_as_float(kMagicBits - (s ? 16 * sum : sum));
-    }
-}
-// Activations that arrive already quantized (natural order: codes [rows][k] int8, block scales
-// [rows][k/32] float, as frx_quantize_q8 writes them) into the fragment form above: a permutation
-// of the code words, the scale table, and the accumulator inputs from the block sums of the codes.
-// A thread owns four consecutive codes (one word in, one word out), eight neighbouring lanes one
-// 32-block.
-__global__ void __launch_bounds__(256) k_q8_to_frag(const int8_t* __restrict__ xq, const float* __restrict__ xd, int k, size_t n_blocks,
-                                                    int8_t* __restrict__ q, float* __restrict__ a, float* __restrict__ c) {
-    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;
-    const size_t blk = quad >> 3;
-    const bool live = blk < n_blocks;   // no early exit: the shuffles below need the whole warp
-    const uint32_t w = live ? reinterpret_cast<const uint32_t*>(xq)[quad] : 0u;
-    int sum = __dp4a(int(w), 0x01010101, 0);   // the four signed codes added up
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (!live) return;
-    const int bpr = k / kQ8, j = int(quad & 7);
-    const size_t row = blk / bpr;
-    const int rb = int(blk % bpr), b = rb >> 1, sh = rb & 1, hi = j >> 2, t = j & 3;
-    reinterpret_cast<uint32_t*>(q + row * k)[(b * 4 + t) * 4 + sh * 2 + hi] = w;
-    if (j == 0) {
-        const float d = xd[blk];
-        a[blk] = sh ? d * 0.0625f : d;
-        c[blk] = __int_as_float(kMagicBits - (sh ? 16 * sum : sum));
-    }
-}
-
-__global__ void __launch_bounds__(256) k_quant_frag(const float* __restrict__ x, int k, size_t n_blocks, int8_t* __restrict__ q,
-                                                    float* __restrict__ a, float* __restrict__ c, int block64) {
-    pdl_wait();
-    pdl_trigger();
-    const size_t quad = size_t(blockIdx.x) * 256 + threadIdx.x;   // (the number of blocks is a multiple of four: warps are live as a whole)
-    quant_frag_quad(x, k, quad, quad < n_blocks * 8, q, a, c, block64 != 0);
-}
+#include "frx_quant.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // Grouping: the distinct experts of up to 64 tokens in ascending id, each with its tokens in
@@ -603,334 +398,7 @@ __host__ __device__ inline SmemPlan smem_plan(int kdim, uint32_t chunk_bytes, in
     return s;
 }
 
-// `count` units of 16 M rows against the item's tokens, continuing the running sums:
-// acc_lo = {M row g, column 2*t4; M row g, column 2*t4+1}, acc_hi = the same columns of M row g + 8.
-// `units` points at the first unit in shared memory, `b0` is the index of its first 64-block.
-//
-// Per 64-weight block two MMAs, one per 32-value activation block. The 2-bit fields of a code
-// word sit at bits 0, 2, 4, 6 of each byte; the first MMA takes fields 0 and 1 (w and w >> 2
-// masked with 0x03), the second takes fields 2 and 3 *in place* (masked with 0x30, i.e. the
-// codes times 16), so one shift serves both. The factor 16 is undone exactly by the activation
-// scale table, which holds d / 16 for the second half. Every accumulator starts at the table's
-// kMagicBits - sum(a) of its token column (times 16 for the second half; the four accumulator
-// inputs of a lane are one 16-byte load, used as they come and left intact for the second group),
-// so it ends as kMagicBits + sum((q - 1) * a): read as a float and with kMagic subtracted, exactly
-// the block's integer dot product.
-// Two groups of 16 M rows (group 1 at units + gstride) share the activation fragments, scales and
-// biases of each block, which are read once for both.
-template <int UPC>   // units per call when known at compile time, else 0
-__device__ __forceinline__ void units_mma(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
-                                          const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
-                                          const int4* __restrict__ ci, int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
-    const int g = lane >> 2, t4 = lane & 3;
-    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
-    const uint8_t* codes = units + lane * 16;
-    const uint8_t* scales = units + kUnitCodeBytes + g * 8;
-    const uint4* bf_p = bfrag + b0 * 32 + lane;
-    const int4* ci_p = ci + (b0 * 4 + t4) * 2;
-    const uint64_t neg_magic = pack2(-kMagic, -kMagic);
-    const ulonglong2* da_p = da + b0 * 4 + t4;
-    const int n_units = UPC ? UPC : count;
-#pragma unroll(2)
-    for (int u = 0; u < n_units; ++u) {
-        uint4 c[2];
-        uint2 sc[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            c[r] = *reinterpret_cast<const uint4*>(codes + r * gstride + u * kUnitBytes);
-            sc[r] = *reinterpret_cast<const uint2*>(scales + r * gstride + u * kUnitBytes);
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int b = 2 * u + j;
-            const uint4 bf = bf_p[b * 32];
-            const int4 cq0 = ci_p[b * 8], cq1 = ci_p[b * 8 + 1];   // accumulator inputs: kMagicBits - sum(codes), per column, both halves
-            const ulonglong2 a = da_p[b * 4];   // {a0[c0], a0[c1]}, {a1[c0] / 16, a1[c1] / 16}
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const uint32_t w0 = j ? c[r].y : c[r].x, w1 = j ? c[r].w : c[r].z;
-                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
-                uint64_t lo0, hi0, lo1, hi1;
-                mma_u8s8_c4(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bf.x, bf.y, cq0);
-                mma_u8s8_c4(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bf.z, bf.w, cq1);
-                const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[r].x), s_hi = *reinterpret_cast<const __half2*>(&sc[r].y);
-                const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
-                const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
-                // a0 * S0 and (a1 / 16) * (16 * S1) are exact (11-bit scale x 13-bit integer), so one fused
-                // multiply-add rounds exactly where the reference's two statements round once.
-                const uint64_t sumi_lo = fma2(a.y, add2(lo1, neg_magic), mul2(a.x, add2(lo0, neg_magic)));
-                const uint64_t sumi_hi = fma2(a.y, add2(hi1, neg_magic), mul2(a.x, add2(hi0, neg_magic)));
-                // The weight scale is applied with scalar multiplies: a packed multiply followed by a
-                // packed add is contracted into one fused multiply-add by the assembler, which would
-                // round once where the reference rounds twice.
-                float s0, s1, s2, s3;
-                unpack2(sumi_lo, s0, s1);
-                unpack2(sumi_hi, s2, s3);
-                acc_lo[r] = add2(acc_lo[r], pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
-                acc_hi[r] = add2(acc_hi[r], pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
-            }
-        }
-    }
-}
-
-// The narrow form of units_mma, for items of at most kNarrowTok tokens (most items of a decode
-// batch: with 64 tokens over 512 experts an expert gets 1.75 tokens on average). The MMA's eight
-// token columns are used twice: the B operand of row group 0 carries the item's tokens in columns
-// 0..3 and zeros in columns 4..7, the B operand of row group 1 zeros in columns 0..3 and the tokens
-// in columns 4..7, and the two MMAs accumulate into one D. Lanes t4 = 0, 1 then hold group 0's sums
-// of tokens (0, 1) and (2, 3), lanes t4 = 2, 3 those of group 1, so every lane's float work is on
-// live values and there is half as much of it per row. Products, scaling and the order of the
-// additions per (row, token) are those of units_mma: the results are the same bits.
-// The item buffer must have been built for the narrow form (see build in k_stream): zeros in token
-// columns 4..7 of the B fragments, scale and bias entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1.
-template <int UPC, int BS = 32>   // BS: 16-byte vectors per block of the B fragments (32: eight token columns; 16: four)
-__device__ __forceinline__ void units_mma_narrow(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
-                                                 const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da,
-                                                 const int4* __restrict__ ci, int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
-    const int g = lane >> 2, t4 = lane & 3;
-    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
-    const uint8_t* codes = units + lane * 16;
-    const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
-    // B operand: lanes g < 4 carry token g for row group 0 and zeros for row group 1, lanes g >= 4
-    // zeros for group 0 and token g - 4 for group 1. The zeros never change, so each lane loads only
-    // its live fragment (a predicated load: half the shared-memory traffic of two full loads).
-    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 3) * 4 + t4);
-    const bool low = g < 4;
-    uint4 bfa = make_uint4(0u, 0u, 0u, 0u), bfb = bfa;
-    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + (b0 * 4 + t4) * 2);   // -(kMagic + sum of the codes), see build
-    const ulonglong2* da_p = da + b0 * 4 + t4;
-    const int n_units = UPC ? UPC : count;
-#pragma unroll(2)
-    for (int u = 0; u < n_units; ++u) {
-        const uint4 c0 = *reinterpret_cast<const uint4*>(codes + u * kUnitBytes);
-        const uint4 c1 = *reinterpret_cast<const uint4*>(codes + gstride + u * kUnitBytes);
-        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int b = 2 * u + j;
-            lds128_if(bfa, bf_a + b * (BS * 16), low);
-            lds128_if(bfb, bf_a + b * (BS * 16), !low);
-            const ulonglong2 nm = nm_p[b * 8];   // {first half: columns c0, c1}, {second half}
-            const ulonglong2 a = da_p[b * 4];
-            const uint32_t w0 = j ? c0.y : c0.x, w1 = j ? c0.w : c0.z;   // group 0: rows g, g + 8
-            const uint32_t x0 = j ? c1.y : c1.x, x1 = j ? c1.w : c1.z;   // group 1
-            const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
-            uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, kMagicBits);
-            mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, kMagicBits);
-            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
-            const float d_lo = j ? __high2float(s_lo) : __low2float(s_lo);
-            const float d_hi = j ? __high2float(s_hi) : __low2float(s_hi);
-            const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
-            const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
-            float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
-            unpack2(sumi_lo, s0, s1);
-            unpack2(sumi_hi, s2, s3);
-            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
-            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
-        }
-    }
-}
-
-// Four row groups at once for items of one or two tokens: the B operand of group j carries the
-// tokens in columns 2j, 2j + 1 and zeros elsewhere, the four MMAs accumulate into one D, and lane
-// (g, t4) finishes group t4: a quarter of the float work of units_mma per row, all of it live.
-// `units` points at the first unit of group 0 of the chunk, group j follows at j * gstride. The item
-// buffer is in the narrow form (zeros in token column 4; scale and bias entries of tokens 0, 1 at
-// the quad of lanes t4 = 0). Same products, same scaling, same order of additions per (row, token).
-template <int UPC, int BS = 32>
-__device__ __forceinline__ void units_mma_n2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
-                                             const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
-                                             int lane, uint64_t& acc_lo, uint64_t& acc_hi) {
-    const int g = lane >> 2, t4 = lane & 3;
-    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
-    const uint8_t* codes = units + lane * 16;
-    const uint8_t* scales = units + t4 * gstride + kUnitCodeBytes + g * 8;   // of the lane's own row group
-    // B operand of row group j: token g & 1 in the lanes with g >> 1 == j, zeros elsewhere; a lane loads
-    // only its live fragment, the zeros of the other three stay in registers
-    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 1) * 4 + t4);
-    uint4 bf[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) bf[j] = make_uint4(0u, 0u, 0u, 0u);
-    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + b0 * 8);
-    const ulonglong2* da_p = da + b0 * 4;
-    const int n_units = UPC ? UPC : count;
-#pragma unroll(1)
-    for (int u = 0; u < n_units; ++u) {
-        uint4 c[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4*>(codes + j * gstride + u * kUnitBytes);
-        const uint2 sc = *reinterpret_cast<const uint2*>(scales + u * kUnitBytes);
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-            const int b = 2 * u + jj;
-            const ulonglong2 nm = nm_p[b * 8];
-            const ulonglong2 a = da_p[b * 4];
-            uint32_t a0[16], a1[16], bb0[8], bb1[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                lds128_if(bf[j], bf_a + b * (BS * 16), (g >> 1) == j);
-                bb0[2 * j] = bf[j].x;
-                bb0[2 * j + 1] = bf[j].y;
-                bb1[2 * j] = bf[j].z;
-                bb1[2 * j + 1] = bf[j].w;
-                const uint32_t w0 = jj ? c[j].y : c[j].x, w1 = jj ? c[j].w : c[j].z;
-                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2;
-                a0[4 * j] = w0 & M0;
-                a0[4 * j + 1] = w1 & M0;
-                a0[4 * j + 2] = v0 & M0;
-                a0[4 * j + 3] = v1 & M0;
-                a1[4 * j] = w0 & M1;
-                a1[4 * j + 1] = w1 & M1;
-                a1[4 * j + 2] = v0 & M1;
-                a1[4 * j + 3] = v1 & M1;
-            }
-            uint64_t lo0, hi0, lo1, hi1;
-            mma_u8s8_chain4(lo0, hi0, a0, bb0, kMagicBits);
-            mma_u8s8_chain4(lo1, hi1, a1, bb1, kMagicBits);
-            const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc.x), s_hi = *reinterpret_cast<const __half2*>(&sc.y);
-            const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
-            const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
-            const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
-            const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
-            float s0, s1, s2, s3;   // scalar multiplies by the weight scale, as in units_mma
-            unpack2(sumi_lo, s0, s1);
-            unpack2(sumi_hi, s2, s3);
-            acc_lo = add2(acc_lo, pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
-            acc_hi = add2(acc_hi, pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
-        }
-    }
-}
-
-// Four row groups as two pairs in the narrow form (items of three or four tokens): the activation
-// fragments, scales and biases of a block are loaded once and serve both pairs.
-template <int UPC, int BS = 32>
-__device__ __forceinline__ void units_mma_n4x2(const uint8_t* __restrict__ units, uint32_t gstride, int count, int b0,
-                                               const uint4* __restrict__ bfrag, const ulonglong2* __restrict__ da, const int4* __restrict__ ci,
-                                               int lane, uint64_t (&acc_lo)[2], uint64_t (&acc_hi)[2]) {
-    const int g = lane >> 2, t4 = lane & 3;
-    constexpr uint32_t M0 = 0x03030303u, M1 = 0x30303030u;
-    const uint8_t* codes = units + lane * 16;
-    const uint8_t* scales = units + (t4 >> 1) * gstride + kUnitCodeBytes + g * 8;   // pair 0; pair 1 two groups on
-    const uint32_t bf_a = smem_u32(bfrag + b0 * BS + (g & 3) * 4 + t4);   // as in units_mma_narrow
-    const bool low = g < 4;
-    uint4 bfa = make_uint4(0u, 0u, 0u, 0u), bfb = bfa;
-    const ulonglong2* nm_p = reinterpret_cast<const ulonglong2*>(ci + (b0 * 4 + t4) * 2);
-    const ulonglong2* da_p = da + b0 * 4 + t4;
-    const int n_units = UPC ? UPC : count;
-#pragma unroll(1)
-    for (int u = 0; u < n_units; ++u) {
-        uint4 c[4];
-        uint2 sc[2];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4*>(codes + j * gstride + u * kUnitBytes);
-#pragma unroll
-        for (int pi = 0; pi < 2; ++pi) sc[pi] = *reinterpret_cast<const uint2*>(scales + 2 * pi * gstride + u * kUnitBytes);
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-            const int b = 2 * u + jj;
-            lds128_if(bfa, bf_a + b * (BS * 16), low);
-            lds128_if(bfb, bf_a + b * (BS * 16), !low);
-            const ulonglong2 nm = nm_p[b * 8];
-            const ulonglong2 a = da_p[b * 4];
-#pragma unroll
-            for (int pi = 0; pi < 2; ++pi) {
-                const uint4 c0 = c[2 * pi], c1 = c[2 * pi + 1];
-                const uint32_t w0 = jj ? c0.y : c0.x, w1 = jj ? c0.w : c0.z;
-                const uint32_t x0 = jj ? c1.y : c1.x, x1 = jj ? c1.w : c1.z;
-                const uint32_t v0 = w0 >> 2, v1 = w1 >> 2, y0 = x0 >> 2, y1 = x1 >> 2;
-                uint64_t lo0, hi0, lo1, hi1;
-                mma_u8s8_chain2(lo0, hi0, w0 & M0, w1 & M0, v0 & M0, v1 & M0, bfa.x, bfa.y, x0 & M0, x1 & M0, y0 & M0, y1 & M0, bfb.x, bfb.y, kMagicBits);
-                mma_u8s8_chain2(lo1, hi1, w0 & M1, w1 & M1, v0 & M1, v1 & M1, bfa.z, bfa.w, x0 & M1, x1 & M1, y0 & M1, y1 & M1, bfb.z, bfb.w, kMagicBits);
-                const __half2 s_lo = *reinterpret_cast<const __half2*>(&sc[pi].x), s_hi = *reinterpret_cast<const __half2*>(&sc[pi].y);
-                const float d_lo = jj ? __high2float(s_lo) : __low2float(s_lo);
-                const float d_hi = jj ? __high2float(s_hi) : __low2float(s_hi);
-                const uint64_t sumi_lo = fma2(a.y, add2(lo1, nm.y), mul2(a.x, add2(lo0, nm.x)));
-                const uint64_t sumi_hi = fma2(a.y, add2(hi1, nm.y), mul2(a.x, add2(hi0, nm.x)));
-                float s0, s1, s2, s3;
-                unpack2(sumi_lo, s0, s1);
-                unpack2(sumi_hi, s2, s3);
-                acc_lo[pi] = add2(acc_lo[pi], pack2(__fmul_rn(d_lo, s0), __fmul_rn(d_lo, s1)));
-                acc_hi[pi] = add2(acc_hi[pi], pack2(__fmul_rn(d_hi, s2), __fmul_rn(d_hi, s3)));
-            }
-        }
-    }
-}
-
-// The narrow forms start their accumulators at kMagicBits and add -(kMagic + sum of the codes) in
-// float (exact: both are integers below 2^24); `c` is the wide form's accumulator input,
-// kMagicBits - sum as an int32 behind a float pointer.
-__device__ __forceinline__ float narrow_bias(float c) { return -(kMagic + float(kMagicBits - __float_as_int(c))); }
-
-// The item buffer of a down item in the narrow form (B fragments of the item's at most kNarrowTok
-// tokens, BS 16-byte vectors per block; scales; -(kMagic + sum of the codes)) straight from the
-// (gate x, up x) pairs of the item's slots: h = silu(gate x) * up x is formed here and quantized as
-// k_quant_hidden does (quant/q2_0/q2_0.cpp:101-113: d = amax / 127, id = 1 / d, q = roundf(v * id),
-// d through fp16). A thread owns four consecutive values, eight neighbouring lanes one 32-block;
-// thread btid of NT (whole warps) takes part. The pairs were written by other SMs, during this
-// kernel or the one before: they are read from the L2.
-template <int BS>
-__device__ __noinline__ void build_hidden_narrow(const float2* __restrict__ gu, int ff, const Item* __restrict__ it, uint32_t* bw,
-                                                    float* daw, float* ciw, int btid, int NT) {
-    const int m = min(it->n_tok, kNarrowTok);
-    const int qpr = ff / 4, total = m * qpr;   // quads per row (a multiple of 32: whole warps stay together)
-    constexpr int kBatch = 2;                  // loads of this many quads are in flight together
-    for (int base = 0; base < total; base += kBatch * NT) {
-        float4 g0[kBatch], g1[kBatch];
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-            const int idx = base + k * NT + btid;
-            if (idx < total) {
-                const int g = idx / qpr, rq = idx - g * qpr;
-                const float4* src = reinterpret_cast<const float4*>(gu + size_t(it->slot[g]) * ff + size_t(rq) * 4);
-                g0[k] = __ldcg(src);
-                g1[k] = __ldcg(src + 1);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-            if (base + k * NT >= total) break;   // uniform for the warp
-            const int idx = base + k * NT + btid;
-            const bool live = idx < total;
-            const int g = live ? idx / qpr : 0, rq = live ? idx - g * qpr : 0;
-            float hv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (live) {
-                hv[0] = swiglu_ref(g0[k].x, g0[k].y);
-                hv[1] = swiglu_ref(g0[k].z, g0[k].w);
-                hv[2] = swiglu_ref(g1[k].x, g1[k].y);
-                hv[3] = swiglu_ref(g1[k].z, g1[k].w);
-            }
-            float am = fmaxf(fmaxf(fabsf(hv[0]), fabsf(hv[1])), fmaxf(fabsf(hv[2]), fabsf(hv[3])));
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            const float d = __fdiv_rn(am, 127.0f);
-            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-            int code[4], sum = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                code[i] = int(round_half_away(__fmul_rn(hv[i], id)));
-                sum += code[i];
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (live) {
-                const int rb = rq >> 3, j = rq & 7, b = rb >> 1, h = rb & 1, hi = j >> 2, t = j & 3;
-                bw[(b * BS + g * 4 + t) * 4 + h * 2 + hi] =
-                    uint32_t(code[0] & 0xff) | (uint32_t(code[1] & 0xff) << 8) | (uint32_t(code[2] & 0xff) << 16) | (uint32_t(code[3] & 0xff) << 24);
-                if (j == 0) {
-                    const float ds = __half2float(__float2half_rn(d));
-                    const float av = h ? ds * 0.0625f : ds, nv = -(kMagic + float(h ? 16 * sum : sum));
-                    const int dst = (b * 4 + (g >> 1)) * 4 + h * 2 + (g & 1);
-                    daw[dst] = av;
-                    daw[dst + 8] = av;
-                    const int cq = (b * 4 + (g >> 1)) * 8 + h * 2 + (g & 1);
-                    ciw[cq] = nv;
-                    ciw[cq + 16] = nv;
-                }
-            }
-        }
-    }
-}
+#include "frx_mma_forms.cuh"
 
 // UPC: units per units_mma call when known at compile time (gate/up: units per chunk; down: units
 // per group), else 0.
@@ -1363,675 +831,9 @@ __global__ void __launch_bounds__(NW * 32, 1) k_stream(const StreamParams p) {
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// The decode FFN as one kernel (items of at most kNarrowTok tokens): gate/up, then SwiGLU and the
-// quantization of the hidden rows, then down, with one ring of weight chunks per warp that is never
-// drained in between.
-//   A block owns the same share of the gate/up tasks and of the down tasks (roughly the same
-//   items). Its warps take the block's tasks round-robin over the whole sequence: first the gate/up
-//   tasks in item order, then the down tasks. A gate/up task is two row groups in chunks of four
-//   units of K, a down task four row groups in chunks of two units: the same 8 units = 4,608 bytes.
-//   A warp that has finished its gate/up tasks of an item adds their number to the item's counter
-//   (release). The hidden rows of an item are complete when its counter has reached the number of
-//   gate/up tasks of an expert; whoever builds a down item waits for that (acquire, bounded), reads
-//   the (gate x, up x) pairs of the item's slots, forms silu(gate x) * up x, quantizes it like
-//   k_quant_hidden and writes codes, scales and accumulator inputs straight into the item buffer.
-//   (Letting one warp build a whole item buffer, the first to get there, instead of all warps in
-//   shares, was measured and is slower: the lone builder's global-memory round trips are serial.)
-//   A block walks its down items starting from its second one: the first is shared with the block
-//   before, which reaches it last in its own gate/up pass, the last is shared with the block after,
-//   which took it first.
-// Blocks wait for counters that other blocks raise, so every block must be resident: the grid is
-// one block per SM (checked on the host), and every wait is bounded.
-// Products, scaling and the order of additions are those of k_stream: the same bits.
-constexpr int kMaxItemBufs4 = 4;                 // item buffers per half, at most
-constexpr int kFfnBS = 16;                       // 16-byte vectors per block of the B fragments: token columns 0..3
-constexpr uint32_t kFfnBfragBlock = kFfnBS * 16;
-struct FfnPlan {
-    uint32_t ring, g_bfrag, g_da, g_ci, g_item, d_bfrag, d_da, d_ci, d_item, bars, abort, total;
-};
-__host__ __device__ inline FfnPlan ffn_plan(int n, int ff, uint32_t chunk_bytes, int slots, int nbuf_g, int nbuf_d) {
-    const uint32_t nbg = uint32_t(n / kQK), nbd = uint32_t(ff / kQK);
-    FfnPlan s{};
-    uint32_t off = 0;
-    s.ring = off;
-    off += uint32_t(slots) * chunk_bytes;
-    off = (off + 127u) & ~127u;
-    s.g_bfrag = off;
-    off += uint32_t(nbuf_g) * nbg * kFfnBfragBlock;
-    s.g_da = off;
-    off += uint32_t(nbuf_g) * nbg * 64;
-    s.g_ci = off;
-    off += uint32_t(nbuf_g) * nbg * 128;
-    s.g_item = off;
-    off += uint32_t(nbuf_g) * 64;
-    s.d_bfrag = off;
-    off += uint32_t(nbuf_d) * nbd * kFfnBfragBlock;
-    s.d_da = off;
-    off += uint32_t(nbuf_d) * nbd * 64;
-    s.d_ci = off;
-    off += uint32_t(nbuf_d) * nbd * 128;
-    s.d_item = off;
-    off += uint32_t(nbuf_d) * 64;
-    s.bars = off;          // `slots` ring barriers, then ready/done of the gate/up buffers, then of the down buffers
-    off += uint32_t(slots + 4 * kMaxItemBufs4) * 8;
-    off = (off + 15u) & ~15u;
-    s.abort = off;
-    off += 16;
-    s.total = off;
-    return s;
-}
-constexpr int kFfnUnitsGu = 4, kFfnUnitsDn = 2;   // units of K per chunk and row group
-constexpr uint32_t kFfnChunkBytes = 2 * kFfnUnitsGu * kUnitBytes;
-static_assert(kFfnChunkBytes == 4 * kFfnUnitsDn * kUnitBytes, "one ring slot serves both halves");
+#include "frx_ffn.cuh"
 
-template <int NW>
-__global__ void __launch_bounds__(NW * 32, 1) k_ffn(const StreamParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, ctid = threadIdx.x;
-    const int nb_g = p.n / kQK, units_g = p.n / kUnitK, nb_d = p.ff / kQK, units_d = p.ff / kUnitK;
-    const uint32_t gbytes_g = uint32_t(units_g) * kUnitBytes, gbytes_d = uint32_t(units_d) * kUnitBytes;   // one row group
-    const int cpt_g = units_g / kFfnUnitsGu, cpt_d = units_d / kFfnUnitsDn, rpw = p.rpw;
-    constexpr uint32_t chunk_bytes = kFfnChunkBytes, half_bytes = chunk_bytes / 2, quarter_bytes = chunk_bytes / 4;
-    const int tpe_g = p.ff / 16, tpe_d = p.n / 64;   // tasks per expert
-    const size_t section_d = size_t(p.ff / 8) * gbytes_g;   // the down rows follow the gate/up groups in a blob
-    const int slots = NW * rpw, nbuf_g = p.nbuf, nbuf_d = p.nbuf_dn;
-    const FfnPlan sp = ffn_plan(p.n, p.ff, chunk_bytes, slots, nbuf_g, nbuf_d);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + sp.bars);
-    uint64_t* ready_g = bars + slots;
-    uint64_t* done_g = ready_g + kMaxItemBufs4;
-    uint64_t* ready_d = done_g + kMaxItemBufs4;
-    uint64_t* done_d = ready_d + kMaxItemBufs4;
-    uint64_t* full = bars + warp * rpw;                                   // this warp's ring barriers
-    uint8_t* ring = smem + sp.ring + size_t(warp) * rpw * chunk_bytes;    // this warp's ring slots
-    volatile int* abort = reinterpret_cast<volatile int*>(smem + sp.abort);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < slots; ++s) mbar_init(bars + s, 1);
-        for (int b = 0; b < 4 * kMaxItemBufs4; ++b) mbar_init(ready_g + b, NW);
-        *abort = 0;
-        mbar_fence_init();
-    }
-    pdl_wait();   // the items, the counters (zeroed) and the quantized x are complete
-    pdl_trigger();
-
-    const int n_items = p.status[1];
-    const long long tot_g = (long long)n_items * tpe_g, tot_d = (long long)n_items * tpe_d;
-    const long long lo_g = tot_g * blockIdx.x / gridDim.x, hi_g = tot_g * (blockIdx.x + 1) / gridDim.x;
-    const long long lo_d = tot_d * blockIdx.x / gridDim.x, hi_d = tot_d * (blockIdx.x + 1) / gridDim.x;
-    const int nt_g = int(hi_g - lo_g), nt_d = int(hi_d - lo_d);
-    if (nt_g + nt_d <= 0) return;   // uniform for the block
-    // segments: runs of consecutive tasks of one item
-    const int fi_g = nt_g > 0 ? int(lo_g / tpe_g) : 0, nseg_g = nt_g > 0 ? int((hi_g - 1) / tpe_g) - fi_g + 1 : 0;
-    const int fi_d = nt_d > 0 ? int(lo_d / tpe_d) : 0, nseg_d = nt_d > 0 ? int((hi_d - 1) / tpe_d) - fi_d + 1 : 0;
-    const int rot_d = nseg_d > 1 ? 1 : 0;
-    const int ahead_g = nbuf_g - 1, ahead_d = nbuf_d - 1;
-    __syncthreads();
-    auto item_d = [&](int s) { return fi_d + (s + rot_d) % nseg_d; };   // the item of the s-th down segment in walking order
-    auto seg_g = [&](int s, long long& a, int& len) {
-        const long long it = fi_g + s;
-        a = max(lo_g, it * tpe_g);
-        len = int(min(hi_g, (it + 1) * tpe_g) - a);
-    };
-    auto seg_d = [&](int s, long long& a, int& len) {
-        const long long it = item_d(s);
-        a = max(lo_d, it * tpe_d);
-        len = int(min(hi_d, (it + 1) * tpe_d) - a);
-    };
-
-    // ---- this warp's stream of chunks (lane 0 issues). The block's tasks are numbered through both
-    // halves; task i belongs to warp i % NW. is_j: index of the task within its half.
-    int is_ph = 0, is_s = -1, is_off = 0, is_len = 0, is_j = warp, is_c = 0, is_slot = 0, is_task = 0;
-    long long is_a = 0;
-    const uint8_t* is_blob = nullptr;
-    auto is_seek = [&]() {   // to the segment that holds task is_j of half is_ph, or on to the next half; is_ph = 2: nothing left
-        while (is_ph < 2) {
-            if (is_s >= 0 && is_j < is_off + is_len) {
-                is_task = int((is_a + (is_j - is_off)) % (is_ph ? tpe_d : tpe_g));
-                return;
-            }
-            if (is_s + 1 < (is_ph ? nseg_d : nseg_g)) {
-                ++is_s;
-                is_off += is_len;
-                if (is_ph) seg_d(is_s, is_a, is_len);
-                else seg_g(is_s, is_a, is_len);
-                is_blob = p.items[is_ph ? item_d(is_s) : fi_g + is_s].blob + (is_ph ? section_d : size_t(0));
-            } else {
-                ++is_ph;
-                is_s = -1;
-                is_off = 0;
-                is_len = 0;
-                is_j = ((warp - nt_g) % NW + NW) % NW;   // the first down task of this warp
-            }
-        }
-    };
-    auto issue_next = [&]() {   // lane 0 only
-        if (is_ph >= 2) return;
-        mbar_expect_tx(full + is_slot, chunk_bytes);
-        uint8_t* dst = ring + size_t(is_slot) * chunk_bytes;
-        int cpt;
-        if (is_ph == 0) {   // the same K range of the task's two groups
-            const uint8_t* src = is_blob + size_t(is_task) * (2 * gbytes_g) + size_t(is_c) * half_bytes;
-            bulk_g2s(dst, src, half_bytes, full + is_slot);
-            bulk_g2s(dst + half_bytes, src + gbytes_g, half_bytes, full + is_slot);
-            cpt = cpt_g;
-        } else {            // of the task's four groups
-            const uint8_t* src = is_blob + size_t(is_task) * (4 * gbytes_d) + size_t(is_c) * quarter_bytes;
-#pragma unroll
-            for (int gq = 0; gq < 4; ++gq) bulk_g2s(dst + gq * quarter_bytes, src + size_t(gq) * gbytes_d, quarter_bytes, full + is_slot);
-            cpt = cpt_d;
-        }
-        if (++is_slot == rpw) is_slot = 0;
-        if (++is_c == cpt) {
-            is_c = 0;
-            is_j += NW;
-            is_seek();
-        }
-    };
-    if (lane == 0) {
-        is_seek();
-        for (int k = 0; k < rpw; ++k) issue_next();
-    }
-    int cs_slot = 0;
-    uint32_t cs_phase = 0;
-    auto chunk_wait = [&]() -> const uint8_t* {
-        mbar_wait_bounded(full + cs_slot, cs_phase, abort, p.wait_ns);
-        return ring + size_t(cs_slot) * chunk_bytes;
-    };
-    auto chunk_done = [&]() {
-        __syncwarp();
-        if (lane == 0) issue_next();
-        if (++cs_slot == rpw) {
-            cs_slot = 0;
-            cs_phase ^= 1u;
-        }
-    };
-
-    // ---- item buffers. gate/up: column g of the B fragments, scales and accumulator inputs <- the
-    // quantized x row of the item's g-th token, in the narrow form (zeros in token columns 4..7, the
-    // entries of lanes t4 = 2, 3 equal to those of t4 = 0, 1).
-    auto build_x = [&](int s, int btid, int NT) {
-        const Item* it = p.items + fi_g + s;
-        const int buf = s % nbuf_g;
-        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.g_bfrag + buf * (nb_g * kFfnBfragBlock));
-        float* daw = reinterpret_cast<float*>(smem + sp.g_da + buf * (nb_g * 64));
-        float* ciw = reinterpret_cast<float*>(smem + sp.g_ci + buf * (nb_g * 128));
-        if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.g_item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
-        const int m = min(it->n_tok, kNarrowTok);
-        const int vpr = nb_g * 4;   // 16-byte vectors per row
-        for (int base = btid; base < m * vpr; base += 4 * NT) {
-            uint4 v[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int idx = base + k * NT;
-                if (idx < m * vpr) {
-                    const int g = idx / vpr, r = idx % vpr;
-                    v[k] = reinterpret_cast<const uint4*>(p.aq + size_t(slot_token(it->slot[g], p.K, p.TK)) * p.n)[r];
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int idx = base + k * NT;
-                if (idx < m * vpr) {
-                    const int g = idx / vpr, r = idx % vpr;
-                    reinterpret_cast<uint4*>(bw)[(r >> 2) * kFfnBS + g * 4 + (r & 3)] = v[k];
-                }
-            }
-        }
-        for (int idx = btid; idx < m * nb_g * 2; idx += NT) {
-            const int g = idx / (nb_g * 2), r = idx % (nb_g * 2), b = r >> 1, h = r & 1;
-            const size_t row = size_t(slot_token(it->slot[g], p.K, p.TK));
-            const float av = p.aa[row * (nb_g * 2) + r], cv = p.ac[row * (nb_g * 2) + r];
-            const int dst = (b * 4 + (g >> 1)) * 4 + h * 2 + (g & 1);
-            daw[dst] = av;
-            daw[dst + 8] = av;
-            const float nv = narrow_bias(cv);
-            const int cq = (b * 4 + (g >> 1)) * 8 + h * 2 + (g & 1);
-            ciw[cq] = nv;
-            ciw[cq + 16] = nv;
-        }
-    };
-    // down: the same form from the item's hidden rows, which are made here from the (gate x, up x)
-    // pairs. A thread owns four consecutive values, eight neighbouring lanes one 32-block.
-    auto build_h = [&](int s, int btid, int NT) {
-        const int item = item_d(s);
-        const Item* it = p.items + item;
-        const int buf = s % nbuf_d;
-        if (lane == 0) {   // every gate/up task of the item has been counted
-            const int* c = p.cnt + item;
-            if (ld_acquire_gpu(c) < tpe_g && !*abort) {
-                uint64_t t0 = 0;
-                for (uint32_t polls = 1;; ++polls) {
-                    if (ld_acquire_gpu(c) >= tpe_g) break;
-                    __nanosleep(polls > 16 ? 200 : 40);
-                    if ((polls & 31u) == 0) {
-                        if (*abort) break;
-                        const uint64_t now = global_ns();
-                        if (t0 == 0) {
-                            t0 = now;
-                        } else if (now - t0 > p.wait_ns) {
-                            *abort = 1;
-                            break;
-                        }
-                    }
-                }
-            }
-        }
-        __syncwarp();
-        uint32_t* bw = reinterpret_cast<uint32_t*>(smem + sp.d_bfrag + buf * (nb_d * kFfnBfragBlock));
-        float* daw = reinterpret_cast<float*>(smem + sp.d_da + buf * (nb_d * 64));
-        float* ciw = reinterpret_cast<float*>(smem + sp.d_ci + buf * (nb_d * 128));
-        if (btid < kItemWords) reinterpret_cast<uint32_t*>(smem + sp.d_item + buf * 64)[btid] = reinterpret_cast<const uint32_t*>(it)[btid];
-        build_hidden_narrow<kFfnBS>(p.gu, p.ff, it, bw, daw, ciw, btid, NT);
-    };
-
-    auto out_row = [&](int sl) -> float* { return sl >= p.TK ? p.ysh + size_t(sl - p.TK) * p.n : p.y + size_t(sl) * p.n; };
-    auto put2 = [&](float* o, int row, float v0, float v8) {
-        o[row] = v0;
-        o[row + 8] = v8;
-    };
-    const int g = lane >> 2, t4 = lane & 3;
-
-    // ---- gate/up
-    if (ahead_g == 2 && nseg_g >= 2) {   // the first two items side by side, one half of the warps each
-        constexpr int H = NW / 2;
-        build_x(warp < H ? 0 : 1, warp < H ? ctid : ctid - H * 32, warp < H ? H * 32 : (NW - H) * 32);
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(ready_g + 0);
-            mbar_arrive(ready_g + 1);
-        }
-    } else {
-        for (int q = 0; q < ahead_g && q < nseg_g; ++q) {
-            build_x(q, ctid, NW * 32);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ready_g + q % nbuf_g);
-        }
-    }
-    int off = 0;
-    for (int s = 0; s < nseg_g; ++s) {
-        const int buf = s % nbuf_g;
-        mbar_wait_bounded(ready_g + buf, uint32_t(s / nbuf_g) & 1u, abort, p.wait_ns);
-        long long a;
-        int len;
-        seg_g(s, a, len);
-        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.g_bfrag + buf * (nb_g * kFfnBfragBlock));
-        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.g_da + buf * (nb_g * 64));
-        const int4* ci = reinterpret_cast<const int4*>(smem + sp.g_ci + buf * (nb_g * 128));
-        const Item* its = reinterpret_cast<const Item*>(smem + sp.g_item + buf * 64);
-        const int m = its->n_tok;
-        const int c0 = 2 * (t4 & 1), c1 = c0 + 1, rn = t4 >> 1;
-        int mine = 0;
-        for (int j = off + ((warp - off % NW) % NW + NW) % NW; j < off + len; j += NW) {
-            const int task = int((a + (j - off)) % tpe_g);
-            uint64_t acc_lo = 0ull, acc_hi = 0ull;
-            for (int c = 0; c < cpt_g; ++c) {
-                const uint8_t* cp = chunk_wait();
-                units_mma_narrow<kFfnUnitsGu, kFfnBS>(cp, half_bytes, kFfnUnitsGu, 2 * c * kFfnUnitsGu, bfrag, da, ci, lane, acc_lo, acc_hi);
-                chunk_done();
-            }
-            float sum[4];
-            unpack2(acc_lo, sum[0], sum[1]);
-            unpack2(acc_hi, sum[2], sum[3]);
-            const int row = (task * 2 + rn) * 8 + g;
-            if (c0 < m) p.gu[size_t(its->slot[c0]) * p.ff + row] = make_float2(sum[0], sum[2]);
-            if (c1 < m) p.gu[size_t(its->slot[c1]) * p.ff + row] = make_float2(sum[1], sum[3]);
-            ++mine;
-        }
-        off += len;
-        __syncwarp();
-        if (lane == 0) {
-            if (mine) red_release_gpu_add(p.cnt + fi_g + s, mine);   // this warp's rows of the item are written
-            mbar_arrive(done_g + buf);
-        }
-        if (s + ahead_g < nseg_g) {
-            const int nxt = (s + ahead_g) % nbuf_g;   // the buffer of segment s - 1
-            if (s >= 1) mbar_wait_bounded(done_g + nxt, uint32_t((s - 1) / nbuf_g) & 1u, abort, p.wait_ns);
-            build_x(s + ahead_g, ctid, NW * 32);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ready_g + nxt);
-        }
-    }
-
-    // ---- down (this warp's weight chunks of it are already on their way)
-    for (int q = 0; q < ahead_d && q < nseg_d; ++q) {
-        build_h(q, ctid, NW * 32);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(ready_d + q % nbuf_d);
-    }
-    off = 0;
-    for (int s = 0; s < nseg_d; ++s) {
-        const int buf = s % nbuf_d;
-        mbar_wait_bounded(ready_d + buf, uint32_t(s / nbuf_d) & 1u, abort, p.wait_ns);
-        long long a;
-        int len;
-        seg_d(s, a, len);
-        const uint4* bfrag = reinterpret_cast<const uint4*>(smem + sp.d_bfrag + buf * (nb_d * kFfnBfragBlock));
-        const ulonglong2* da = reinterpret_cast<const ulonglong2*>(smem + sp.d_da + buf * (nb_d * 64));
-        const int4* ci = reinterpret_cast<const int4*>(smem + sp.d_ci + buf * (nb_d * 128));
-        const Item* its = reinterpret_cast<const Item*>(smem + sp.d_item + buf * 64);
-        const int m = its->n_tok;
-        for (int j = off + ((warp - (nt_g + off) % NW) % NW + NW) % NW; j < off + len; j += NW) {
-            const int task = int((a + (j - off)) % tpe_d);
-            if (m <= 2) {   // lane (g, t4) finishes row group t4 for tokens 0 and 1
-                uint64_t acc_lo = 0ull, acc_hi = 0ull;
-                for (int c = 0; c < cpt_d; ++c) {
-                    const uint8_t* cp = chunk_wait();
-                    units_mma_n2<kFfnUnitsDn, kFfnBS>(cp, quarter_bytes, kFfnUnitsDn, 2 * c * kFfnUnitsDn, bfrag, da, ci, lane, acc_lo, acc_hi);
-                    chunk_done();
-                }
-                float sum[4];
-                unpack2(acc_lo, sum[0], sum[1]);
-                unpack2(acc_hi, sum[2], sum[3]);
-                const int row = (task * 4 + t4) * 16 + g;
-                put2(out_row(its->slot[0]), row, sum[0], sum[2]);
-                if (m > 1) put2(out_row(its->slot[1]), row, sum[1], sum[3]);
-            } else {        // two pairs in the narrow form: lanes t4 = 0, 1 finish the first group of a pair, 2, 3 the second
-                uint64_t acc_lo[2] = {0ull, 0ull}, acc_hi[2] = {0ull, 0ull};
-                for (int c = 0; c < cpt_d; ++c) {
-                    const uint8_t* cp = chunk_wait();
-                    units_mma_n4x2<kFfnUnitsDn, kFfnBS>(cp, quarter_bytes, kFfnUnitsDn, 2 * c * kFfnUnitsDn, bfrag, da, ci, lane, acc_lo, acc_hi);
-                    chunk_done();
-                }
-                const int t0 = 2 * (t4 & 1), t1 = t0 + 1;
-                float* o0 = t0 < m ? out_row(its->slot[t0]) : nullptr;
-                float* o1 = t1 < m ? out_row(its->slot[t1]) : nullptr;
-#pragma unroll
-                for (int pi = 0; pi < 2; ++pi) {
-                    float sum[4];
-                    unpack2(acc_lo[pi], sum[0], sum[1]);
-                    unpack2(acc_hi[pi], sum[2], sum[3]);
-                    const int row = (task * 4 + 2 * pi + (t4 >> 1)) * 16 + g;
-                    if (o0) put2(o0, row, sum[0], sum[2]);
-                    if (o1) put2(o1, row, sum[1], sum[3]);
-                }
-            }
-        }
-        off += len;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(done_d + buf);
-        if (s + ahead_d < nseg_d) {
-            const int nxt = (s + ahead_d) % nbuf_d;
-            if (s >= 1) mbar_wait_bounded(done_d + nxt, uint32_t((s - 1) / nbuf_d) & 1u, abort, p.wait_ns);
-            build_h(s + ahead_d, ctid, NW * 32);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ready_d + nxt);
-        }
-    }
-    __syncthreads();
-    if (*abort) {
-        // A wait ran out: report it, and give copies still in flight time to land before the
-        // block's shared memory is released.
-        if (threadIdx.x == 0) p.status[0] = kDevWaitTimeout;
-        const uint64_t t0 = global_ns();
-        while (global_ns() - t0 < 2000000ull) {
-        }
-    }
-}
-
-// out[t] = sum over the token's slots in ascending expert id of w * y, then + ysh * sigmoid(gate).
-// A thread owns four consecutive elements of one token. The order entries, the weights and the rows
-// of eight slots at a time are loaded before the first addition (the loads do not depend on one
-// another, the additions keep their order), so the kernel is three round trips to memory long
-// instead of two per slot.
-constexpr int kCombineElems = 4, kCombineBatch = 8;
-__global__ void __launch_bounds__(256) k_combine_ordered(float* __restrict__ out, const float* __restrict__ y,
-                                                         const float* __restrict__ wts, const int32_t* __restrict__ order,
-                                                         const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
-                                                         int sh_lo, int sh_hi) {   // the shared expert's rows exist for tokens [sh_lo, sh_hi)
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * kCombineElems, t = blockIdx.y;   // n is a multiple of 128: four elements are all inside or all outside
-    if (threadIdx.x == 0) {
-        touch_l2(order + size_t(t) * K);
-        touch_l2(wts);
-        touch_l2(y);
-        touch_l2(out + size_t(t) * n);
-        if (ysh) touch_l2(ysh + size_t(t) * n);
-    }
-    pdl_wait();
-    pdl_trigger();
-    if (i >= n) return;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int k0 = 0; k0 < K; k0 += kCombineBatch) {
-        int s[kCombineBatch];
-        float w[kCombineBatch];
-        float4 v[kCombineBatch];
-#pragma unroll
-        for (int j = 0; j < kCombineBatch; ++j) s[j] = k0 + j < K ? order[t * K + k0 + j] : -1;
-#pragma unroll
-        for (int j = 0; j < kCombineBatch; ++j)
-            if (s[j] >= 0) {
-                w[j] = wts[s[j]];
-                v[j] = *reinterpret_cast<const float4*>(y + size_t(s[j]) * n + i);
-            }
-#pragma unroll
-        for (int j = 0; j < kCombineBatch; ++j)
-            if (s[j] >= 0) {
-                acc.x = __fadd_rn(acc.x, __fmul_rn(w[j], v[j].x));
-                acc.y = __fadd_rn(acc.y, __fmul_rn(w[j], v[j].y));
-                acc.z = __fadd_rn(acc.z, __fmul_rn(w[j], v[j].z));
-                acc.w = __fadd_rn(acc.w, __fmul_rn(w[j], v[j].w));
-            }
-    }
-    if (ysh && t >= sh_lo && t < sh_hi) {
-        const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
-        const float4 v = *reinterpret_cast<const float4*>(ysh + size_t(t) * n + i);
-        acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
-        acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, g));
-        acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, g));
-        acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, g));
-    }
-    *reinterpret_cast<float4*>(out + size_t(t) * n + i) = acc;
-}
-
-// ---- combine fused with the expert-parallel all-reduce over peer memory
-// Layout of a rank's communication buffer: two slots of partial sums [max_T][n] fp32, then
-// (256-byte aligned) flag words [FRX_EP_MAX_RANKS][kEpMaxBlocks] (word [q][b] is written by block b
-// of rank q: the number of the last call whose partial sums that block has published), then local
-// words: the number of calls completed, a ticket counter, and four cycle stamps of the last call.
-constexpr int kEpMaxBlocks = FRX_EP_MAX_BLOCKS;
-struct EpLayout {
-    size_t slot_floats, flags, state, total;
-};
-__host__ __device__ inline EpLayout ep_layout(int max_T, int n) {
-    EpLayout L{};
-    L.slot_floats = size_t(max_T) * n;
-    L.flags = align_up(2 * L.slot_floats * 4);
-    L.state = L.flags + size_t(FRX_EP_MAX_RANKS) * kEpMaxBlocks * 4;
-    L.total = L.state + 256;
-    return L;
-}
-struct EpParams {
-    int world, rank;
-    float* partial[FRX_EP_MAX_RANKS];      // slot 0 of every rank's buffer
-    uint32_t* flags[FRX_EP_MAX_RANKS];     // every rank's flag words
-    uint32_t* state;                       // local: [0] calls completed so far, [1] ticket, [8..15] cycle stamps
-    size_t slot_floats;
-    unsigned long long wait_ns;
-    int sh_lo, sh_hi;                      // this rank adds the shared expert's rows of tokens [sh_lo, sh_hi)
-};
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// out[t] = sum over ranks (in rank order) of that rank's partial sum; this rank's partial sum is
-// what k_combine_ordered computes. A thread owns kEpElems output elements of one token, and their
-// partial sums never leave its registers, so no barrier inside the GPU is needed. Block b stores
-// its part into this rank's buffer and raises its own flag word at every peer (one thread per
-// peer: system-scope fence, then the flag store), waits for block b of every peer (the only blocks
-// whose data it reads; one thread per peer polls), then issues the loads of all peers' parts
-// before the first addition, so the reads cost one NVLink round trip, and adds them in rank
-// order: every rank gets the same bits. Blocks of different GPUs wait on one another, so all blocks
-// of a launch must be resident at once: the host keeps the grid below the number of SMs times four.
-// A slot is reused every other call, which is safe: a block sees a peer's flag of call c only
-// after that peer's kernel of call c - 1 has ended (kernels of one stream run in order), i.e. after
-// the peer has read everything of call c - 1.
-constexpr int kEpElems = 4;   // consecutive elements per thread: one 16-byte access
-__device__ __forceinline__ float4 ld_peer4(const float* p) {   // never from a cache of this GPU: the buffer is rewritten every other call
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__global__ void __launch_bounds__(256) k_combine_allreduce(float* __restrict__ out, const float* __restrict__ y,
-                                                           const float* __restrict__ wts, const int32_t* __restrict__ order,
-                                                           const float* __restrict__ ysh, const float* __restrict__ gate, int n, int K,
-                                                           const EpParams ep, int* __restrict__ status) {
-    __shared__ int s_fail;
-    pdl_wait();
-    pdl_trigger();
-    const int t = blockIdx.y;
-    const int i = (blockIdx.x * 256 + threadIdx.x) * kEpElems;   // n is a multiple of 128: a thread's four elements are all inside or all outside
-    const uint32_t bid = blockIdx.y * gridDim.x + blockIdx.x;
-    const bool stamp = bid == 0 && threadIdx.x == 0;
-    long long* stamps = reinterpret_cast<long long*>(ep.state + 8);
-    const uint32_t call = ep.state[0] + 1;   // the same in every block: state[0] only changes after all blocks have read it
-    const size_t slot = size_t(call & 1u) * ep.slot_floats;
-    if (threadIdx.x == 0) s_fail = 0;
-    if (stamp) stamps[0] = clock64();
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (i < n) {
-        for (int k = 0; k < K; ++k) {
-            const int s = order[t * K + k];
-            if (s >= 0) {
-                const float w = wts[s];
-                const float4 v = *reinterpret_cast<const float4*>(y + size_t(s) * n + i);
-                acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
-                acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
-                acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
-                acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
-            }
-        }
-        if (ysh && t >= ep.sh_lo && t < ep.sh_hi) {
-            const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
-            const float4 v = *reinterpret_cast<const float4*>(ysh + size_t(t) * n + i);
-            acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, g));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, g));
-            acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, g));
-        }
-        *reinterpret_cast<float4*>(ep.partial[ep.rank] + slot + size_t(t) * n + i) = acc;
-    }
-    // publish and wait, one thread per peer: the block's stores are ordered before these threads by
-    // the block barrier; each makes them visible to the system, raises this block's flag at its
-    // peer, and waits for the same block of that peer (flags only grow; the signed distance makes
-    // wrap-around harmless)
-    __syncthreads();
-    if (stamp) stamps[1] = clock64();
-    if (int(threadIdx.x) < ep.world && int(threadIdx.x) != ep.rank) {
-        const int q = threadIdx.x;
-        fence_acq_rel_sys();
-        st_relaxed_sys(ep.flags[q] + size_t(ep.rank) * kEpMaxBlocks + bid, call);
-        const uint32_t* theirs = ep.flags[ep.rank] + size_t(q) * kEpMaxBlocks + bid;
-        uint64_t t0 = 0;
-        uint32_t polls = 0;
-        while (int32_t(ld_acquire_sys(theirs) - call) < 0) {
-            if ((++polls & 63u) == 0) {
-                const uint64_t now = global_ns();
-                if (t0 == 0) {
-                    t0 = now;
-                } else if (now - t0 > ep.wait_ns) {
-                    s_fail = 1;
-                    break;
-                }
-            }
-        }
-    }
-    __syncthreads();
-    if (stamp) stamps[2] = clock64();
-    if (s_fail) {
-        if (threadIdx.x == 0) status[0] = kDevWaitTimeout;
-    } else if (i < n) {
-        float4 v[FRX_EP_MAX_RANKS];
-#pragma unroll
-        for (int q = 0; q < FRX_EP_MAX_RANKS; ++q)   // every peer's part is requested before any is used
-            if (q < ep.world && q != ep.rank) v[q] = ld_peer4(ep.partial[q] + slot + size_t(t) * n + i);
-        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-        for (int q = 0; q < FRX_EP_MAX_RANKS; ++q) {
-            if (q >= ep.world) break;
-            const float4 a = q == ep.rank ? acc : v[q];
-            if (q == 0) {
-                sum = a;
-            } else {
-                sum.x = __fadd_rn(sum.x, a.x);
-                sum.y = __fadd_rn(sum.y, a.y);
-                sum.z = __fadd_rn(sum.z, a.z);
-                sum.w = __fadd_rn(sum.w, a.w);
-            }
-        }
-        *reinterpret_cast<float4*>(out + size_t(t) * n + i) = sum;
-    }
-    if (stamp) stamps[3] = clock64();
-    // the call is complete on this rank once every block has passed its wait: a ticket counts
-    // them and the last one advances the call number
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t blocks = gridDim.x * gridDim.y;
-        if (atomicAdd(&ep.state[1], 1u) == blocks - 1) {
-            ep.state[1] = 0;
-            __threadfence();
-            ep.state[0] = call;
-        }
-    }
-}
-
-// Expert-parallel prefill: this rank's part of the weighted sum, out[t] = sum over the token's
-// slots whose expert is held here (e_map[id] >= 0), in ascending expert id, of w * y; tokens with
-// no such slot get zeros (the rows are then summed over the ranks). One block per token.
-__global__ void __launch_bounds__(256) k_combine_partial(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
-                                                         const int32_t* __restrict__ ids, const int32_t* __restrict__ e_map, int n, int K) {
-    __shared__ int s_slot[32];
-    __shared__ float s_w[32];
-    __shared__ int s_cnt;
-    const int t = blockIdx.x;
-    if (threadIdx.x == 0) s_cnt = 0;
-    __syncthreads();
-    if (int(threadIdx.x) < K) {
-        const int k = threadIdx.x, e = ids[size_t(t) * K + k];
-        if (e_map[e] >= 0) {
-            int rank = 0;   // among the token's local slots, by expert id (then by k)
-            for (int j = 0; j < K; ++j) {
-                const int ej = ids[size_t(t) * K + j];
-                if (e_map[ej] >= 0 && (ej < e || (ej == e && j < k))) ++rank;
-            }
-            s_slot[rank] = t * K + k;
-            s_w[rank] = wts[size_t(t) * K + k];
-            atomicAdd(&s_cnt, 1);
-        }
-    }
-    __syncthreads();
-    const int cnt = s_cnt;
-    for (int i = threadIdx.x * 4; i < n; i += 256 * 4) {
-        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int r = 0; r < cnt; ++r) {
-            const float w = s_w[r];
-            const float4 v = *reinterpret_cast<const float4*>(y + size_t(s_slot[r]) * n + i);
-            acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
-            acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
-        }
-        *reinterpret_cast<float4*>(out + size_t(t) * n + i) = acc;
-    }
-}
-
-// k_moe_combine / k_stream_combine semantics: k order, as the hit list gives it
-__global__ void __launch_bounds__(256) k_combine_hits(float* __restrict__ out, const float* __restrict__ yh,
-                                                      const float* __restrict__ w, const int32_t* __restrict__ hit_n,
-                                                      const float* __restrict__ shexp, const float* __restrict__ gate, int n, int K) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
-    if (i >= n) return;
-    const int kn = hit_n ? hit_n[t] : K;
-    float acc = 0.0f;
-    for (int k = 0; k < kn; ++k) acc = __fadd_rn(acc, __fmul_rn(w[t * K + k], yh[(size_t(t) * K + k) * n + i]));
-    if (shexp) {
-        const float g = gate ? sigmoid_ref(gate[t]) : 1.0f;
-        acc = __fadd_rn(acc, __fmul_rn(shexp[size_t(t) * n + i], g));
-    }
-    out[size_t(t) * n + i] = acc;
-}
+#include "frx_combine.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // moe_hits grouping: items from per-token lists of expert pointers. Slots s = t * K + k with
