@@ -249,6 +249,8 @@ def run_frx(args):
         moe.check(moe.lib.frx_debug_set_evict_first(args.evict_first))
     if args.down_item_weight is not None:
         moe.check(moe.lib.frx_debug_set_down_item_weight(args.down_item_weight))
+    if args.small_limits:
+        moe.check(moe.lib.frx_debug_set_small_launch_limits(*[int(v) for v in args.small_limits.split(",")]))
     if args.fold is not None:
         moe.check(moe.lib.frx_debug_set_fold_quant(args.fold))
     if args.ffn_buffers:
@@ -983,6 +985,7 @@ def main():
     ap.add_argument("--down-weight", type=int, default=None, help="tuning: weight (in 1/16) of a down task of a 3-4 token item in the split over blocks; 0 = even split")
     ap.add_argument("--evict-first", type=int, default=None, help="tuning: 0 copies the decode layer's weights with the default L2 policy")
     ap.add_argument("--down-item-weight", type=int, default=None, help="tuning: weight (in 1/16 of a task) of an item's buffer in down's split over blocks")
+    ap.add_argument("--small-limits", default=None, help="tuning: tasks per SM up to which blocks of 4 and of 8 warps are used, e.g. 4,8 (default) or 0,0")
     ap.add_argument("--fold", type=int, default=None, help="tuning: 0 runs the hidden-row quantizer as its own kernel")
     ap.add_argument("--ffn-buffers", default=None, help="tuning: item buffers of the fused FFN kernel, gate/up,down (e.g. 3,3)")
     ap.add_argument("--task4", type=int, default=None, help="tuning: 0 keeps two row groups per task in the decode layer")

@@ -911,6 +911,7 @@ __global__ void __launch_bounds__(256) k_pf_items(const int* __restrict__ bounds
 // ---------------------------------------------------------------------------------------------
 
 int g_nw = 16;   // consumer warps of k_stream (8, 12 or 16)
+int g_small4 = 0, g_small8 = 8;   // launches of at most this many tasks per SM take blocks of 4 / 8 warps with deeper rings (measured at 1 to 3 tokens: 8 warps 26.9 us per layer, 4 warps 27.7, 16 warps 28.9)
 int g_narrow = 1; // items of at most kNarrowTok tokens take the narrow form of the inner product
 int g_gu_chunks = 0;   // chunks per gate/up task (0: by shape)
 
@@ -952,8 +953,8 @@ int stream_cfg(int n, int ff, StreamCfg& c, long long max_items = 0, bool task4 
         cpt = chunks;
         const uint32_t chunk = task_bytes / uint32_t(cpt);
         int first = task4 ? (g_nw >= 12 ? 16 : 8) : g_nw;
-        if (max_tasks > 0 && max_tasks <= 4LL * sms) first = 4;
-        else if (max_tasks > 0 && max_tasks <= 8LL * sms) first = 8;
+        if (max_tasks > 0 && max_tasks <= (long long)g_small4 * sms) first = 4;
+        else if (max_tasks > 0 && max_tasks <= (long long)g_small8 * sms) first = 8;
         const int prefs[3] = {first, first > 16 ? 16 : first > 12 ? 12 : 8, 8};
         for (int k = 0; k < 3; ++k) {
             nw = prefs[k];
@@ -1658,6 +1659,12 @@ int frx_debug_set_gate_up_chunks(int chunks) {
 int frx_debug_set_consumer_warps(int nw) {
     if (nw != 8 && nw != 12 && nw != 16 && nw != 20) return FRX_ERR_ARG;
     g_nw = nw;
+    return FRX_OK;
+}
+int frx_debug_set_small_launch_limits(int four_warps, int eight_warps) {
+    if (four_warps < 0 || eight_warps < four_warps) return FRX_ERR_ARG;
+    g_small4 = four_warps;
+    g_small8 = eight_warps;
     return FRX_OK;
 }
 int frx_debug_set_narrow_items(int on) {

@@ -81,6 +81,7 @@ SIGNATURES = {
     "frx_debug_set_gate_up_chunks": (_i, [_i]),
     "frx_debug_set_narrow_items": (_i, [_i]),
     "frx_debug_set_four_group_tasks": (_i, [_i]),
+    "frx_debug_set_small_launch_limits": (_i, [_i, _i]),
     "frx_debug_set_fused_ffn": (_i, [_i]),
     "frx_debug_set_fold_quant": (_i, [_i]),
     "frx_debug_set_evict_first": (_i, [_i]),

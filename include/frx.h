@@ -77,6 +77,9 @@ const char* frx_profile_class_name(int cls);
  * frx_debug_set_wait_limit_ns: the longest a kernel waits on a barrier, a flag or a peer before it
  * gives up and reports FRX_ERR_DEVICE through the workspace status (default 2 s; 0 restores it). */
 int frx_debug_set_consumer_warps(int nw);
+/* Launches with at most `four_warps` (`eight_warps`) tasks per SM use blocks of 4 (8) warps with deeper copy rings
+ * instead of the setting above (defaults 0 and 8; 0, 0: never). */
+int frx_debug_set_small_launch_limits(int four_warps, int eight_warps);
 int frx_debug_set_gate_up_chunks(int chunks);
 int frx_debug_set_narrow_items(int on);
 int frx_debug_set_four_group_tasks(int on);
