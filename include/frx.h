@@ -213,7 +213,7 @@ int frx_moe_decode_ep(const void* experts, size_t stride, int E, int e_lo, int e
  * allocates and frees nothing. Same arguments and result as frx_moe_decode with yslot = null.
  * Limits and rules:
  *   - T, K, n, ff must satisfy frx_moe_decode_workspace_bytes(T, K, n, ff) <= 4 MiB (for n = 2048,
- *     ff = 512, K = 10 that is up to 32 tokens); otherwise FRX_ERR_WORKSPACE, and the message
+ *     ff = 512, K = 10 that is up to 24 tokens); otherwise FRX_ERR_WORKSPACE, and the message
  *     gives both sizes;
  *   - the first call on each device looks up the array's device address (with that device
  *     current); make that first call before any stream capture begins;
