@@ -37,10 +37,25 @@ def _worker(rank, world, port_no, ret):
     dist.all_reduce(tot)
     full = port.moe_layer(planar, planar.shape[1], None, n, ff, x, ids, wts)
     err = float(np.abs(tot.numpy() - full).max() / np.sqrt(np.mean(full.astype(np.float64) ** 2)))
+    # with a shared expert dealt among the ranks by token ranges: every rank adds the shared expert's
+    # gated output for its own tokens only, and the sum of the parts is the full layer again
+    from flashrt_b200.ep import shared_token_range
+    shared_blob = port.repack_expert(*synth.expert_ggml(rng, n, ff), n, ff)
+    gate = np.linspace(-1.0, 1.0, T).astype(np.float32)
+    full_sh, _, ysh = port.moe_layer(planar, planar.shape[1], shared_blob, n, ff, x, ids, wts, gate, want_slots=True)
+    t0, t1 = shared_token_range(rank, world, T)
+    part_sh = part.copy()
+    sig = 1.0 / (1.0 + np.exp(-gate.astype(np.float64)))
+    for t in range(t0, t1):
+        part_sh[t] = part_sh[t] + ysh[t] * np.float32(sig[t])
+    tot_sh = torch.from_numpy(part_sh)
+    dist.all_reduce(tot_sh)
+    err_sh = float(np.abs(tot_sh.numpy() - full_sh).max() / np.sqrt(np.mean(full_sh.astype(np.float64) ** 2)))
     ranges = [None] * world
     dist.all_gather_object(ranges, (lo, hi))
     if rank == 0:
         ret["err"] = err
+        ret["err_shared_dealt"] = err_sh
         ret["ranges"] = ranges
     dist.destroy_process_group()
 
@@ -56,6 +71,7 @@ def test_two_rank_partial_sums_reproduce_the_layer():
             p.join(120)
             assert p.exitcode == 0
         assert ret["err"] < 1e-6
+        assert ret["err_shared_dealt"] < 1e-6
         assert ret["ranges"] == [(0, 5), (5, 10)]
 
 
