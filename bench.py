@@ -25,8 +25,10 @@ CPU oracle at the full shape (512 experts):
                     three tokens: tokens/s, us per layer, HBM fraction (latency-limited by nature).
 
 With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the experts of every layer
-are sharded over the ranks (expert parallel), activations and routing are replicated, and each
-layer ends in an all-reduce of the [B][2048] partial sums; total work is fixed ("strong").
+are sharded over the ranks (expert parallel), activations and routing are replicated, the shared
+expert's tokens are dealt among the ranks, and each layer ends in an all-reduce of the [B][2048]
+partial sums inside its last kernel; total work is fixed ("strong"). The line then also carries
+`ep_allreduce`: where that kernel's time goes on every rank (its own cycle stamps).
 
 --impl reference times the reference's CPU implementation alone, on rank 0.
 """
